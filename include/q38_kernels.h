@@ -1,0 +1,242 @@
+/* q38_kernels.h — C ABI of the B200 (sm_100a) kernels of the ragged continuous-batching step.
+ *
+ * This is the drop-in boundary: every entry point replaces one launcher of the reference's internal
+ * kernel API `src/kernels/kernels.h` (namespace qwen38::kernels). Signatures use plain pointers,
+ * sizes and POD structs only (no C++ or torch types), so the library can be bound from C, C++, or any
+ * FFI. The contract of the reference launchers is kept (src/kernels/kernels.h:3-6):
+ *   - activations are row-major, M = number of tokens of the step;
+ *   - every pointer is a device pointer unless stated otherwise (the embedding table may be mapped
+ *     pinned host memory);
+ *   - every launcher is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ *     default stream), allocates nothing, never synchronises the host and may be captured into a CUDA
+ *     graph: all data-dependent sizes are read from device memory, only `num_seqs`, `num_tokens` and
+ *     `max_tokens_per_seq` are host values fixed per captured graph.
+ * Errors: launchers validate arguments on the host and return Q38_OK or a negative code; the message
+ * is available from q38_last_error(). Kernels never trap or assert; bounded device-side waits report
+ * through q38_device_error().
+ */
+#ifndef Q38_KERNELS_H_
+#define Q38_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q38_OK 0
+#define Q38_ERR_INVALID (-1) /* argument validation failed (reference: QWEN38_CHECK -> qwen38::Error) */
+#define Q38_ERR_CUDA (-2)    /* a CUDA runtime / driver call made by the launcher failed */
+
+#define Q38_PAGE_TOKENS 64 /* src/kernels/kernels.h:38 kPageTokens */
+#define Q38_HEAD_DIM 256   /* src/kernels/kernels.h:39 kHeadDim */
+
+typedef uint16_t q38_bf16; /* raw bfloat16 bits */
+typedef uint16_t q38_f16;  /* raw IEEE half bits */
+
+/* Ragged batch of one step. Replaces kernels::BatchDesc (src/kernels/kernels.h:22-31). */
+typedef struct q38_batch_desc {
+  int num_seqs;           /* B (host value) */
+  int num_tokens;         /* M (host value) */
+  int max_tokens_per_seq; /* upper bound of a sequence's run length in this step (host value) */
+  const int* seq_start;   /* [B + 1] */
+  const int* seq_slot;    /* [B] state slot = block-table row */
+  const int* seq_pos0;    /* [B] position of the sequence's first token of this step */
+  const int* tok_pos;     /* [M] absolute position of every token */
+  const int* tok_seq;     /* [M] sequence index of every token */
+} q38_batch_desc;
+
+/* Paged KV cache. Replaces kernels::KvCacheDesc (src/kernels/kernels.h:36-70); the byte layout of a
+ * (layer, page) block is the reference's: K [kv_head][64][256], V same, then for int8 the fp16 scales
+ * K [kv_head][64][4], V same. */
+#define Q38_KV_INT8 0
+#define Q38_KV_BF16 1
+typedef struct q38_kv_cache_desc {
+  uint8_t* pool;
+  int dtype; /* Q38_KV_INT8 | Q38_KV_BF16 */
+  int kv_heads;
+  int num_pages;
+  size_t page_bytes;
+  size_t layer_stride;
+  const int* block_table; /* [slots][max_pages_per_seq] */
+  int max_pages_per_seq;
+} q38_kv_cache_desc;
+size_t q38_kv_page_bytes(int dtype, int kv_heads); /* KvCacheDesc::page_bytes_for, kernels.h:66-69 */
+
+/* BQ weight (reference docs/FORMAT.md section 2). Replaces kernels::BQWeight (kernels.h:82-90). */
+typedef struct q38_bq_weight {
+  const uint8_t* lo;
+  const uint8_t* hi;      /* NULL for 4-bit */
+  const q38_bf16* scales;
+  int bits;               /* 4, 5, 6, 8 */
+  int n;                  /* padded rows, multiple of 128 */
+  int k;                  /* multiple of 64 */
+  int rows;               /* logical rows */
+} q38_bq_weight;
+
+/* GEMM epilogues. Replaces kernels::Epilogue / GemmEpilogue / GemmWorkspace (kernels.h:75-111). */
+#define Q38_EPI_STORE_BF16 0 /* out = bf16(C * rs) */
+#define Q38_EPI_SWIGLU 1     /* out[i] = bf16(silu(C[2i] * rs) * C[2i+1] * rs) */
+#define Q38_EPI_RESIDUAL 2   /* residual += C; xbf = bf16(residual); partials_out = sum of squares / 128 cols */
+#define Q38_EPI_STORE_F32 3  /* out = C * rs */
+typedef struct q38_gemm_epilogue {
+  int kind;
+  void* out;
+  int ldo;
+  int n_store;
+  float* residual;
+  q38_bf16* xbf;
+  float* partials_out;
+  const float* partials_in; /* rs = rsqrt(sum(partials_in[row]) / hidden + eps); NULL = 1 */
+  int hidden;
+  float eps;
+} q38_gemm_epilogue;
+
+typedef struct q38_gemm_workspace {
+  float* partials;       /* stream-K partial tiles */
+  size_t partial_floats;
+  int* counters;         /* per-tile arrival counters: zeroed once by the caller, self-resetting */
+  int num_counters;
+} q38_gemm_workspace;
+
+/* kernels.h:113-125 */
+#define Q38_GEMM_CONFIG_AUTO (-1)
+int q38_qgemm_num_configs(void);
+const char* q38_qgemm_config_name(int config);
+int q38_qgemm_config_tile_m(int config);
+/* C[M][N] = A[M][K] * W^T; A bf16 row-major with leading dimension K. (kernels::qgemm, kernels.h:120-121) */
+int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep,
+              const q38_gemm_workspace* ws, void* stream, int config);
+typedef int (*q38_gemm_tuning_lookup)(int bits, int n, int k, int m);
+void q38_set_qgemm_tuning(q38_gemm_tuning_lookup lookup); /* kernels::set_qgemm_tuning, kernels.h:124-125 */
+
+/* Dequantised weights W[n][k] as bf16 (row-major, padded rows included): the values the GEMM feeds to
+ * the tensor cores. Test / inspection helper of the in-register decoder (the reference checks the same
+ * logic on the host, tests/host/test_bq_layout.cpp). */
+int q38_bq_dequant(const q38_bq_weight* w, q38_bf16* out, void* stream);
+
+/* kernels::embed, kernels.h:131-134 */
+int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, int hidden, float* residual, q38_bf16* xbf,
+              float* partials, void* stream);
+
+/* kernels::QkNormRopeParams + qk_norm_rope_append, kernels.h:140-155 */
+typedef struct q38_qk_norm_rope_params {
+  const q38_bf16* proj; /* [M][ld_proj]: [q | gate | k | v] */
+  int ld_proj;
+  const float* q_norm;  /* [256], already 1 + w */
+  const float* k_norm;
+  float eps;
+  float rope_theta;
+  int num_q_heads;
+  int num_kv_heads;
+  q38_f16* q_out;       /* [M][nq][256] */
+  int attn_layer;
+} q38_qk_norm_rope_params;
+int q38_qk_norm_rope_append(const q38_qk_norm_rope_params* p, const q38_batch_desc* batch,
+                            const q38_kv_cache_desc* kv, void* stream);
+
+/* kernels::AttentionParams, attention_decode_splits, attention_decode, attention_prefill, kernels.h:157-179 */
+typedef struct q38_attention_params {
+  const q38_f16* q;      /* [M][nq][256] */
+  const q38_bf16* gate;  /* proj + nq*256, row stride ld_gate */
+  int ld_gate;
+  q38_bf16* out;         /* [M][nq*256] */
+  int num_q_heads;
+  int num_kv_heads;
+  int attn_layer;
+  float* split_scratch;  /* [B][nq][max_splits][256 + 2] floats */
+  int max_splits;
+} q38_attention_params;
+int q38_attention_decode_splits(int batch_seqs, int kv_heads, int num_sms, int max_splits);
+int q38_attention_decode(const q38_attention_params* p, const q38_batch_desc* batch, const q38_kv_cache_desc* kv,
+                         void* stream);
+int q38_attention_prefill(const q38_attention_params* p, const q38_batch_desc* batch, const q38_kv_cache_desc* kv,
+                          void* stream);
+
+/* kernels::GdnDims / GdnStateDesc, kernels.h:184-195 */
+typedef struct q38_gdn_dims {
+  int num_k_heads;
+  int num_v_heads;
+  int conv_dim; /* 2 * nk * 128 + nv * 128 */
+  int ld_proj;
+} q38_gdn_dims;
+typedef struct q38_gdn_state_desc {
+  float* recurrent;  /* [slots][gdn_layers][nv][128 dv][128 dk] */
+  q38_bf16* conv;    /* [slots][gdn_layers][3][conv_dim] */
+  int num_gdn_layers;
+} q38_gdn_state_desc;
+
+/* kernels::gdn_ab, kernels.h:197-199 */
+int q38_gdn_ab(const q38_bf16* xbf, int m, int hidden, const q38_bf16* w_ab, int rows, const float* partials_in,
+               float eps, float* ab_out, void* stream);
+
+/* kernels::GdnConvParams + gdn_conv, kernels.h:201-210 */
+typedef struct q38_gdn_conv_params {
+  const q38_bf16* proj;
+  const float* conv_w; /* [conv_dim][4] */
+  float* qkv;          /* [M][conv_dim] */
+  int gdn_layer;
+} q38_gdn_conv_params;
+int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d, const q38_batch_desc* batch,
+                 const q38_gdn_state_desc* st, void* stream);
+
+/* kernels::GdnRecurrenceParams + gdn_recurrence, kernels.h:212-228 */
+typedef struct q38_gdn_recurrence_params {
+  const float* qkv;
+  const float* ab;
+  const float* A;
+  const float* dt_bias;
+  const q38_bf16* z;
+  int ld_z;
+  const float* norm_w;
+  float eps;
+  q38_bf16* out;
+  int gdn_layer;
+} q38_gdn_recurrence_params;
+int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d, const q38_batch_desc* batch,
+                       const q38_gdn_state_desc* st, void* stream);
+
+/* kernels::SamplingParamsDev / SamplingArgs / sample / target_logprobs, kernels.h:233-260 */
+typedef struct q38_sampling_params_dev {
+  float temperature;
+  int top_k;
+  float top_p;
+  float min_p;
+  float presence_penalty;
+  float repetition_penalty;
+  uint64_t seed;
+} q38_sampling_params_dev;
+typedef struct q38_sampling_args {
+  float* logits;
+  int ld;
+  int vocab;
+  const q38_sampling_params_dev* params;
+  const int* row_slot;
+  int32_t* history;
+  int* history_len;
+  int history_cap;
+  const int* step;
+  int32_t* tokens_out;
+  float* logprob_out;
+} q38_sampling_args;
+int q38_sample(const q38_sampling_args* a, int batch, void* stream);
+int q38_target_logprobs(const float* logits, int ld, int vocab, const int32_t* targets, int rows, float* out,
+                        void* stream);
+
+/* Ragged-batch packing on the GPU. Replaces the host loops that fill the step metadata
+ * (src/model_runner.cpp:458-469 for prefill, :534-560 for decode): expands per-sequence
+ * (slot, pos0, count) rows into seq_start / tok_pos / tok_seq. Inputs are device arrays of num_seqs
+ * entries; outputs are the arrays a q38_batch_desc points at. num_tokens must equal sum(count). */
+int q38_pack_ragged(const int* seq_count, const int* seq_pos0, int num_seqs, int num_tokens, int* seq_start,
+                    int* tok_pos, int* tok_seq, void* stream);
+
+/* Diagnostics. */
+const char* q38_last_error(void);           /* message of the last failed launcher call on this thread */
+unsigned int q38_device_error(int clear);   /* non-zero if a bounded device-side wait ran out (synchronises) */
+int q38_num_sms(void);                      /* SM count of the current device as cached by the library */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q38_KERNELS_H_ */

@@ -1,0 +1,434 @@
+// Full-attention layers: fused q/k-norm + partial RoPE + KV quantise + paged append, split-KV GQA
+// flash-decoding with the merge + sigmoid output gate, and chunked-prefill causal attention over the
+// paged int8 / bf16 KV cache.
+//
+// Replaces kernels::qk_norm_rope_append, attention_decode(+_splits) and attention_prefill of the
+// reference (src/kernels/kernels.h:140-179; src/kernels/qk_norm_rope.cu, attention_decode.cu,
+// attention_prefill.cu). Page layout per (layer, page): K [kv_head][64][256], V same, then (int8) fp16
+// scales K [kv_head][64][4], V same (reference docs/FORMAT.md 3.1).
+#include <cmath>
+
+#include "common.cuh"
+#include "host_util.h"
+
+namespace q38 {
+namespace {
+
+constexpr int kHd = Q38_HEAD_DIM;
+constexpr int kPage = Q38_PAGE_TOKENS;
+
+struct KvView {
+  uint8_t* pool;
+  int int8;
+  int kv_heads;
+  int num_pages;
+  size_t page_bytes;
+  size_t layer_stride;
+  const int* block_table;
+  int max_pages_per_seq;
+
+  __device__ __forceinline__ size_t elem() const { return int8 ? 1 : 2; }
+  __device__ __forceinline__ size_t k_off(int head, int tok) const { return ((size_t)head * kPage + tok) * kHd * elem(); }
+  __device__ __forceinline__ size_t v_off(int head, int tok) const {
+    return (size_t)kv_heads * kPage * kHd * elem() + k_off(head, tok);
+  }
+  __device__ __forceinline__ size_t ks_off(int head, int tok) const {
+    return 2 * (size_t)kv_heads * kPage * kHd + ((size_t)head * kPage + tok) * 8;
+  }
+  __device__ __forceinline__ size_t vs_off(int head, int tok) const {
+    return ks_off(head, tok) + (size_t)kv_heads * kPage * 8;
+  }
+  // base of the (layer, page) block holding position `pos` of `slot`; nullptr if the table entry is invalid
+  __device__ __forceinline__ uint8_t* page_of(int layer, int slot, int pos) const {
+    const int page = block_table[(size_t)slot * max_pages_per_seq + pos / kPage];
+    if (page < 0 || page >= num_pages) return nullptr;
+    return pool + (size_t)layer * layer_stride + (size_t)page * page_bytes;
+  }
+};
+
+KvView make_view(const q38_kv_cache_desc& d) {
+  KvView v;
+  v.pool = d.pool;
+  v.int8 = d.dtype == Q38_KV_INT8;
+  v.kv_heads = d.kv_heads;
+  v.num_pages = d.num_pages;
+  v.page_bytes = d.page_bytes;
+  v.layer_stride = d.layer_stride;
+  v.block_table = d.block_table;
+  v.max_pages_per_seq = d.max_pages_per_seq;
+  return v;
+}
+
+struct RopeTable {
+  float inv_freq[32];  // evaluated on the host exactly as the CPU oracle does (src/ref/ops.cpp:104)
+};
+
+// ---------------------------------------------------------------------------------------------------
+// qk_norm_rope_append: one CTA per token, one warp per head (nq query heads, nkv key heads, nkv value
+// heads); a lane owns 8 consecutive dims. Rounding points (reference src/kernels/qk_norm_rope.cu:38-89,
+// oracle src/ref/ops.cpp:79-142): q -> fp16; K (after norm + RoPE) and V (raw) -> int8 with one fp16
+// scale = amax / 127 per 64 dims, q = clamp(rint(x / scale), +-127); or bf16.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
+                                                            const float* __restrict__ q_norm,
+                                                            const float* __restrict__ k_norm, float eps, int nq, int nkv,
+                                                            __half* __restrict__ q_out, int layer, RopeTable rope,
+                                                            const int* __restrict__ tok_pos,
+                                                            const int* __restrict__ tok_seq,
+                                                            const int* __restrict__ seq_slot, KvView kv) {
+  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= nq + 2 * nkv) return;
+  const int pos = tok_pos[m];
+  const bool is_q = warp < nq, is_k = !is_q && warp < nq + nkv;
+  const int head = is_q ? warp : is_k ? warp - nq : warp - nq - nkv;
+  const size_t col = is_q ? (size_t)head * kHd : is_k ? (size_t)(2 * nq + head) * kHd : (size_t)(2 * nq + nkv + head) * kHd;
+  const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)m * ld_proj + col + 8 * lane);
+  const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float x[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __low2float(rp[i]);
+    x[2 * i + 1] = __high2float(rp[i]);
+  }
+  if (is_q || is_k) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / float(kHd) + eps);
+    const float* w = (is_q ? q_norm : k_norm) + 8 * lane;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = x[i] * r * w[i];
+    // partial RoPE on dims (i, i + 32), i < 32: lanes 0-3 hold dims 0..31, lanes 4-7 hold dims 32..63
+    float other[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], 4);
+    if (lane < 8) {
+      const bool low = lane < 4;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int fi = 8 * (lane & 3) + i;
+        const float angle = float(pos) * rope.inv_freq[fi];
+        const float c = cosf(angle), s = sinf(angle);
+        // low half: x1 c - x2 s ; high half: x2 c + x1 s
+        x[i] = low ? x[i] * c - other[i] * s : x[i] * c + other[i] * s;
+      }
+    }
+  }
+  if (is_q) {
+    __half2 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+    *reinterpret_cast<uint4*>(q_out + ((size_t)m * nq + head) * kHd + 8 * lane) = *reinterpret_cast<uint4*>(h);
+    return;
+  }
+  const int slot = seq_slot[tok_seq[m]];
+  uint8_t* page = kv.page_of(layer, slot, pos);
+  if (page == nullptr) {
+    report_error(0x201);
+    return;
+  }
+  const int tok = pos % kPage;
+  if (kv.int8) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    // one scale per 64 dims = 8 lanes
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const __half sh = __float2half_rn(amax / 127.0f);
+    const float scale = __half2float(sh);
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float q = 0.0f;
+      if (scale > 0.0f) q = fminf(fmaxf(rintf(x[i] / scale), -127.0f), 127.0f);
+      packed[i >> 2] |= (uint32_t(int(q)) & 255u) << (8 * (i & 3));
+    }
+    uint8_t* dst = page + (is_k ? kv.k_off(head, tok) : kv.v_off(head, tok)) + 8 * lane;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
+    if ((lane & 7) == 0) {
+      uint8_t* sdst = page + (is_k ? kv.ks_off(head, tok) : kv.vs_off(head, tok)) + 2 * (lane >> 3);
+      *reinterpret_cast<__half*>(sdst) = sh;
+    }
+  } else {
+    __nv_bfloat162 b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    uint8_t* dst = page + (is_k ? kv.k_off(head, tok) : kv.v_off(head, tok)) + 16 * lane;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(b);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Token attention (generic path): one CTA per (split, kv head, row). A row is one query token with its
+// causal length L; the GROUP query heads of the kv head share every K/V byte read. Warps stride over
+// the keys of the split, a lane owns 8 dims; online softmax in the log2 domain; the warps' states are
+// merged through shared memory. With num_splits == 1 the CTA normalises, applies the sigmoid gate and
+// writes bf16 itself; otherwise it writes (acc[256], m, l) per head to the scratch for the merge kernel.
+// Serves decode (row = sequence, L = pos0 + 1) and, as the first prefill implementation, every prompt
+// token of a chunk (row = token, L = pos + 1).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kAttnWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int GROUP, bool INT8>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_token_kernel(
+    const __half* __restrict__ q, const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ out,
+    int nq, int layer, float* __restrict__ scratch, int max_splits, int num_splits, int decode_rows,
+    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, KvView kv) {
+  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int m, slot, L;
+  if (decode_rows) {
+    m = seq_start[row];
+    slot = seq_slot[row];
+    L = seq_pos0[row] + 1;
+  } else {
+    m = row;
+    slot = seq_slot[tok_seq[row]];
+    L = tok_pos[row] + 1;
+  }
+  // keys of this split (whole pages except possibly the last)
+  const int pages = (L + kPage - 1) / kPage;
+  const int pages_per_split = (pages + num_splits - 1) / num_splits;
+  const int t0 = min(L, split * pages_per_split * kPage), t1 = min(L, (split + 1) * pages_per_split * kPage);
+
+  float qv[GROUP][8];
+#pragma unroll
+  for (int h = 0; h < GROUP; ++h) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(q + ((size_t)m * nq + kvh * GROUP + h) * kHd + 8 * lane);
+    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(hp[i]);
+      qv[h][2 * i] = f.x * (kLog2e / 16.0f);  // 1 / sqrt(256), log2 domain
+      qv[h][2 * i + 1] = f.y * (kLog2e / 16.0f);
+    }
+  }
+  float mx[GROUP], l[GROUP], acc[GROUP][8];
+#pragma unroll
+  for (int h = 0; h < GROUP; ++h) {
+    mx[h] = -INFINITY;
+    l[h] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[h][i] = 0.0f;
+  }
+
+  for (int t = t0 + warp; t < t1; t += kAttnWarps) {
+    const uint8_t* page = kv.page_of(layer, slot, t);
+    if (page == nullptr) {
+      report_error(0x202);
+      break;
+    }
+    const int tok = t % kPage;
+    float kx[8], vx[8];
+    if constexpr (INT8) {
+      const uint2 kr = *reinterpret_cast<const uint2*>(page + kv.k_off(kvh, tok) + 8 * lane);
+      const uint2 vr = *reinterpret_cast<const uint2*>(page + kv.v_off(kvh, tok) + 8 * lane);
+      const float ks = __half2float(*reinterpret_cast<const __half*>(page + kv.ks_off(kvh, tok) + 2 * (lane >> 3)));
+      const float vs = __half2float(*reinterpret_cast<const __half*>(page + kv.vs_off(kvh, tok) + 2 * (lane >> 3)));
+      const uint32_t kw[2] = {kr.x, kr.y}, vw[2] = {vr.x, vr.y};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        kx[i] = float(int8_t(kw[i >> 2] >> (8 * (i & 3)))) * ks;
+        vx[i] = float(int8_t(vw[i >> 2] >> (8 * (i & 3)))) * vs;
+      }
+    } else {
+      const uint4 kr = *reinterpret_cast<const uint4*>(page + kv.k_off(kvh, tok) + 16 * lane);
+      const uint4 vr = *reinterpret_cast<const uint4*>(page + kv.v_off(kvh, tok) + 16 * lane);
+      const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr);
+      const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vr);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        kx[2 * i] = __low2float(kp[i]);
+        kx[2 * i + 1] = __high2float(kp[i]);
+        vx[2 * i] = __low2float(vp[i]);
+        vx[2 * i + 1] = __high2float(vp[i]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < GROUP; ++h) {
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += qv[h][i] * kx[i];
+      s = warp_sum(s);
+      const float mn = fmaxf(mx[h], s);
+      const float corr = exp2f(mx[h] - mn), p = exp2f(s - mn);
+      mx[h] = mn;
+      l[h] = l[h] * corr + p;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[h][i] = acc[h][i] * corr + p * vx[i];
+    }
+  }
+
+  // merge the warps' states: shared [warp][GROUP][256 + 2]
+  __shared__ float sm_acc[kAttnWarps][GROUP][kHd];
+  __shared__ float sm_ml[kAttnWarps][GROUP][2];
+#pragma unroll
+  for (int h = 0; h < GROUP; ++h) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm_acc[warp][h][8 * lane + i] = acc[h][i];
+    if (lane == 0) {
+      sm_ml[warp][h][0] = mx[h];
+      sm_ml[warp][h][1] = l[h];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < GROUP * kHd; idx += kAttnWarps * 32) {
+    const int h = idx / kHd, d = idx % kHd;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm_ml[w][h][0]);
+    float ll = 0.0f, a = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float mw = sm_ml[w][h][0];
+      const float c = mw == -INFINITY ? 0.0f : exp2f(mw - mm);
+      ll += sm_ml[w][h][1] * c;
+      a += sm_acc[w][h][d] * c;
+    }
+    const int qh = kvh * GROUP + h;
+    if (num_splits == 1) {
+      const float g = __bfloat162float(gate[(size_t)m * ld_gate + (size_t)qh * kHd + d]);
+      out[(size_t)m * nq * kHd + (size_t)qh * kHd + d] = __float2bfloat16_rn(a / ll * sigmoid_f(g));
+    } else {
+      float* dst = scratch + (((size_t)row * nq + qh) * max_splits + split) * (kHd + 2);
+      dst[d] = a;
+      if (d == 0) {
+        dst[kHd] = mm;
+        dst[kHd + 1] = ll;
+      }
+    }
+  }
+}
+
+// Merge of the splits + normalisation + sigmoid gate -> bf16 (reference attention_decode.cu:241-257).
+__global__ void __launch_bounds__(kHd) attn_merge_kernel(const float* __restrict__ scratch, int max_splits,
+                                                         int num_splits, const __nv_bfloat16* __restrict__ gate,
+                                                         int ld_gate, __nv_bfloat16* __restrict__ out, int nq,
+                                                         const int* __restrict__ seq_start) {
+  const int qh = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  const int m = seq_start[row];
+  const float* base = scratch + ((size_t)row * nq + qh) * max_splits * (kHd + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, base[(size_t)s * (kHd + 2) + kHd]);
+  float ll = 0.0f, a = 0.0f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float* p = base + (size_t)s * (kHd + 2);
+    const float ms = p[kHd];
+    const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+    ll += p[kHd + 1] * c;
+    a += p[d] * c;
+  }
+  const float g = __bfloat162float(gate[(size_t)m * ld_gate + (size_t)qh * kHd + d]);
+  out[(size_t)m * nq * kHd + (size_t)qh * kHd + d] = __float2bfloat16_rn(a / ll * sigmoid_f(g));
+}
+
+template <int GROUP>
+int launch_token_attention(const q38_attention_params& p, const q38_batch_desc& b, const q38_kv_cache_desc& kvd,
+                           bool decode, int splits, cudaStream_t s) {
+  const KvView kv = make_view(kvd);
+  const int rows = decode ? b.num_seqs : b.num_tokens;
+  const dim3 grid(splits, p.num_kv_heads, rows);
+  const __half* q = reinterpret_cast<const __half*>(p.q);
+  const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p.gate);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+  if (kv.int8)
+    attn_token_kernel<GROUP, true><<<grid, kAttnWarps * 32, 0, s>>>(
+        q, gate, p.ld_gate, out, p.num_q_heads, p.attn_layer, p.split_scratch, p.max_splits, splits, decode ? 1 : 0,
+        b.seq_start, b.seq_slot, b.seq_pos0, b.tok_pos, b.tok_seq, kv);
+  else
+    attn_token_kernel<GROUP, false><<<grid, kAttnWarps * 32, 0, s>>>(
+        q, gate, p.ld_gate, out, p.num_q_heads, p.attn_layer, p.split_scratch, p.max_splits, splits, decode ? 1 : 0,
+        b.seq_start, b.seq_slot, b.seq_pos0, b.tok_pos, b.tok_seq, kv);
+  Q38_LAUNCH_OK("attn_token_kernel");
+  if (splits > 1) {
+    attn_merge_kernel<<<dim3(p.num_q_heads, rows), kHd, 0, s>>>(p.split_scratch, p.max_splits, splits, gate, p.ld_gate,
+                                                               out, p.num_q_heads, b.seq_start);
+    Q38_LAUNCH_OK("attn_merge_kernel");
+  }
+  return Q38_OK;
+}
+
+int dispatch_group(int group, const q38_attention_params& p, const q38_batch_desc& b, const q38_kv_cache_desc& kv,
+                   bool decode, int splits, cudaStream_t s) {
+  switch (group) {
+    case 1: return launch_token_attention<1>(p, b, kv, decode, splits, s);
+    case 2: return launch_token_attention<2>(p, b, kv, decode, splits, s);
+    case 3: return launch_token_attention<3>(p, b, kv, decode, splits, s);
+    case 4: return launch_token_attention<4>(p, b, kv, decode, splits, s);
+    case 5: return launch_token_attention<5>(p, b, kv, decode, splits, s);
+    case 6: return launch_token_attention<6>(p, b, kv, decode, splits, s);
+    case 7: return launch_token_attention<7>(p, b, kv, decode, splits, s);
+    case 8: return launch_token_attention<8>(p, b, kv, decode, splits, s);
+    default: set_error("attention: GQA group %d is not implemented (1..8)", group); return Q38_ERR_INVALID;
+  }
+}
+
+int check_attention(const q38_attention_params* p, const q38_batch_desc* b, const q38_kv_cache_desc* kv) {
+  Q38_REQUIRE(p && b && kv, "attention: null argument");
+  Q38_REQUIRE(p->q && p->gate && p->out, "attention: null pointer");
+  Q38_REQUIRE(p->num_kv_heads > 0 && p->num_q_heads % p->num_kv_heads == 0, "attention: heads %d / %d",
+              p->num_q_heads, p->num_kv_heads);
+  Q38_REQUIRE(kv->kv_heads == p->num_kv_heads, "attention: kv head count mismatch");
+  Q38_REQUIRE(kv->pool && kv->block_table && kv->max_pages_per_seq > 0, "attention: kv cache descriptor");
+  return Q38_OK;
+}
+
+}  // namespace
+
+unsigned int attention_error(bool clear) { return read_tu_error(clear); }
+
+}  // namespace q38
+
+using namespace q38;
+
+extern "C" int q38_qk_norm_rope_append(const q38_qk_norm_rope_params* p, const q38_batch_desc* batch,
+                                       const q38_kv_cache_desc* kv, void* stream) {
+  Q38_REQUIRE(p && batch && kv, "qk_norm_rope_append: null argument");
+  if (batch->num_tokens == 0) return Q38_OK;
+  const int warps = p->num_q_heads + 2 * p->num_kv_heads;
+  Q38_REQUIRE(warps > 0 && warps <= 32, "qk_norm_rope_append: %d heads per token exceed one CTA", warps);
+  Q38_REQUIRE(kv->kv_heads == p->num_kv_heads, "qk_norm_rope_append: kv head count mismatch");
+  Q38_REQUIRE(p->ld_proj % 8 == 0, "qk_norm_rope_append: ld_proj must be a multiple of 8");
+  RopeTable rope;
+  for (int i = 0; i < 32; ++i) rope.inv_freq[i] = 1.0f / std::pow(float(p->rope_theta), float(2 * i) / 64.0f);
+  qk_norm_rope_kernel<<<batch->num_tokens, warps * 32, 0, as_stream(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(p->proj), p->ld_proj, p->q_norm, p->k_norm, p->eps, p->num_q_heads,
+      p->num_kv_heads, reinterpret_cast<__half*>(p->q_out), p->attn_layer, rope, batch->tok_pos, batch->tok_seq,
+      batch->seq_slot, make_view(*kv));
+  Q38_LAUNCH_OK("qk_norm_rope_kernel");
+  return Q38_OK;
+}
+
+// Split count of the decode launcher: enough CTAs for two waves over the SMs, at most max_splits.
+extern "C" int q38_attention_decode_splits(int batch_seqs, int kv_heads, int num_sms, int max_splits) {
+  const int ctas = batch_seqs * kv_heads;
+  if (ctas <= 0) return 1;
+  int s = (2 * num_sms + ctas - 1) / ctas;
+  if (s < 1) s = 1;
+  if (s > max_splits) s = max_splits;
+  if (s > 64) s = 64;
+  return s;
+}
+
+extern "C" int q38_attention_decode(const q38_attention_params* p, const q38_batch_desc* batch,
+                                    const q38_kv_cache_desc* kv, void* stream) {
+  const int rc = check_attention(p, batch, kv);
+  if (rc != Q38_OK) return rc;
+  if (batch->num_seqs == 0) return Q38_OK;
+  Q38_REQUIRE(batch->num_tokens == batch->num_seqs, "attention_decode: one token per sequence expected");
+  int splits = q38_attention_decode_splits(batch->num_seqs, p->num_kv_heads, num_sms(), p->max_splits);
+  if (!p->split_scratch) splits = 1;
+  return dispatch_group(p->num_q_heads / p->num_kv_heads, *p, *batch, *kv, true, splits, as_stream(stream));
+}
+
+extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_batch_desc* batch,
+                                     const q38_kv_cache_desc* kv, void* stream) {
+  const int rc = check_attention(p, batch, kv);
+  if (rc != Q38_OK) return rc;
+  if (batch->num_tokens == 0) return Q38_OK;
+  return dispatch_group(p->num_q_heads / p->num_kv_heads, *p, *batch, *kv, false, 1, as_stream(stream));
+}

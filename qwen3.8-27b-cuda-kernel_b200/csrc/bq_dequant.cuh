@@ -1,0 +1,73 @@
+// In-register decoder of BQ 4/5/6/8-bit weight slabs (format: reference docs/FORMAT.md 2.1-2.5).
+//
+// One warp lane owns 16 bytes of a slab's lo plane (+ 4 / 8 / 16 bytes of its hi plane): 16 pairs
+// q = 2 j + h of weights for column 8 j + g and rows 2 t + 8 h + {0, 1} (g = lane >> 2, t = lane & 3).
+// decode_slab() turns them into 16 packed bf16x2 values w[q] = bf16(code * scale), bit-exact with the
+// format definition W = bf16(float(c) * float(s)): the unsigned code u is placed in the mantissa of the
+// bf16 number 128 (0x4300 | u == 128 + u exactly, u < 128), the bias 128 + 2^(b-1) is removed with an
+// exact bf16 subtraction, and one bf16 multiply by the group scale performs the single rounding.
+#pragma once
+
+#include "common.cuh"
+
+namespace q38 {
+
+template <int BITS>
+struct BqGeom {
+  static_assert(BITS == 4 || BITS == 5 || BITS == 6 || BITS == 8, "BQ bit width");
+  static constexpr int kHiSlabBytes = BITS == 4 ? 0 : BITS == 5 ? 128 : BITS == 6 ? 256 : 512;
+  static constexpr int kHiLaneWords = kHiSlabBytes / 128;  // u32 words per lane: 0, 1, 2, 4
+  static constexpr int kLoGroupBytes = 4 * 512;            // one 64-wide k-group of one 64-column block
+  static constexpr int kHiGroupBytes = 4 * kHiSlabBytes;
+  static constexpr int kScGroupBytes = 128;
+};
+
+__device__ __forceinline__ uint32_t bf16x2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __nv_bfloat162 bits_bf16x2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+
+// lo: the lane's four lo words. hi: the lane's hi words (BqGeom::kHiLaneWords of them are read).
+// s2[j]: the scale of column 8 j + g duplicated into both halves of a bf16x2.
+template <int BITS>
+__device__ __forceinline__ void decode_slab(const uint32_t (&lo)[4], const uint32_t (&hi)[4], const uint32_t (&s2)[8],
+                                            uint32_t (&w)[16]) {
+  constexpr uint32_t kMagic = 0x43004300u;  // bf16x2 (128, 128)
+  constexpr uint32_t kNib = 0x000F000Fu;
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    const int p = q & 3;
+    uint32_t v = ((lo[q >> 2] >> (4 * p)) & kNib) | kMagic;
+    __nv_bfloat162 c;
+    if constexpr (BITS == 4) {
+      c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43084308u));  // 136
+    } else if constexpr (BITS == 5) {
+      const uint32_t h = q >= 4 ? (hi[0] >> (q - 4)) : (hi[0] << (4 - q));
+      v |= h & 0x00100010u;
+      c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43104310u));  // 144
+    } else if constexpr (BITS == 6) {
+      const int r = q & 7;
+      const uint32_t word = hi[q >> 3];
+      const uint32_t h = 2 * r >= 4 ? (word >> (2 * r - 4)) : (word << (4 - 2 * r));
+      v |= h & 0x00300030u;
+      c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43204320u));  // 160
+    } else {
+      const uint32_t vh = ((hi[q >> 2] >> (4 * p)) & kNib) | kMagic;
+      // code = 16 * (hi - 8) + lo, every intermediate is a small integer (exact in bf16)
+      const __nv_bfloat162 top = __hsub2(bits_bf16x2(vh), bits_bf16x2(0x43084308u));
+      const __nv_bfloat162 low = __hsub2(bits_bf16x2(v), bits_bf16x2(kMagic));
+      c = __hfma2(top, bits_bf16x2(0x41804180u), low);  // 16.0
+    }
+    w[q] = bf16x2_bits(__hmul2(c, bits_bf16x2(s2[q >> 1])));
+  }
+}
+
+// Expands the lane's eight scales (one 16-byte read: columns 8 j + g, j = 0..7) into duplicated pairs.
+__device__ __forceinline__ void expand_scales(const uint4& sv, uint32_t (&s2)[8]) {
+  const uint32_t words[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    s2[2 * i] = __byte_perm(words[i], 0, 0x1010);
+    s2[2 * i + 1] = __byte_perm(words[i], 0, 0x3232);
+  }
+}
+
+}  // namespace q38

@@ -1,0 +1,267 @@
+// Gated DeltaNet layers: a/b gate projection, fused causal conv(4) + SiLU + q/k L2 norm with the conv
+// state carry, and the 128x128 fp32 recurrent-state update with the gated RMSNorm, over ragged
+// sequences. Replaces kernels::gdn_ab, gdn_conv and gdn_recurrence of the reference
+// (src/kernels/kernels.h:184-228, src/kernels/gdn.cu). State layouts (reference docs/FORMAT.md 3.2):
+// recurrent fp32 [slot][gdn_layer][v_head][128 dv][128 dk]; conv bf16 [slot][gdn_layer][3][conv_dim],
+// tap 0 oldest.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace q38 {
+namespace {
+
+constexpr int kDk = 128, kDv = 128;
+
+// ---------------------------------------------------------------------------------------------------
+// gdn_ab: ab[m][j] = rs[m] * sum_k xbf[m][k] * w[j][k]  (fp32; rows j < nv are b, the rest a).
+// One CTA per token, one warp per output row (strided), 16-byte loads of both operands.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __restrict__ xbf, int hidden,
+                                                     const __nv_bfloat16* __restrict__ w, int rows,
+                                                     const float* __restrict__ partials_in, float eps,
+                                                     float* __restrict__ ab_out) {
+  extern __shared__ __align__(16) uint8_t ab_smem[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ab_smem);
+  __shared__ float rs_sm;
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < hidden / 8; i += 256)
+    reinterpret_cast<uint4*>(xs)[i] = reinterpret_cast<const uint4*>(xbf + (size_t)m * hidden)[i];
+  if (tid == 0) {
+    float rs = 1.0f;
+    if (partials_in) {
+      const int blocks = hidden / 128;
+      float sum = 0.0f;
+      for (int b = 0; b < blocks; ++b) sum += partials_in[(size_t)m * blocks + b];
+      rs = 1.0f / sqrtf(sum / float(hidden) + eps);
+    }
+    rs_sm = rs;
+  }
+  __syncthreads();
+  for (int j = warp; j < rows; j += 8) {
+    const __nv_bfloat16* wr = w + (size_t)j * hidden;
+    float acc = 0.0f;
+    for (int c = lane; c < hidden / 8; c += 32) {
+      const uint4 wv = reinterpret_cast<const uint4*>(wr)[c];
+      const uint4 xv = reinterpret_cast<const uint4*>(xs)[c];
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc += __low2float(wp[i]) * __low2float(xp[i]);
+        acc += __high2float(wp[i]) * __high2float(xp[i]);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) ab_out[(size_t)m * rows + j] = acc * rs_sm;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// gdn_conv: depthwise causal conv (width 4) + SiLU over the [q | k | v] channels; q/k heads are
+// L2-normalised (x * rsqrt(sum x^2 + 1e-6)), q additionally scaled by 1/sqrt(128).
+// Token-parallel: one CTA per (128-channel head block, token). The three previous inputs of a channel
+// come from the same chunk's earlier rows of `proj`, or from the conv state for the first tokens of a
+// sequence's chunk. A second small kernel then rolls the conv state forward by the chunk.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
+                                                       const float* __restrict__ conv_w, float* __restrict__ qkv,
+                                                       int conv_dim, int key_dim, int layer, int num_layers,
+                                                       const __nv_bfloat16* __restrict__ conv_state,
+                                                       const int* __restrict__ seq_start,
+                                                       const int* __restrict__ seq_slot,
+                                                       const int* __restrict__ tok_seq) {
+  const int c = blockIdx.x * 128 + threadIdx.x, m = blockIdx.y;
+  const int b = tok_seq[m];
+  const int i = m - seq_start[b];  // index of the token inside its sequence's chunk
+  const __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
+  const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)c * 4);
+  float x[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {  // x[j] = input 3 - j steps back
+    const int back = 3 - j;
+    x[j] = back <= i ? __bfloat162float(proj[(size_t)(m - back) * ld_proj + c])
+                     : __bfloat162float(st[(size_t)(3 + i - back) * conv_dim + c]);
+  }
+  float acc = 0.0f;
+  acc += w.x * x[0];
+  acc += w.y * x[1];
+  acc += w.z * x[2];
+  acc += w.w * x[3];
+  float y = silu_f(acc);
+  if (c < 2 * key_dim) {  // block-uniform: the 128 channels of a CTA are one q or k head
+    __shared__ float red[4];
+    const float ss = warp_sum(y * y);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float total = red[0] + red[1] + red[2] + red[3];
+    y *= 1.0f / sqrtf(total + 1e-6f);
+    if (c < key_dim) y *= 0.08838834764831845f;  // 1 / sqrt(128)
+  }
+  qkv[(size_t)m * conv_dim + c] = y;
+}
+
+__global__ void __launch_bounds__(128) gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
+                                                             int conv_dim, int layer, int num_layers,
+                                                             __nv_bfloat16* __restrict__ conv_state,
+                                                             const int* __restrict__ seq_start,
+                                                             const int* __restrict__ seq_slot) {
+  const int c = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
+  const int s = seq_start[b], n = seq_start[b + 1] - s;
+  if (n <= 0) return;
+  __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
+  __nv_bfloat16 old[3], nw[3];
+#pragma unroll
+  for (int t = 0; t < 3; ++t) old[t] = st[(size_t)t * conv_dim + c];
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {  // history = [old0 old1 old2 x0 .. x(n-1)], keep its last three
+    const int idx = n + t;
+    nw[t] = idx < 3 ? old[idx] : proj[(size_t)(s + idx - 3) * ld_proj + c];
+  }
+#pragma unroll
+  for (int t = 0; t < 3; ++t) st[(size_t)t * conv_dim + c] = nw[t];
+}
+
+// ---------------------------------------------------------------------------------------------------
+// gdn_recurrence: one CTA per (v head, sequence). The 128x128 fp32 state lives in registers for the
+// whole chunk: 16 warps x 8 rows, a lane owns 4 consecutive columns of each row, so a row is one
+// coalesced 512-byte access. Per token (reference src/kernels/gdn.cu:275-334, oracle
+// src/ref/ops.cpp:210-240):
+//   beta = sigmoid(b); decay = exp(A * softplus(a + dt_bias));
+//   S *= decay; kv = S k; delta = beta (v - kv); S += delta k^T; o = S q;
+//   out = bf16(o * rsqrt(mean(o^2) + eps) * norm_w * silu(z)).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kRecWarps = 16;
+constexpr int kRowsPerWarp = kDv / kRecWarps;
+
+__global__ void __launch_bounds__(kRecWarps * 32, 1) gdn_recurrence_kernel(
+    const float* __restrict__ qkv, int conv_dim, const float* __restrict__ ab, const float* __restrict__ A,
+    const float* __restrict__ dt_bias, const __nv_bfloat16* __restrict__ z, int ld_z,
+    const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
+    int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot) {
+  const int vh = blockIdx.x, b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s0 = seq_start[b], s1 = seq_start[b + 1];
+  if (s1 <= s0) return;
+  const int kh = vh / (nv / nk);
+  float* S = recurrent + (((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv * kDk;
+  const int row0 = warp * kRowsPerWarp;
+  float4 st[kRowsPerWarp];
+#pragma unroll
+  for (int r = 0; r < kRowsPerWarp; ++r) st[r] = *reinterpret_cast<const float4*>(S + (size_t)(row0 + r) * kDk + 4 * lane);
+
+  __shared__ float o_sm[kDv];
+  __shared__ float red[kRecWarps];
+  const float a_h = A[vh], dt_h = dt_bias[vh];
+  const size_t q_off = (size_t)kh * kDk, k_off = (size_t)nk * kDk + (size_t)kh * kDk, v_off = (size_t)2 * nk * kDk + (size_t)vh * kDv;
+
+  for (int m = s0; m < s1; ++m) {
+    const float* row = qkv + (size_t)m * conv_dim;
+    const float4 q4 = *reinterpret_cast<const float4*>(row + q_off + 4 * lane);
+    const float4 k4 = *reinterpret_cast<const float4*>(row + k_off + 4 * lane);
+    const float bb = ab[(size_t)m * 2 * nv + vh], aa = ab[(size_t)m * 2 * nv + nv + vh];
+    const float beta = 1.0f / (1.0f + expf(-bb));
+    const float xsp = aa + dt_h;
+    const float sp = xsp > 20.0f ? xsp : log1pf(expf(xsp));
+    const float decay = expf(a_h * sp);
+    float ov[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+      float4 sv = st[r];
+      sv.x *= decay;
+      sv.y *= decay;
+      sv.z *= decay;
+      sv.w *= decay;
+      const float kv = warp_sum(sv.x * k4.x + sv.y * k4.y + sv.z * k4.z + sv.w * k4.w);
+      const float delta = beta * (row[v_off + row0 + r] - kv);
+      sv.x += delta * k4.x;
+      sv.y += delta * k4.y;
+      sv.z += delta * k4.z;
+      sv.w += delta * k4.w;
+      st[r] = sv;
+      ov[r] = warp_sum(sv.x * q4.x + sv.y * q4.y + sv.z * q4.z + sv.w * q4.w);
+    }
+    // gated RMSNorm over the 128 outputs of the head
+    float ss = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) ss += ov[r] * ov[r];
+    if (lane == 0) red[warp] = ss;
+    if (lane < kRowsPerWarp) {
+      float mine = ov[0];
+#pragma unroll
+      for (int r = 1; r < kRowsPerWarp; ++r)
+        if (lane == r) mine = ov[r];
+      o_sm[row0 + lane] = mine;
+    }
+    __syncthreads();
+    if (threadIdx.x < kDv) {
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kRecWarps; ++w) total += red[w];
+      const float r = 1.0f / sqrtf(total / float(kDv) + eps);
+      const int d = threadIdx.x;
+      const float zz = __bfloat162float(z[(size_t)m * ld_z + (size_t)vh * kDv + d]);
+      out[(size_t)m * nv * kDv + (size_t)vh * kDv + d] = __float2bfloat16_rn(o_sm[d] * r * norm_w[d] * silu_f(zz));
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < kRowsPerWarp; ++r) *reinterpret_cast<float4*>(S + (size_t)(row0 + r) * kDk + 4 * lane) = st[r];
+}
+
+}  // namespace
+
+unsigned int gdn_error(bool clear) { return read_tu_error(clear); }
+
+}  // namespace q38
+
+using namespace q38;
+
+extern "C" int q38_gdn_ab(const q38_bf16* xbf, int m, int hidden, const q38_bf16* w_ab, int rows,
+                          const float* partials_in, float eps, float* ab_out, void* stream) {
+  if (m == 0) return Q38_OK;
+  Q38_REQUIRE(xbf && w_ab && ab_out, "gdn_ab: null argument");
+  Q38_REQUIRE(m > 0 && hidden > 0 && hidden % 128 == 0 && rows > 0, "gdn_ab: m %d hidden %d rows %d", m, hidden, rows);
+  Q38_REQUIRE(hidden * 2 <= 96 * 1024, "gdn_ab: hidden %d too large for the shared-memory row", hidden);
+  static const cudaError_t attr =
+      cudaFuncSetAttribute(gdn_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+  Q38_CUDA_OK(attr);
+  gdn_ab_kernel<<<m, 256, size_t(hidden) * 2, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(xbf), hidden,
+                                                                  reinterpret_cast<const __nv_bfloat16*>(w_ab), rows,
+                                                                  partials_in, eps, ab_out);
+  Q38_LAUNCH_OK("gdn_ab_kernel");
+  return Q38_OK;
+}
+
+extern "C" int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d, const q38_batch_desc* batch,
+                            const q38_gdn_state_desc* st, void* stream) {
+  Q38_REQUIRE(p && d && batch && st, "gdn_conv: null argument");
+  if (batch->num_tokens == 0) return Q38_OK;
+  Q38_REQUIRE(d->conv_dim == (2 * d->num_k_heads + d->num_v_heads) * 128, "gdn_conv: conv_dim %d", d->conv_dim);
+  Q38_REQUIRE(p->proj && p->conv_w && p->qkv && st->conv, "gdn_conv: null pointer");
+  const cudaStream_t s = as_stream(stream);
+  const __nv_bfloat16* proj = reinterpret_cast<const __nv_bfloat16*>(p->proj);
+  __nv_bfloat16* cs = reinterpret_cast<__nv_bfloat16*>(st->conv);
+  gdn_conv_kernel<<<dim3(d->conv_dim / 128, batch->num_tokens), 128, 0, s>>>(
+      proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128, p->gdn_layer, st->num_gdn_layers, cs,
+      batch->seq_start, batch->seq_slot, batch->tok_seq);
+  Q38_LAUNCH_OK("gdn_conv_kernel");
+  gdn_conv_state_kernel<<<dim3(d->conv_dim / 128, batch->num_seqs), 128, 0, s>>>(
+      proj, d->ld_proj, d->conv_dim, p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot);
+  Q38_LAUNCH_OK("gdn_conv_state_kernel");
+  return Q38_OK;
+}
+
+extern "C" int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d,
+                                  const q38_batch_desc* batch, const q38_gdn_state_desc* st, void* stream) {
+  Q38_REQUIRE(p && d && batch && st, "gdn_recurrence: null argument");
+  if (batch->num_tokens == 0) return Q38_OK;
+  Q38_REQUIRE(d->num_k_heads > 0 && d->num_v_heads % d->num_k_heads == 0, "gdn_recurrence: head ratio");
+  Q38_REQUIRE(p->qkv && p->ab && p->A && p->dt_bias && p->z && p->norm_w && p->out && st->recurrent,
+              "gdn_recurrence: null pointer");
+  gdn_recurrence_kernel<<<dim3(d->num_v_heads, batch->num_seqs), kRecWarps * 32, 0, as_stream(stream)>>>(
+      p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w,
+      p->eps, reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads,
+      d->num_v_heads, st->recurrent, batch->seq_start, batch->seq_slot);
+  Q38_LAUNCH_OK("gdn_recurrence_kernel");
+  return Q38_OK;
+}

@@ -1,0 +1,138 @@
+// GEMM dispatcher: argument validation, tile-configuration choice (tuning hook or M heuristic) and the
+// BQ dequantisation dump. Replaces the host part of the reference's src/kernels/qgemm.cu:470-616.
+#include <algorithm>
+
+#include "bq_dequant.cuh"
+#include "common.cuh"
+#include "host_util.h"
+#include "qgemm.h"
+
+namespace q38 {
+namespace {
+
+struct ConfigInfo {
+  const char* name;
+  int tile_m;
+};
+constexpr ConfigInfo kConfigs[] = {
+    {"stream_m8", 8},
+    {"stream_m16", 16},
+    {"stream_m32", 32},
+    {"stream_m64", 64},
+};
+constexpr int kNumConfigs = int(sizeof(kConfigs) / sizeof(kConfigs[0]));
+
+q38_gemm_tuning_lookup g_tuning = nullptr;
+
+int auto_config(int m) {
+  if (m <= 8) return 0;
+  if (m <= 16) return 1;
+  if (m <= 32) return 2;
+  return 3;
+}
+
+// One lane decodes one slab exactly as the GEMM does and writes the 32 weights to W[n][k] (bf16).
+template <int BITS>
+__global__ void bq_dequant_kernel(const uint8_t* __restrict__ lo, const uint8_t* __restrict__ hi,
+                                  const uint8_t* __restrict__ sc, int n, int k, __nv_bfloat16* __restrict__ out) {
+  using G = BqGeom<BITS>;
+  const int lane = threadIdx.x & 31;
+  const long long slab = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long slabs = (long long)(n / 64) * (k / 16);
+  if (slab >= slabs) return;
+  const int kb = int(slab % (k / 16));
+  const long long nb = slab / (k / 16);
+  const int g = lane >> 2, t = lane & 3;
+  const uint4 lv = *reinterpret_cast<const uint4*>(lo + slab * 512 + lane * 16);
+  const uint32_t lw[4] = {lv.x, lv.y, lv.z, lv.w};
+  uint32_t hw[4] = {0, 0, 0, 0};
+  for (int i = 0; i < G::kHiLaneWords; ++i)
+    hw[i] = *reinterpret_cast<const uint32_t*>(hi + slab * G::kHiSlabBytes + lane * 4 * G::kHiLaneWords + 4 * i);
+  uint32_t s2[8];
+  expand_scales(*reinterpret_cast<const uint4*>(sc + (nb * (k / 64) + kb / 4) * 128 + 16 * g), s2);
+  uint32_t w[16];
+  decode_slab<BITS>(lw, hw, s2, w);
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    const int j = q >> 1, h = q & 1;
+    const long long row = nb * 64 + 8 * j + g;
+    const int col = kb * 16 + 2 * t + 8 * h;
+    *reinterpret_cast<uint32_t*>(out + row * k + col) = w[q];
+  }
+}
+
+}  // namespace
+}  // namespace q38
+
+using namespace q38;
+
+extern "C" int q38_qgemm_num_configs(void) { return kNumConfigs; }
+extern "C" const char* q38_qgemm_config_name(int c) { return c >= 0 && c < kNumConfigs ? kConfigs[c].name : "?"; }
+extern "C" int q38_qgemm_config_tile_m(int c) { return c >= 0 && c < kNumConfigs ? kConfigs[c].tile_m : 0; }
+extern "C" void q38_set_qgemm_tuning(q38_gemm_tuning_lookup lookup) { g_tuning = lookup; }
+
+extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep,
+                         const q38_gemm_workspace* ws, void* stream, int config) {
+  Q38_REQUIRE(a && w && ep, "qgemm: null argument");
+  Q38_REQUIRE(m > 0, "qgemm: m must be positive, got %d", m);
+  Q38_REQUIRE(w->bits == 4 || w->bits == 5 || w->bits == 6 || w->bits == 8, "qgemm: unsupported bit width %d", w->bits);
+  Q38_REQUIRE(w->n > 0 && w->n % 128 == 0 && w->k > 0 && w->k % 64 == 0, "qgemm: BQ shape %d x %d", w->n, w->k);
+  Q38_REQUIRE(w->lo && w->scales && (w->bits == 4 || w->hi), "qgemm: missing weight plane");
+  Q38_REQUIRE(config >= -1 && config < kNumConfigs, "qgemm: config %d out of range", config);
+  Q38_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0, "qgemm: A must be 16-byte aligned");
+  if (ep->kind == Q38_EPI_RESIDUAL) {
+    Q38_REQUIRE(ep->residual && ep->xbf && ep->partials_out, "qgemm: Residual epilogue needs residual/xbf/partials");
+  } else {
+    Q38_REQUIRE(ep->kind >= 0 && ep->kind <= 3 && ep->out && ep->ldo > 0, "qgemm: epilogue output");
+  }
+  if (ep->partials_in) Q38_REQUIRE(ep->hidden > 0 && ep->hidden % 128 == 0, "qgemm: hidden %d", ep->hidden);
+  if (config < 0 && g_tuning) {
+    const int t = g_tuning(w->bits, w->n, w->k, m);
+    if (t >= 0 && t < kNumConfigs) config = t;
+  }
+  if (config < 0) config = auto_config(m);
+  const int tm = kConfigs[config].tile_m;
+  const cudaStream_t s = as_stream(stream);
+  const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(a);
+  for (int r0 = 0; r0 < m; r0 += tm) {
+    const int rows = std::min(tm, m - r0);
+    q38_gemm_epilogue e = *ep;
+    if (e.kind == Q38_EPI_RESIDUAL) {
+      e.residual += (size_t)r0 * w->n;
+      e.xbf += (size_t)r0 * w->n;
+      e.partials_out += (size_t)r0 * (w->n / 128);
+    } else if (e.kind == Q38_EPI_STORE_F32) {
+      e.out = static_cast<float*>(e.out) + (size_t)r0 * e.ldo;
+    } else {
+      e.out = static_cast<q38_bf16*>(e.out) + (size_t)r0 * e.ldo;
+    }
+    if (e.partials_in) e.partials_in += (size_t)r0 * (e.hidden / 128);
+    const int rc = qgemm_stream_launch(tm / 8, ap + (size_t)r0 * w->k, rows, *w, e, ws, s);
+    if (rc != Q38_OK) return rc;
+  }
+  return Q38_OK;
+}
+
+extern "C" int q38_bq_dequant(const q38_bq_weight* w, q38_bf16* out, void* stream) {
+  Q38_REQUIRE(w && out, "bq_dequant: null argument");
+  Q38_REQUIRE(w->n % 64 == 0 && w->k % 64 == 0, "bq_dequant: shape");
+  const long long slabs = (long long)(w->n / 64) * (w->k / 16);
+  const int warps = 8;
+  const unsigned grid = unsigned((slabs + warps - 1) / warps);
+  const uint8_t* sc = reinterpret_cast<const uint8_t*>(w->scales);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  const cudaStream_t s = as_stream(stream);
+  switch (w->bits) {
+    case 4: bq_dequant_kernel<4><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 5: bq_dequant_kernel<5><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 6: bq_dequant_kernel<6><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 8: bq_dequant_kernel<8><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
+    default: Q38_REQUIRE(false, "bq_dequant: unsupported bit width %d", w->bits);
+  }
+  Q38_LAUNCH_OK("bq_dequant_kernel");
+  return Q38_OK;
+}
+
+namespace q38 {
+unsigned int qgemm_dispatch_error(bool clear) { return read_tu_error(clear); }
+}

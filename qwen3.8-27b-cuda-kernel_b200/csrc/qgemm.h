@@ -1,0 +1,16 @@
+// Internal interface between the GEMM dispatcher (qgemm.cu) and its kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/q38_kernels.h"
+
+namespace q38 {
+
+// Weight-streaming kernel for m <= 8 * mt, mt in {1, 2, 4, 8} (qgemm_stream.cu).
+int qgemm_stream_launch(int mt, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
+                        const q38_gemm_workspace* ws, cudaStream_t s);
+unsigned int qgemm_stream_error(bool clear);
+
+}  // namespace q38
