@@ -1,0 +1,4 @@
+// Source-compatibility header: the declarations of the reference's include/qwen38/model_runner.h live in
+// qwen38/api.h together with the rest of the host API.
+#pragma once
+#include "qwen38/api.h"

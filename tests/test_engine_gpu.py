@@ -1,0 +1,285 @@
+"""GPU end-to-end parity: ModelRunner / Engine on the config-1 model against the golden logits and tokens the
+reference's own CPU model (`qwen38-ref`, engine mode, int8 KV) produced for the same file and prompts, and
+against the whole-model oracle. Mirrors reference tests/gpu/test_e2e.cpp and adds ragged multi-sequence steps,
+page-id checks and error paths."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import q38_testlib as tl
+from oracle_model import OracleModel
+from q38b200 import engine as eng
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+LENS = (17, 64, 65, 130)
+
+
+def tiny_options(**kw):
+    base = dict(max_batch=4, prefill_chunk=128, kv_dtype=0, kv_tokens=8192, max_context=4096, verbose=0)
+    base.update(kw)
+    return eng.default_runner_options(**base)
+
+
+@pytest.fixture(scope="module")
+def gold():
+    return np.load(GOLD / "tiny_cfg1_golden.npz")
+
+
+def rel_max(got, want):
+    return float(np.abs(got - want).max() / np.abs(want).max())
+
+
+def prefill_all(runner, slot, tokens, chunk):
+    """Logits of every position through chunked prefill."""
+    out = []
+    for p0 in range(0, len(tokens), chunk):
+        out.append(runner.prefill_logits(slot, p0, tokens[p0:p0 + chunk]))
+    return np.concatenate(out)
+
+
+@pytest.mark.parametrize("tag", ["", "_unit"])
+@pytest.mark.parametrize("chunk", [64, 128])
+def test_prefill_logits_match_reference_model(gold, tag, chunk):
+    model = eng.Model(GOLD / f"tiny_cfg1{tag}.q38")
+    runner = eng.Runner(model, tiny_options(prefill_chunk=chunk))
+    agree = total = 0
+    worst = 0.0
+    for i, n in enumerate(LENS):
+        full = np.concatenate([gold[f"prompt{i}"], gold[f"gen{tag}{i}"]])
+        want = gold[f"logits{tag}{i}"].astype(np.float32)
+        runner.reset_slot(i)
+        got = prefill_all(runner, i, full, chunk)
+        worst = max(worst, rel_max(got, want))
+        agree += int((got.argmax(-1) == want.argmax(-1)).sum())
+        total += len(full)
+    print(f"prefill{tag} chunk {chunk}: rel_max {worst:.3e}, top-1 {agree}/{total}")
+    assert worst <= 2e-2
+    assert agree >= 0.99 * total
+    runner.close()
+    model.close()
+
+
+@pytest.mark.parametrize("tag", ["", "_unit"])
+def test_ragged_batch_decode_matches_reference_step_by_step(gold, tag):
+    """Config 1: the four prompts prefilled (one ragged step per chunk round), then 32 greedy decode steps as
+    one ragged batch with teacher forcing on the reference's tokens; logits compared at every step."""
+    model = eng.Model(GOLD / f"tiny_cfg1{tag}.q38")
+    runner = eng.Runner(model, tiny_options(prefill_chunk=128))
+    g = eng.greedy()
+    prompts = [gold[f"prompt{i}"] for i in range(4)]
+    gens = [gold[f"gen{tag}{i}"] for i in range(4)]
+    refs = [gold[f"logits{tag}{i}"].astype(np.float32) for i in range(4)]
+    for s in range(4):
+        runner.reset_slot(s)
+        assert runner.kv_ensure(s, len(prompts[s]) + 33)
+    # ragged prefill: prompts 17 + 64 in one step (81 tokens), then 65, then 130 as 128 + 2 with 65's tail...
+    toks, _ = runner.prefill([(0, 0, prompts[0], g, 0), (1, 0, prompts[1], g, 0)])
+    first = {0: int(toks[0]), 1: int(toks[1])}
+    toks, _ = runner.prefill([(2, 0, prompts[2], g, 0), (3, 0, prompts[3][:60], None, 0)])
+    first[2] = int(toks[0])
+    toks, _ = runner.prefill([(3, 60, prompts[3][60:], g, 0)])
+    first[3] = int(toks[0])
+    agree = total = 0
+    for s in range(4):
+        agree += first[s] == int(gens[s][0])
+        total += 1
+    worst = 0.0
+    for step in range(32):
+        rows = [(s, len(prompts[s]) + step, int(gens[s][step]), g, step + 1) for s in range(4)]
+        toks, _ = runner.decode(rows)
+        logits = runner.last_logits(4)
+        for s in range(4):
+            want = refs[s][len(prompts[s]) + step]
+            worst = max(worst, rel_max(logits[s], want))
+            agree += int(logits[s].argmax()) == int(want.argmax())
+            total += 1
+            assert int(toks[s]) == int(logits[s].argmax()), "greedy token = lowest-id argmax of the logits"
+    print(f"decode{tag}: rel_max {worst:.3e}, top-1 {agree}/{total}")
+    assert worst <= 2e-2
+    assert agree >= 0.99 * total
+    runner.close()
+    model.close()
+
+
+@pytest.mark.parametrize("kv_dtype", [0, 1])
+def test_random_prompt_against_whole_model_oracle(kv_dtype):
+    """120 random tokens (seed 21) through prefill_logits vs the oracle model, int8 and bf16 KV
+    (reference tests/gpu/test_e2e.cpp:56-88: mean KL < 2e-3, top-1 >= 95%)."""
+    path = GOLD / "tiny_cfg1_unit.q38"
+    model = eng.Model(path)
+    runner = eng.Runner(model, tiny_options(kv_dtype=kv_dtype))
+    tokens = np.random.default_rng(21).integers(0, 1000, size=120).astype(np.int32)
+    got = runner.prefill_logits(0, 0, tokens)
+    om = OracleModel(path, kv_dtype=2 if kv_dtype == 0 else 1, max_positions=128)
+    want = om.forward(om.new_sequence(), tokens, all_logits=True)
+
+    def logsm(x):
+        x = x.astype(np.float64)
+        x = x - x.max(-1, keepdims=True)
+        return x - np.log(np.exp(x).sum(-1, keepdims=True))
+    lw, lg = logsm(want), logsm(got)
+    kl = (np.exp(lw) * (lw - lg)).sum(-1)
+    top1 = (got.argmax(-1) == want.argmax(-1)).mean()
+    print(f"kv={kv_dtype}: KL mean {kl.mean():.2e} max {kl.max():.2e}, top-1 {top1:.3f}, rel_max {rel_max(got, want):.2e}")
+    assert kl.mean() < 2e-3 and top1 >= 0.95 and rel_max(got, want) <= 2e-2
+    runner.close()
+    model.close()
+
+
+def test_chunked_prefill_then_graph_decode_is_consistent():
+    """One 100-token prefill vs chunks 37 + 23 then 40 CUDA-graph decode steps (reference test_e2e.cpp:90-132)."""
+    model = eng.Model(GOLD / "tiny_cfg1_unit.q38")
+    runner = eng.Runner(model, tiny_options())
+    tokens = np.random.default_rng(8).integers(0, 1000, size=100).astype(np.int32)
+    runner.reset_slot(0)
+    full = runner.prefill_logits(0, 0, tokens)
+    runner.kv_release(0)
+    runner.reset_slot(1)
+    assert runner.kv_ensure(1, 101)
+    g = eng.greedy()
+    runner.prefill([(1, 0, tokens[:37], None, 0)])
+    toks, _ = runner.prefill([(1, 37, tokens[37:60], g, 0)])
+    agree = int(toks[0] == full[59].argmax())
+    for pos in range(60, 100):
+        toks, _ = runner.decode([(1, pos, int(tokens[pos]), g, pos)])
+        agree += int(toks[0] == full[pos].argmax())
+    assert agree >= 41 - 2
+    # graphs on and off give the same tokens
+    runner.reset_slot(2)
+    assert runner.kv_ensure(2, 101)
+    runner.set_graphs(False)
+    runner.prefill([(2, 0, tokens[:60], None, 0)])
+    eager = [int(runner.decode([(2, pos, int(tokens[pos]), g, pos)])[0][0]) for pos in range(60, 70)]
+    runner.set_graphs(True)
+    runner.reset_slot(3)
+    assert runner.kv_ensure(3, 101)
+    runner.prefill([(3, 0, tokens[:60], None, 0)])
+    graph = [int(runner.decode([(3, pos, int(tokens[pos]), g, pos)])[0][0]) for pos in range(60, 70)]
+    assert eager == graph
+    runner.close()
+    model.close()
+
+
+def test_engine_batches_independent_sequences(gold):
+    """Four requests together = each alone (reference test_e2e.cpp:134-181), plus the golden continuations."""
+    model = eng.Model(GOLD / "tiny_cfg1_unit.q38")
+    prompts = [gold[f"prompt{i}"] for i in range(4)]
+    alone = []
+    e = eng.Engine(model, tiny_options())
+    for p in prompts:
+        e.submit(p, eng.greedy(), max_new_tokens=32, ignore_eos=True)
+        e.run()
+        alone.append(e.take_finished()[0].tokens)
+    e.close()
+    for ragged in (False, True):
+        e = eng.Engine(model, tiny_options(), ragged_prefill=ragged)
+        for p in prompts:
+            e.submit(p, eng.greedy(), max_new_tokens=32, ignore_eos=True)
+        e.run()
+        done = sorted(e.take_finished(), key=lambda r: r.id)
+        st = e.stats()
+        assert len(done) == 4 and all(len(r.tokens) == 32 and r.finish == "length" for r in done)
+        assert st.decode_tokens / max(1, st.decode_steps) > 1.5
+        assert st.prefill_tokens == sum(LENS)
+        same = total = gold_same = 0
+        for i, r in enumerate(done):
+            for t in range(32):
+                total += 1
+                if r.tokens[t] != alone[i][t]:
+                    break
+                same += 1
+            gold_same += int((r.tokens == gold[f"gen_unit{i}"]).sum())
+        print(f"ragged={ragged}: batched vs alone {same}/{total}; vs reference tokens {gold_same}/128")
+        assert same >= 0.9 * 128
+        assert gold_same >= 0.9 * 128
+        e.close()
+    model.close()
+
+
+def test_engine_error_results_and_stop_tokens():
+    model = eng.Model(GOLD / "tiny_cfg1_unit.q38")
+    e = eng.Engine(model, tiny_options(kv_tokens=256, max_context=512))
+    ids = [e.submit([], eng.greedy(), 4), e.submit(np.zeros(600, np.int32), eng.greedy(), 4),
+           e.submit(np.arange(300, dtype=np.int32), eng.greedy(), 64, ignore_eos=True)]
+    e.run()
+    done = {r.id: r for r in e.take_finished()}
+    assert done[ids[0]].finish == "error" and "empty prompt" in done[ids[0]].error
+    assert done[ids[1]].finish == "error" and "context limit" in done[ids[1]].error
+    assert done[ids[2]].finish == "error" and "more KV cache" in done[ids[2]].error
+    # a stop token ends the request with reason "stop" and is part of the output
+    prompt = np.random.default_rng(4).integers(0, 1000, size=20).astype(np.int32)
+    e.submit(prompt, eng.greedy(), 16, ignore_eos=True)
+    e.run()
+    free = e.take_finished()[0].tokens
+    e.submit(prompt, eng.greedy(), 16, stop_tokens=[int(free[3])])
+    e.run()
+    r = e.take_finished()[0]
+    first = int(np.argmax(free == free[3]))
+    assert r.finish == "stop" and list(r.tokens) == list(free[:first + 1])
+    e.close()
+    model.close()
+
+
+def test_kv_page_ids_follow_the_reference_free_list():
+    """Page ids are part of the parity contract: a Python model of the reference's free list
+    (src/kv_cache.cpp:34-35, 53-76: page 0 first, LIFO reuse) must predict every block-table row."""
+    model = eng.Model(GOLD / "tiny_cfg1.q38")
+    runner = eng.Runner(model, tiny_options(kv_tokens=64 * 40))
+    pages = 41
+    free = list(range(pages - 1, -1, -1))
+    owned = {s: [] for s in range(5)}
+
+    def ensure(slot, tokens):
+        need = (tokens + 63) // 64 - len(owned[slot])
+        if need <= 0:
+            return True
+        if need > len(free):
+            return False
+        for _ in range(need):
+            owned[slot].append(free.pop())
+        return True
+
+    def release(slot):
+        free.extend(reversed(owned[slot]))
+        owned[slot].clear()
+
+    assert ensure(4, 1)  # the runner's dummy sequence owns the first page
+    rng = np.random.default_rng(1)
+    for _ in range(200):
+        slot = int(rng.integers(0, 4))
+        if rng.random() < 0.6:
+            tokens = int(rng.integers(1, 900))
+            assert runner.kv_ensure(slot, tokens) == ensure(slot, tokens)
+        else:
+            runner.kv_release(slot)
+            release(slot)
+        assert runner.kv_pages(slot) == owned[slot]
+        assert runner.kv_free_pages() == len(free)
+    runner.close()
+    model.close()
+
+
+def test_sampled_generation_is_reproducible_and_scores_match_logits():
+    model = eng.Model(GOLD / "tiny_cfg1_unit.q38")
+    outs = []
+    for _ in range(2):
+        e = eng.Engine(model, tiny_options(), seed=77)
+        e.submit(np.arange(40, dtype=np.int32), eng.Sampling(0.8, 50, 0.95, 0.0, 0.3, 1.1, 0), 24, ignore_eos=True)
+        e.run()
+        outs.append(e.take_finished()[0].tokens)
+        e.close()
+    assert np.array_equal(outs[0], outs[1])
+    runner = eng.Runner(model, tiny_options())
+    tokens = np.random.default_rng(2).integers(0, 1000, size=50).astype(np.int32)
+    targets = np.roll(tokens, -1)
+    lp = runner.score(0, 0, tokens, targets)
+    runner.kv_release(0)
+    runner.reset_slot(0)
+    logits = runner.prefill_logits(0, 0, tokens).astype(np.float64)
+    want = logits[np.arange(50), targets] - np.log(np.exp(logits - logits.max(-1, keepdims=True)).sum(-1)) - logits.max(-1)
+    assert np.allclose(lp, want, atol=2e-4)
+    runner.close()
+    model.close()

@@ -1,0 +1,485 @@
+"""GPU parity tests: every kernel, called through the C ABI, against the CPU oracle on the same seeded
+inputs. Shapes, seeds and tolerances restate the reference's own kernel tests
+(reference tests/gpu/test_kernels.cu); cases the reference does not cover (ragged B > 1, GQA with 4 KV
+heads, several layers in the pools, shuffled page tables, 27B-sized matrices) are added."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import q38_testlib as tl
+from q38_testlib import bq, pkg
+
+pytestmark = pytest.mark.gpu
+
+
+def K():
+    return pkg.kernels()
+
+
+def sync_ok():
+    torch.cuda.synchronize()
+    assert K().q38_device_error(1) == 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# BQ decode: bit-exact dequantised weights
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("bits", [4, 5, 6, 8])
+def test_dequantised_weights_are_bit_exact(bits):
+    gold = np.load(tl.ROOT / "tests" / "golden" / "bq_golden.npz")
+    cases = [bq.Packed(bits, 128, 192, gold[f"lo{bits}"].tobytes(), gold[f"hi{bits}"].tobytes(),
+                       gold[f"sc{bits}"].tobytes()),
+             tl.make_bq(256, 320, bits, seed=40 + bits)]
+    for p in cases:
+        w = tl.DeviceBQ(p)
+        out = torch.empty((p.n, p.k), dtype=torch.bfloat16, device="cuda")
+        pkg.check(K().q38_bq_dequant(C.byref(w.desc), pkg.ptr(out), None))
+        sync_ok()
+        want = tl.oracle().dequant(p)
+        assert np.array_equal(out.float().cpu().numpy(), want)
+
+
+# ---------------------------------------------------------------------------------------------------
+# qgemm
+# ---------------------------------------------------------------------------------------------------
+def run_gemm_f32(a_dev, m, w, ws, config):
+    out = torch.empty((m, w.packed.n), dtype=torch.float32, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_STORE_F32, pkg.ptr(out), w.packed.n, 0, None, None, None, None, 0, 1e-6)
+    pkg.check(K().q38_qgemm(pkg.ptr(a_dev), m, C.byref(w.desc), C.byref(ep), C.byref(ws) if ws else None, None, config))
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("bits", [4, 5, 6, 8])
+def test_qgemm_matches_oracle_all_configs(bits):
+    rng = np.random.default_rng(42)
+    ws = tl.Workspace()
+    for (n, k) in ((256, 256), (1536, 192), (384, 1024)):
+        p = tl.make_bq(n, k, bits, seed=bits * 100 + n, std=0.05, fast=(n > 256))
+        w = tl.DeviceBQ(p)
+        wd = tl.oracle().dequant(p)
+        for m in (1, 3, 16, 17, 40, 64, 130):
+            a = tl.bf16_round(rng.standard_normal((m, k)))
+            a_dev = tl.to_dev_bf16(a)
+            want = np.zeros((m, n), np.float32)
+            tl.oracle().qgemm(a, wd, None, 3, out=want, ldo=n)
+            mag = np.abs(a).astype(np.float64) @ np.abs(wd).astype(np.float64).T
+            for cfg in range(K().q38_qgemm_num_configs()):
+                for use_ws in (True, False):
+                    got = run_gemm_f32(a_dev, m, w, ws.desc if use_ws else None, cfg)
+                    err = np.abs(got.cpu().numpy().astype(np.float64) - want)
+                    bad = err > 1e-6 + 2e-3 * mag
+                    assert not bad.any(), (bits, n, k, m, cfg, use_ws, float(err.max()))
+                    again = run_gemm_f32(a_dev, m, w, ws.desc if use_ws else None, cfg)
+                    assert torch.equal(got, again), "second run is not bit-identical"
+    sync_ok()
+    assert int(ws.counters.abs().sum()) == 0, "tile counters must reset themselves"
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 77])
+def test_qgemm_epilogues(m):
+    rng = np.random.default_rng(7)
+    o = tl.oracle()
+    H, I = 512, 1024
+    ws = tl.Workspace()
+    residual = tl.bf16_round(rng.standard_normal((m, H)) * 3)
+    xbf = tl.bf16_round(residual)
+    partials = np.stack([o.norm_partials(residual[i]) for i in range(m)])
+    rs = np.array([o.norm_row_scale(partials[i], H, 1e-6) for i in range(m)], np.float32)
+    xbf_dev, part_dev = tl.to_dev_bf16(xbf), torch.from_numpy(partials).cuda()
+
+    # StoreBF16 + folded-norm row scale, with padded rows trimmed by n_store
+    p = tl.make_bq(1152, H, 5, seed=1, std=0.05)
+    w, wd = tl.DeviceBQ(p, rows=1100), o.dequant(p)
+    want = np.zeros((m, 1152), np.float32)
+    o.qgemm(xbf, wd, rs, 0, out=want, ldo=1152)
+    out = torch.full((m, 1152), 7.0, dtype=torch.bfloat16, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_STORE_BF16, pkg.ptr(out), 1152, 1100, None, None, None, pkg.ptr(part_dev), H, 1e-6)
+    pkg.check(K().q38_qgemm(pkg.ptr(xbf_dev), m, C.byref(w.desc), C.byref(ep), C.byref(ws.desc), None, -1))
+    got = out.float().cpu().numpy()
+    assert np.all(np.abs(got[:, :1100] - want[:, :1100]) <= 1e-3 + 2e-2 * np.abs(want[:, :1100]))
+    assert np.all(got[:, 1100:] == 7.0), "columns beyond n_store must not be written"
+
+    # SwiGLU on interleaved gate/up columns
+    p = tl.make_bq(2 * I, H, 4, seed=2, std=0.05)
+    w, wd = tl.DeviceBQ(p), o.dequant(p)
+    want = np.zeros((m, I), np.float32)
+    o.qgemm(xbf, wd, rs, 1, out=want, ldo=I)
+    out = torch.empty((m, I), dtype=torch.bfloat16, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_SWIGLU, pkg.ptr(out), I, 0, None, None, None, pkg.ptr(part_dev), H, 1e-6)
+    pkg.check(K().q38_qgemm(pkg.ptr(xbf_dev), m, C.byref(w.desc), C.byref(ep), C.byref(ws.desc), None, -1))
+    got = out.float().cpu().numpy()
+    assert np.all(np.abs(got - want) <= 2e-2 * (np.abs(want) + 1e-3 * np.abs(want).max()))
+
+    # Residual: residual += C, xbf == bf16(residual) exactly, next-norm partials
+    p = tl.make_bq(H, I, 6, seed=3, std=0.05)
+    w, wd = tl.DeviceBQ(p), o.dequant(p)
+    act = tl.bf16_round(rng.standard_normal((m, I)) * 0.5)
+    res_want, xbf_want, part_want = residual.copy(), np.zeros_like(residual), np.zeros_like(partials)
+    o.qgemm(act, wd, None, 2, residual=res_want, xbf=xbf_want, partials=part_want)
+    res_dev = torch.from_numpy(residual.copy()).cuda()
+    xbf_out = torch.empty((m, H), dtype=torch.bfloat16, device="cuda")
+    part_out = torch.empty((m, H // 128), dtype=torch.float32, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_RESIDUAL, None, 0, 0, pkg.ptr(res_dev), pkg.ptr(xbf_out), pkg.ptr(part_out), None, 0, 1e-6)
+    act_d = tl.to_dev_bf16(act)
+    pkg.check(K().q38_qgemm(pkg.ptr(act_d), m, C.byref(w.desc), C.byref(ep), C.byref(ws.desc), None, -1))
+    sync_ok()
+    res_got = res_dev.cpu().numpy()
+    assert np.all(np.abs(res_got - res_want) <= 1e-3 + 1e-3 * np.abs(res_want))
+    assert np.array_equal(xbf_out.float().cpu().numpy(), tl.bf16_round(res_got))
+    assert np.all(np.abs(part_out.cpu().numpy() - part_want) <= 1e-3 + 1e-4 * np.abs(part_want))
+
+
+@pytest.mark.parametrize("n,k,bits", [(34816, 5120, 4), (5120, 17408, 6)])
+def test_qgemm_27b_shapes(n, k, bits):
+    """Full-size projection matrices; the oracle is evaluated on a seeded subset of output columns."""
+    g = torch.Generator(device="cuda").manual_seed(n)
+    wt = torch.randn((n, k), generator=g, device="cuda") * 0.02
+    codes, scales = bq.quantize_absmax(wt, bits)
+    p = bq.pack(codes.cpu(), scales.cpu(), bits)
+    w = tl.DeviceBQ(p)
+    ws = tl.Workspace()
+    rng = np.random.default_rng(5)
+    cols = np.sort(rng.choice(n, size=192, replace=False))
+    wd = bq.dequantize(codes[cols].cpu(), scales[cols].cpu()).numpy()
+    # whole-matrix dequant check against the python definition (bit-exact)
+    deq = torch.empty((n, k), dtype=torch.bfloat16, device="cuda")
+    pkg.check(K().q38_bq_dequant(C.byref(w.desc), pkg.ptr(deq), None))
+    assert torch.equal(deq[cols].float().cpu(), torch.from_numpy(wd))
+    for m in (1, 8, 64):
+        a = tl.bf16_round(rng.standard_normal((m, k)))
+        want = np.zeros((m, len(cols)), np.float32)
+        tl.oracle().qgemm(a, wd, None, 3, out=want, ldo=len(cols))
+        mag = np.abs(a).astype(np.float64) @ np.abs(wd).astype(np.float64).T
+        a_dev = tl.to_dev_bf16(a)
+        got = run_gemm_f32(a_dev, m, w, ws.desc, -1)
+        err = np.abs(got[:, cols].cpu().numpy().astype(np.float64) - want)
+        assert not (err > 1e-6 + 2e-3 * mag).any(), (m, float(err.max()))
+        assert torch.equal(got, run_gemm_f32(a_dev, m, w, ws.desc, -1))
+    sync_ok()
+
+
+# ---------------------------------------------------------------------------------------------------
+# embed, ragged packing
+# ---------------------------------------------------------------------------------------------------
+def test_embed_matches_oracle():
+    H, V = 512, 1024
+    g = torch.Generator().manual_seed(1)
+    table = (torch.randn((V, H), generator=g)).to(torch.bfloat16)
+    tokens = torch.tensor([0, 5, 1023, 17, 17, 400], dtype=torch.int32)
+    m = len(tokens)
+    # device table and mapped pinned host table (zero-copy)
+    host_table = table.clone().pin_memory()
+    for tab in (table.cuda(), host_table):
+        res = torch.empty((m, H), dtype=torch.float32, device="cuda")
+        xbf = torch.empty((m, H), dtype=torch.bfloat16, device="cuda")
+        part = torch.empty((m, H // 128), dtype=torch.float32, device="cuda")
+        tok_d = tokens.cuda()
+        pkg.check(K().q38_embed(pkg.ptr(tab), pkg.ptr(tok_d), m, H, pkg.ptr(res), pkg.ptr(xbf), pkg.ptr(part), None))
+        sync_ok()
+        rows = table[tokens.long()].float().numpy()
+        assert np.array_equal(res.cpu().numpy(), rows)
+        assert np.array_equal(xbf.float().cpu().numpy(), rows)
+        want = np.stack([tl.oracle().norm_partials(rows[i]) for i in range(m)])
+        assert np.all(np.abs(part.cpu().numpy() - want) <= 1e-4 + 1e-5 * np.abs(want))
+
+
+def test_pack_ragged_matches_host_loops():
+    rng = np.random.default_rng(3)
+    for nseq in (1, 4, 64, 1500):
+        counts = rng.integers(0, 9, size=nseq).astype(np.int32)
+        counts[0] = max(counts[0], 1)
+        pos0 = rng.integers(0, 5000, size=nseq).astype(np.int32)
+        total = int(counts.sum())
+        d = lambda a: torch.from_numpy(a).cuda()
+        seq_start = torch.empty(nseq + 1, dtype=torch.int32, device="cuda")
+        tok_pos = torch.empty(max(total, 1), dtype=torch.int32, device="cuda")
+        tok_seq = torch.empty(max(total, 1), dtype=torch.int32, device="cuda")
+        counts_d, pos0_d = d(counts), d(pos0)
+        pkg.check(K().q38_pack_ragged(pkg.ptr(counts_d), pkg.ptr(pos0_d), nseq, total, pkg.ptr(seq_start),
+                                      pkg.ptr(tok_pos), pkg.ptr(tok_seq), None))
+        sync_ok()
+        want_start = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+        assert np.array_equal(seq_start.cpu().numpy(), want_start)
+        want_pos = np.concatenate([pos0[b] + np.arange(counts[b]) for b in range(nseq)]).astype(np.int32)
+        want_seq = np.concatenate([np.full(counts[b], b) for b in range(nseq)]).astype(np.int32)
+        assert np.array_equal(tok_pos.cpu().numpy()[:total], want_pos)
+        assert np.array_equal(tok_seq.cpu().numpy()[:total], want_seq)
+
+
+# ---------------------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------------------
+def run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decode, split_rows=4):
+    n = batch.num_tokens
+    ld = proj.shape[1]
+    proj_dev = tl.to_dev_bf16(proj)
+    q16 = torch.empty((n, nq, 256), dtype=torch.float16, device="cuda")
+    out = torch.empty((n, nq * 256), dtype=torch.bfloat16, device="cuda")
+    qp = pkg.QkNormRopeParams(pkg.ptr(proj_dev), ld, pkg.ptr(qn_dev), pkg.ptr(kn_dev), 1e-6, 1e7, nq, nkv, pkg.ptr(q16), layer)
+    pkg.check(K().q38_qk_norm_rope_append(C.byref(qp), C.byref(batch.desc), C.byref(pool.desc), None))
+    split = torch.empty(max(split_rows, batch.desc.num_seqs) * nq * 64 * 258, dtype=torch.float32, device="cuda")
+    ap = pkg.AttentionParams(pkg.ptr(q16), pkg.ptr(proj_dev) + nq * 256 * 2, ld, pkg.ptr(out), nq, nkv, layer,
+                             pkg.ptr(split), 64)
+    fn = K().q38_attention_decode if decode else K().q38_attention_prefill
+    pkg.check(fn(C.byref(ap), C.byref(batch.desc), C.byref(pool.desc), None))
+    sync_ok()
+    return q16.float().cpu().numpy().reshape(n, nq * 256), out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("prefix", [0, 1, 63, 64, 300, 2100])
+def test_attention_matches_oracle(dtype, prefix):
+    """One sequence: chunked prefill up to `prefix`, then two decode tokens (6 q heads / 1 kv head)."""
+    nq, nkv = 6, 1
+    ld = 2 * nq * 256 + 2 * nkv * 256
+    rng = np.random.default_rng(11 + prefix)
+    r3 = np.random.default_rng(3)
+    qn, kn = (1 + 0.2 * r3.standard_normal(256)).astype(np.float32), (1 + 0.2 * r3.standard_normal(256)).astype(np.float32)
+    qn_dev, kn_dev = torch.from_numpy(qn).cuda(), torch.from_numpy(kn).cuda()
+    pool = tl.KvPool(nkv, layers=2, num_pages=64, slots=4, max_pages_per_seq=64, dtype=dtype)
+    perm = np.random.default_rng(5).permutation(64).astype(np.int32)
+    pool.table[2] = torch.from_numpy(perm).cuda()
+    chunks, pos = [], 0
+    sizes = (37, 64, 90, 211)
+    while pos < prefix:
+        n = min(sizes[len(chunks) % 4], prefix - pos)
+        chunks.append((pos, n))
+        pos += n
+    chunks += [(prefix, 1), (prefix + 1, 1)]
+    o = tl.oracle()
+    okv = tl.OracleKv(o, nkv, prefix + 2)
+    got_all, want_all = [], []
+    layer = 1
+    for pos0, n in chunks:
+        proj = tl.bf16_round(rng.standard_normal((n, ld)))
+        batch = tl.Batch([(2, pos0, n)])
+        q_got, out_got = run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decode=(n == 1))
+        kd, vd = pool.read_sequence(layer, 2, pos0 + n)
+        for i in range(n):
+            q_ref = okv.append(nq, 1e-6, 1e7, proj[i], pos0 + i, qn, kn, 2 if dtype == 0 else 1)
+            assert np.all(np.abs(q_got[i] - q_ref) <= 2e-3 + 2e-3 * np.abs(q_ref)), (pos0 + i)
+            # K written by the kernel vs the oracle's quantisation: at most one int8 step apart
+            for h in range(nkv):
+                diff = np.abs(kd[h, pos0 + i] - okv.k[h, pos0 + i]).max()
+                assert diff <= np.abs(okv.k[h, pos0 + i]).max() / 100.0 + 1e-3
+        # attention over the cache contents the kernel actually wrote
+        seen = tl.OracleKv(o, nkv, pos0 + n)
+        seen.k[:], seen.v[:] = kd, vd
+        for i in range(n):
+            want_all.append(seen.attend(nq, q_got[i], proj[i, nq * 256:2 * nq * 256], pos0 + i))
+            got_all.append(out_got[i])
+    got, want = np.stack(got_all), np.stack(want_all)
+    assert np.all(np.abs(got - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max()))
+
+
+def test_attention_ragged_batch_gqa4_long_context():
+    """B = 5 sequences decoded together, 8 q / 4 kv heads (group 2) and 24 / 4 (group 6), contexts up to 9000,
+    shuffled page table, attention layer 2 of 3."""
+    rng = np.random.default_rng(21)
+    o = tl.oracle()
+    for nq, nkv in ((8, 4), (24, 4)):
+        ld = 2 * nq * 256 + 2 * nkv * 256
+        qn = (1 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+        kn = (1 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+        qn_dev, kn_dev = torch.from_numpy(qn).cuda(), torch.from_numpy(kn).cuda()
+        ctx = [1, 64, 130, 4100, 9000]
+        pages_needed = sum((c + 64) // 64 + 1 for c in ctx)
+        pool = tl.KvPool(nkv, layers=3, num_pages=pages_needed + 3, slots=8, max_pages_per_seq=160, dtype=0)
+        perm = np.random.default_rng(5).permutation(pages_needed + 3).astype(np.int32)
+        used = 0
+        slots = [6, 0, 3, 1, 5]
+        for s, c in zip(slots, ctx):
+            need = (c + 64) // 64 + 1
+            pool.table[s, :need] = torch.from_numpy(perm[used:used + need]).cuda()
+            used += need
+        layer = 2
+        # fill the caches by prefill chunks of 512 through the append kernel (K/V only matter here)
+        for s, c in zip(slots, ctx):
+            for p0 in range(0, c - 1, 512):
+                n = min(512, c - 1 - p0)
+                proj = tl.bf16_round(rng.standard_normal((n, ld)))
+                batch = tl.Batch([(s, p0, n)])
+                q16 = torch.empty((n, nq, 256), dtype=torch.float16, device="cuda")
+                proj_d = tl.to_dev_bf16(proj)
+                qp = pkg.QkNormRopeParams(pkg.ptr(proj_d), ld, pkg.ptr(qn_dev), pkg.ptr(kn_dev), 1e-6, 1e7,
+                                          nq, nkv, pkg.ptr(q16), layer)
+                pkg.check(K().q38_qk_norm_rope_append(C.byref(qp), C.byref(batch.desc), C.byref(pool.desc), None))
+        # one decode step for all five
+        proj = tl.bf16_round(rng.standard_normal((len(ctx), ld)))
+        batch = tl.Batch([(s, c - 1, 1) for s, c in zip(slots, ctx)])
+        q_got, out_got = run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decode=True, split_rows=8)
+        for b, (s, c) in enumerate(zip(slots, ctx)):
+            kd, vd = pool.read_sequence(layer, s, c)
+            seen = tl.OracleKv(o, nkv, c)
+            seen.k[:], seen.v[:] = kd, vd
+            want = seen.attend(nq, q_got[b], proj[b, nq * 256:2 * nq * 256], c - 1)
+            assert np.all(np.abs(out_got[b] - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())), (nq, b)
+        # the same tokens as a ragged "prefill" batch of single-token chunks must agree as well
+        _, out_pf = run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decode=False, split_rows=8)
+        assert np.all(np.abs(out_pf - out_got) <= 2e-2 * (np.abs(out_got) + 0.02 * np.abs(out_got).max()))
+
+
+# ---------------------------------------------------------------------------------------------------
+# Gated DeltaNet
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("nk,nv", [(2, 6), (2, 2)])
+def test_gdn_matches_oracle(nk, nv):
+    """Chunk lengths {37, 64, 1, 1, 100, 1, 17} on slot 1 of 3, GDN layer 1 of 2; a second sequence runs in
+    the same ragged batch on slot 2 with its own lengths."""
+    rng = np.random.default_rng(5)
+    o = tl.oracle()
+    H = 512
+    conv_dim = 2 * nk * 128 + nv * 128
+    ld = conv_dim + nv * 128
+    layers, layer, slots = 2, 1, 3
+    w_ab = tl.bf16_round(rng.standard_normal((2 * nv, H)) / np.sqrt(H))
+    conv_w = (0.4 * rng.standard_normal((conv_dim, 4))).astype(np.float32)
+    A = (-rng.uniform(0.5, 8, nv)).astype(np.float32)
+    dt = (0.5 * rng.standard_normal(nv)).astype(np.float32)
+    nw = (1 + 0.2 * rng.standard_normal(128)).astype(np.float32)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    w_ab_d, conv_w_d, A_d, dt_d, nw_d = tl.to_dev_bf16(w_ab), dev(conv_w), dev(A), dev(dt), dev(nw)
+    rec = torch.zeros((slots, layers, nv, 128, 128), dtype=torch.float32, device="cuda")
+    conv = torch.zeros((slots, layers, 3, conv_dim), dtype=torch.bfloat16, device="cuda")
+    st = pkg.GdnStateDesc(pkg.ptr(rec), pkg.ptr(conv), layers)
+    dims = pkg.GdnDims(nk, nv, conv_dim, ld)
+    ref_state = {1: (np.zeros(nv * 128 * 128, np.float32), np.zeros(3 * conv_dim, np.float32)),
+                 2: (np.zeros(nv * 128 * 128, np.float32), np.zeros(3 * conv_dim, np.float32))}
+    pos = {1: 0, 2: 0}
+    for n1, n2 in zip((37, 64, 1, 1, 100, 1, 17), (1, 2, 3, 70, 1, 1, 1)):
+        seqs = [(1, pos[1], n1), (2, pos[2], n2)]
+        batch = tl.Batch(seqs)
+        n = n1 + n2
+        proj = tl.bf16_round(rng.standard_normal((n, ld)))
+        x = tl.bf16_round(rng.standard_normal((n, H)))
+        partials = np.stack([o.norm_partials(x[i]) for i in range(n)])
+        ab = torch.empty((n, 2 * nv), dtype=torch.float32, device="cuda")
+        qkv = torch.empty((n, conv_dim), dtype=torch.float32, device="cuda")
+        out = torch.empty((n, nv * 128), dtype=torch.bfloat16, device="cuda")
+        proj_d = tl.to_dev_bf16(proj)
+        x_d, part_d = tl.to_dev_bf16(x), dev(partials)
+        pkg.check(K().q38_gdn_ab(pkg.ptr(x_d), n, H, pkg.ptr(w_ab_d), 2 * nv, pkg.ptr(part_d), 1e-6, pkg.ptr(ab), None))
+        cp = pkg.GdnConvParams(pkg.ptr(proj_d), pkg.ptr(conv_w_d), pkg.ptr(qkv), layer)
+        pkg.check(K().q38_gdn_conv(C.byref(cp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
+        rp = pkg.GdnRecurrenceParams(pkg.ptr(qkv), pkg.ptr(ab), pkg.ptr(A_d), pkg.ptr(dt_d), pkg.ptr(proj_d) + conv_dim * 2,
+                                     ld, pkg.ptr(nw_d), 1e-6, pkg.ptr(out), layer)
+        pkg.check(K().q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
+        sync_ok()
+        ab_got = ab.cpu().numpy()
+        rs = np.array([o.norm_row_scale(partials[i], H, 1e-6) for i in range(n)], np.float32)
+        ab_ref = np.zeros((n, 2 * nv), np.float32)
+        o.qgemm(x, w_ab, rs, 3, out=ab_ref, ldo=2 * nv)
+        assert np.all(np.abs(ab_got - ab_ref) <= 1e-3 + 1e-3 * np.abs(ab_ref))
+        got = out.float().cpu().numpy()
+        row = 0
+        for slot, _, cnt in seqs:
+            s, cs = ref_state[slot]
+            for i in range(cnt):
+                want = o.gdn_token(nk, nv, 1e-6, proj[row], ab_got[row], conv_w, A, dt, nw, s, cs)
+                assert np.all(np.abs(got[row] - want) <= 2e-2 * (np.abs(want) + 0.05)), (slot, pos[slot] + i)
+                row += 1
+            pos[slot] += cnt
+    for slot in (1, 2):
+        s_got = rec[slot, layer].cpu().numpy().reshape(-1)
+        assert np.all(np.abs(s_got - ref_state[slot][0]) <= 1e-3 + 1e-2 * np.abs(ref_state[slot][0]))
+        c_got = conv[slot, layer].float().cpu().numpy().reshape(-1)
+        assert np.array_equal(c_got, ref_state[slot][1])
+    assert float(rec[0].abs().sum()) == 0 and float(rec[:, 0].abs().sum()) == 0, "other slots / layers untouched"
+
+
+# ---------------------------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------------------------
+def run_sampler(logits, params, step, history=None, hist_len=None, cap=16):
+    B, V = logits.shape
+    lg = torch.from_numpy(logits.copy()).cuda()
+    prm = (pkg.SamplingParamsDev * B)(*params)
+    prm_dev = torch.frombuffer(bytearray(bytes(prm)), dtype=torch.uint8).cuda()
+    slot = torch.arange(B, dtype=torch.int32, device="cuda")
+    steps = torch.full((B,), step, dtype=torch.int32, device="cuda")
+    hl = torch.zeros(B, dtype=torch.int32, device="cuda") if hist_len is None else torch.tensor(hist_len, dtype=torch.int32, device="cuda")
+    hist = torch.zeros((B, cap), dtype=torch.int32, device="cuda") if history is None else torch.tensor(history, dtype=torch.int32, device="cuda")
+    out = torch.empty(B, dtype=torch.int32, device="cuda")
+    lp = torch.empty(B, dtype=torch.float32, device="cuda")
+    a = pkg.SamplingArgs(pkg.ptr(lg), V, V, pkg.ptr(prm_dev), pkg.ptr(slot), pkg.ptr(hist), pkg.ptr(hl), cap,
+                         pkg.ptr(steps), pkg.ptr(out), pkg.ptr(lp))
+    pkg.check(K().q38_sample(C.byref(a), B, None))
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), lp.cpu().numpy(), lg.cpu().numpy(), hl.cpu().numpy(), hist.cpu().numpy()
+
+
+def P(t=0.0, k=0, p=1.0, minp=0.0, pres=0.0, rep=1.0, seed=1):
+    return pkg.SamplingParamsDev(t, k, p, minp, pres, rep, seed)
+
+
+def test_sampling_filters_and_determinism():
+    V, B = 248320, 4
+    rng = np.random.default_rng(9)
+    logits = (2.0 * rng.standard_normal((B, V))).astype(np.float32)
+    logits[3] = -1e4
+    toks, lps = [10, 20, 30, 40, 50], [0.0, -0.5, -1.0, -2.0, -8.0]
+    for t, l in zip(toks, lps):
+        logits[3, t] = l
+    logits[1, 77] = logits[1].max() + 1.0
+    logits[1, 50000] = logits[1, 77]  # a tie: the lowest id wins
+    argmax = logits.argmax(axis=1)
+    assert argmax[1] == 77
+    got, lp, _, hl, hist = run_sampler(logits, [P()] * B, 0)
+    assert np.array_equal(got, argmax) and np.all(lp == 0.0)
+    assert np.all(hl == 1) and np.array_equal(hist[:, 0], argmax), "the sampled token is appended to the history"
+    got, *_ = run_sampler(logits, [P(t=1.0, k=1)] * B, 0)
+    assert np.array_equal(got, argmax)
+    # top-p 0.9 on row 3: nucleus {10, 20, 30}
+    counts, trials = {}, 1500
+    for s in range(trials):
+        t = int(run_sampler(logits, [P(t=1.0, p=0.9, seed=1234)] * B, s)[0][3])
+        counts[t] = counts.get(t, 0) + 1
+    assert set(counts) <= {10, 20, 30}
+    z = sum(np.exp(l) for l in lps[:3])
+    for t, l in zip(toks[:3], lps[:3]):
+        expect = np.exp(l) / z * trials
+        assert abs(counts.get(t, 0) - expect) < 5 * np.sqrt(expect)
+    for s in range(200):  # min_p 0.3 keeps logits >= log 0.3
+        assert int(run_sampler(logits, [P(t=1.0, minp=0.3, seed=99)] * B, s)[0][3]) in (10, 20, 30)
+    a = run_sampler(logits, [P(t=0.8, k=50, p=0.95, seed=777)] * B, 5)[0]
+    b = run_sampler(logits, [P(t=0.8, k=50, p=0.95, seed=777)] * B, 5)[0]
+    assert np.array_equal(a, b)
+    # penalties: each distinct history token is penalised once
+    history = np.zeros((B, 16), np.int32)
+    history[0, :3] = [argmax[0], argmax[0], 5]
+    _, _, lg_after, _, _ = run_sampler(logits, [P(pres=0.5, rep=2.0)] * B, 0, history=history.tolist(), hist_len=[3, 0, 0, 0])
+    l0 = logits[0, argmax[0]]
+    assert np.isclose(lg_after[0, argmax[0]], (l0 / 2.0 if l0 > 0 else l0 * 2.0) - 0.5)
+    l5 = logits[0, 5]
+    assert np.isclose(lg_after[0, 5], (l5 / 2.0 if l5 > 0 else l5 * 2.0) - 0.5)
+
+
+def test_target_logprobs_matches_oracle():
+    rng = np.random.default_rng(2)
+    V, rows = 4096, 5
+    logits = (3 * rng.standard_normal((rows, V))).astype(np.float32)
+    targets = rng.integers(0, V, size=rows).astype(np.int32)
+    out = torch.empty(rows, dtype=torch.float32, device="cuda")
+    lg_d, tg_d = torch.from_numpy(logits).cuda(), torch.from_numpy(targets).cuda()
+    pkg.check(K().q38_target_logprobs(pkg.ptr(lg_d), V, V, pkg.ptr(tg_d), rows, pkg.ptr(out), None))
+    torch.cuda.synchronize()
+    lib = tl.oracle().fn("target_logprob", C.c_float)
+    want = [lib(logits[i].ctypes.data_as(C.c_void_p), C.c_int(V), C.c_int(int(targets[i]))) for i in range(rows)]
+    assert np.allclose(out.cpu().numpy(), np.array(want, np.float32), atol=1e-5)
+
+
+def test_launchers_reject_bad_arguments_without_launching():
+    p = tl.make_bq(128, 64, 4, seed=1, fast=True)
+    w = tl.DeviceBQ(p)
+    a = torch.zeros((1, 64), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros((1, 128), dtype=torch.float32, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_STORE_F32, pkg.ptr(out), 128, 0, None, None, None, None, 0, 1e-6)
+    assert K().q38_qgemm(pkg.ptr(a), 0, C.byref(w.desc), C.byref(ep), None, None, -1) == -1
+    assert b"m must be positive" in K().q38_last_error()
+    bad = pkg.BQWeight(w.desc.lo, None, w.desc.scales, 7, 128, 64, 128)
+    assert K().q38_qgemm(pkg.ptr(a), 1, C.byref(bad), C.byref(ep), None, None, -1) == -1
+    assert K().q38_embed(None, None, 0, 128, None, None, None, None) == 0  # m == 0 is a no-op
