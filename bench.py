@@ -1,0 +1,399 @@
+#!/usr/bin/env python3
+"""Benchmark of the hot path: ragged continuous-batching DECODE of the 27B-geometry Qwen3.8 hybrid model
+(64 layers = 48 Gated DeltaNet + 16 full attention, BQ default recipe, int8 paged KV) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one decode step of `--batch` (64) sequences per GPU whose context lengths are a seeded snapshot of
+the continuous-batching trace (prompt log-uniform 64..8192 + tokens generated so far). Weights are random BQ
+planes of the real geometry (no checkpoint exists offline); the states are produced by really prefilling the
+prompts through the engine. With N > 1 every rank runs its own engine replica on its own GPU (request
+sharding, no collective on the data path); the value is the whole-job tok/s.
+
+  value      device-timed steps with inputs resident in HBM (CUDA events around K replays of the step's graph)
+  e2e        the same K steps through ModelRunner::decode() from host buffers: metadata upload, graph launch,
+             token download, stream sync every step (what a caller of the engine sees)
+  roofline   the op class with the largest share of a step: algorithmic bytes / CUDA-event time, against the
+             measured HBM copy bandwidth of this pool
+  cpu_baseline / --impl reference: the reference's own CPU model (oracle/_ref/qwen38-ref) on the host cores, on
+             a bounded sample: one GDN + one attention layer of the same geometry, extrapolated to 64 layers.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL_DIR = Path(os.environ.get("Q38_BENCH_DIR", "/dev/shm" if Path("/dev/shm").is_dir() else tempfile.gettempdir()))
+SEED = 11
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return float(j["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+
+
+# ----------------------------------------------------------------------------------------------------
+# workload
+# ----------------------------------------------------------------------------------------------------
+def trace_contexts(batch: int, rank: int):
+    """Context lengths of the `batch` running sequences of one replica: prompt log-uniform in [64, 8192]
+    (the trace of BASELINE config 5) plus a uniform number of already generated tokens in [0, 512)."""
+    rng = np.random.default_rng(SEED + 1000 * rank)
+    prompt = np.rint(np.exp(rng.uniform(math.log(64), math.log(8192), size=batch))).astype(int)
+    done = rng.integers(0, 512, size=batch)
+    return (prompt + done).astype(int)
+
+
+def weight_bytes_by_role(cfg, recipe):
+    """Algorithmic weight bytes of every GEMM class per step (all layers), group size 64."""
+    from q38b200 import bqformat as bq
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    lk, lv = cfg["linear_num_key_heads"], cfg["linear_num_value_heads"]
+    n_attn = sum(t == "full_attention" for t in cfg["layer_types"])
+    n_gdn = len(cfg["layer_types"]) - n_attn
+    up = lambda x: (x + 127) // 128 * 128
+    bits = bq.RECIPES[recipe]
+
+    def planes(role, rows, k):
+        return sum(bq.plane_bytes(up(rows), k, bits[role]))
+    conv_dim = 2 * lk * 128 + lv * 128
+    return {
+        "gemm.attn_qkvg": n_attn * planes("attn.qkvg", 2 * nq * 256 + 2 * nkv * 256, H),
+        "gemm.attn_o": n_attn * planes("attn.o", H, nq * 256),
+        "gemm.gdn_qkvz": n_gdn * planes("gdn.qkvz", conv_dim + lv * 128, H),
+        "gemm.gdn_out": n_gdn * planes("gdn.out", H, lv * 128),
+        "gemm.mlp_gate_up": len(cfg["layer_types"]) * planes("mlp.gate_up", 2 * I, H),
+        "gemm.mlp_down": len(cfg["layer_types"]) * planes("mlp.down", H, I),
+        "gemm.lm_head": planes("lm_head", V, H),
+    }
+
+
+def op_bytes(cfg, recipe, batch, ctx_sum):
+    """Algorithmic bytes per decode step of every op class (the per-unit figures of DESIGN.md)."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    lk, lv = cfg["linear_num_key_heads"], cfg["linear_num_value_heads"]
+    n_attn = sum(t == "full_attention" for t in cfg["layer_types"])
+    n_gdn = len(cfg["layer_types"]) - n_attn
+    conv_dim = 2 * lk * 128 + lv * 128
+    b = dict(weight_bytes_by_role(cfg, recipe))
+    b["attn.decode"] = n_attn * (ctx_sum * 2 * nkv * (256 + 8) + batch * 3 * nq * 256 * 2)
+    b["attn.qk_norm_rope_kv"] = n_attn * batch * ((2 * nq + 2 * nkv) * 256 * 2 + nq * 256 * 2 + 2 * nkv * (256 + 8))
+    b["gdn.recurrence"] = n_gdn * batch * (2 * lv * 128 * 128 * 4 + conv_dim * 4 + 2 * lv * 128 * 2)
+    b["gdn.conv"] = n_gdn * batch * (conv_dim * 2 + conv_dim * 4 + 2 * 3 * conv_dim * 2)
+    b["gdn.ab"] = n_gdn * (2 * lv * H * 2 + batch * H * 2)
+    b["embed"] = batch * H * (2 + 4 + 2)
+    b["sample"] = batch * V * 4
+    return b
+
+
+def build_model(path: Path, layers: int, recipe: str, rank: int, world: int):
+    from q38b200 import synth
+    cfg = synth.model_config(**{**synth.CONFIG_27B, "layers": layers})
+    if rank == 0 and not path.exists():
+        t = time.time()
+        log(f"bench: writing {path} ...")
+        synth.write_random_planes_q38(path, cfg, recipe=recipe, seed=SEED)
+        log(f"bench: model file written in {time.time() - t:.0f} s ({path.stat().st_size / 1e9:.1f} GB)")
+    return cfg
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            self.proc.wait()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's own CPU model on a bounded sample
+# ----------------------------------------------------------------------------------------------------
+def cpu_reference_sample(recipe: str, max_procs: int = 8):
+    """tok/s of `qwen38-ref` for 27B-geometry decode, extrapolated from one GDN + one attention layer."""
+    from q38b200 import synth
+    exe = ROOT / "oracle" / "_ref" / "qwen38-ref"
+    if not exe.exists():
+        return None
+    cfg = synth.model_config(**{**synth.CONFIG_27B, "layers": 2, "vocab": 1024,
+                                "layer_types": ["linear_attention", "full_attention"]})
+    path = MODEL_DIR / f"q38_cpu_sample_{recipe}.q38"
+    if not path.exists():
+        synth.write_random_planes_q38(path, cfg, recipe=recipe, seed=SEED)
+    procs = max(1, min(max_procs, os.cpu_count() or 1))
+    td = Path(tempfile.mkdtemp())
+
+    def timed(ntok: int) -> float:
+        jobs = []
+        t0 = time.time()
+        for p in range(procs):
+            tok = td / f"t{p}_{ntok}.i32"
+            np.random.default_rng(p).integers(1000, 1020, size=ntok).astype("<i4").tofile(tok)
+            jobs.append(subprocess.Popen([str(exe), "--model", str(path), "--tokens", str(tok), "--out",
+                                          str(td / f"l{p}.f32"), "--kv", "int8"], stderr=subprocess.DEVNULL))
+        for j in jobs:
+            j.wait()
+        return time.time() - t0
+    t1, t3 = timed(1), timed(3)
+    pair_s = max((t3 - t1) / 2.0, 1e-6)          # one token through (1 GDN + 1 attention layer), per process
+    macs = weight_macs()
+    full_s = pair_s * (macs["all_layers"] + macs["lm_head"]) / macs["pair"]
+    return {"value": procs / full_s, "unit": "tok/s", "cores": procs, "kind": "reference",
+            "sample": (f"{procs} qwen38-ref processes x 2 decode tokens through 1 GDN + 1 attention layer of the 27B "
+                       f"geometry ({pair_s:.2f} s per token-pair-of-layers), extrapolated by GEMM MACs to 64 layers + LM head; "
+                       "short context, so attention over the KV cache is not in the sample")}
+
+
+def weight_macs():
+    H, I, V = 5120, 17408, 248320
+    gdn = 16384 * H + H * 6144 + 2 * I * H + H * I
+    attn = 14336 * H + H * 6144 + 2 * I * H + H * I
+    return {"pair": gdn + attn, "all_layers": 48 * gdn + 16 * attn, "lm_head": V * H}
+
+
+# ----------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=64, help="debug: fewer layers (the result is then not a bench value)")
+    ap.add_argument("--recipe", default="default")
+    ap.add_argument("--max-context", type=int, default=8192 + 512 + 1024)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-steps", type=int, default=3)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = (f"27B-geometry hybrid model ({args.layers} layers), BQ {args.recipe} recipe, int8 paged KV, ragged decode "
+                f"step of {args.batch} sequences per GPU, contexts = trace prompts log-uniform 64..8192 + generated 0..511")
+    config = {"workload": workload, "batch_per_gpu": args.batch, "recipe": args.recipe, "kv": "int8, 64-token pages",
+              "parallelism": f"request-sharded x{world}" if world > 1 else "single replica",
+              "l2": "inputs larger than L2 (15.9 GB of weights per step)"}
+
+    import __graft_entry__ as entry
+    entry.load_package()
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base = cpu_reference_sample(args.recipe)
+        if base is None:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/qwen38-ref has not been built"}))
+            return
+        line = {"impl": "reference", "metric": "decode_tok_per_s", "value": base["value"], "unit": "tok/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": 1000.0 * args.batch * world / base["value"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16 x BQ4/5/8 weights, fp32 accumulate", "data": "synthetic",
+                "config": config, "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import torch
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from q38b200 import engine as eng
+
+    model_path = MODEL_DIR / f"q38_bench_27b_{args.recipe}_L{args.layers}.q38"
+    cfg = build_model(model_path, args.layers, args.recipe, rank, world)
+    barrier()
+    model = eng.Model(model_path)
+    B = args.batch
+    ctx = trace_contexts(B, rank)
+    kv_tokens = int(sum((c + args.steps + args.warmup + 64 + 63) // 64 * 64 for c in ctx)) + 64 * 8
+    runner = eng.Runner(model, eng.default_runner_options(max_batch=B, prefill_chunk=512, kv_tokens=kv_tokens,
+                                                          max_context=args.max_context, verbose=int(rank == 0)))
+    g = eng.greedy()
+    rng = np.random.default_rng(SEED + rank)
+
+    # ---- state: really prefill every sequence's context (ragged steps of up to 512 tokens) ----------
+    t0 = time.time()
+    for s in range(B):
+        runner.reset_slot(s)
+        assert runner.kv_ensure(s, int(ctx[s]) + args.steps + args.warmup + 8 + args.profile_steps)
+    todo = [[s, 0] for s in range(B)]
+    prefill_tokens, prefill_ms = 0, 0.0
+    while todo:
+        rows, budget = [], 512
+        for item in list(todo):
+            if budget == 0:
+                break
+            s, done = item
+            n = min(budget, int(ctx[s]) - done)
+            rows.append((s, done, rng.integers(1000, 150000, size=n).astype(np.int32), None, 0))
+            budget -= n
+            item[1] += n
+            if item[1] == ctx[s]:
+                todo.remove(item)
+        runner.prefill(rows)
+        prefill_ms += runner.last_step_ms()
+        prefill_tokens += 512 - budget
+    torch.cuda.synchronize()
+    log(f"bench[{rank}]: prefilled {prefill_tokens} tokens in {time.time() - t0:.1f} s "
+        f"({prefill_tokens / max(prefill_ms, 1e-3) * 1000:.0f} tok/s device-timed)")
+
+    pos = [int(c) for c in ctx]
+    tok = rng.integers(1000, 150000, size=B).astype(np.int32)
+
+    def host_step():
+        nonlocal tok
+        toks, _ = runner.decode([(s, pos[s], int(tok[s]), g, 1) for s in range(B)])
+        for s in range(B):
+            pos[s] += 1
+        tok = toks
+
+    for _ in range(args.warmup):
+        host_step()
+
+    # ---- timed region 1: e2e through the host API ---------------------------------------------------
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        t_start = time.perf_counter()
+        for _ in range(args.steps):
+            host_step()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t_start
+        barrier()
+        # ---- timed region 2: device-resident replay (CUDA events inside the runner) ------------------
+        core_ms = runner.replay_decode_core(B, args.steps)
+        torch.cuda.synchronize()
+    clock_summary = clocks.summary()
+    times = torch.tensor([e2e_s, core_ms * args.steps / 1000.0], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    e2e_s, core_s = float(times[0]), float(times[1])
+    total_tokens = B * world * args.steps
+
+    # ---- per-op device times of the same step (eager, CUDA events between kernels) -----------------
+    runner.set_profiling(True)
+    for _ in range(args.profile_steps):
+        host_step()
+    prof = runner.profile(clear=True)
+    runner.set_profiling(False)
+    peak, peak_src = measured_peaks()
+    bytes_by_op = op_bytes(cfg, args.recipe, B, int(sum(pos)))
+    per_step = {k: v[0] / args.profile_steps for k, v in prof.items() if k != "start"}
+    calls = {k: v[1] // args.profile_steps for k, v in prof.items()}
+    step_ms_profiled = sum(per_step.values())
+    families = {"qgemm_stream (all BQ GEMMs)": [k for k in per_step if k.startswith("gemm.")],
+                "gdn_recurrence": ["gdn.recurrence"], "attn_token + merge (decode attention)": ["attn.decode"]}
+    fam = {}
+    for name, ops in families.items():
+        ms = sum(per_step.get(o, 0.0) for o in ops)
+        by = sum(bytes_by_op.get(o, 0) for o in ops)
+        n = sum(calls.get(o, 0) for o in ops)
+        if ms > 0:
+            fam[name] = {"ms_per_step": ms, "share": ms / step_ms_profiled, "launches_per_step": n,
+                         "GBps": by / ms / 1e6, "frac": by / ms / 1e6 / peak}
+    top = max(fam, key=lambda k: fam[k]["ms_per_step"])
+    roofline = {"bound": "hbm", "kernel": top, "achieved": fam[top]["GBps"], "peak": peak, "unit": "GB/s",
+                "frac": fam[top]["frac"], "traffic": None, "peak_source": peak_src,
+                "avg_launch_us": 1000.0 * fam[top]["ms_per_step"] / max(1, fam[top]["launches_per_step"]),
+                "share_of_step": fam[top]["share"], "all": fam}
+    step_bytes = sum(bytes_by_op.values())
+    launches = sum(calls.get(k, 0) for k in per_step) + calls.get("gdn.conv", 0) + calls.get("attn.decode", 0) + 1
+
+    line = {
+        "metric": "decode_tok_per_s", "value": total_tokens / core_s, "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * core_s / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 x BQ4/5/8 weights, fp32 accumulate", "data": "synthetic", "config": config,
+        "e2e": {"value": total_tokens / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": B * (4 + 5 * 4 + 32),
+                "d2h_bytes_per_step": B * 8, "ms_per_step": 1000.0 * e2e_s / args.steps},
+        "gpu_launches": launches * args.steps,
+        "clocks": clock_summary, "roofline": roofline,
+        "step_bytes_algorithmic": step_bytes, "step_hbm_frac": step_bytes / (core_s / args.steps) / 1e9 / peak,
+        "prefill_tok_per_s": prefill_tokens / max(prefill_ms, 1e-3) * 1000.0,
+        "context_tokens_per_gpu": int(sum(pos)),
+        "per_op_ms": {k: round(v, 4) for k, v in sorted(per_step.items())},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        base = cpu_reference_sample(args.recipe)
+        line["cpu_baseline"] = base if base else {"value": None, "unit": "tok/s", "cores": 0, "kind": "reference",
+                                                  "sample": "oracle/_ref/qwen38-ref not built"}
+    if rank == 0:
+        print(json.dumps(line))
+    runner.close()
+    model.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -124,3 +124,107 @@ def write_q38(path: str | Path, cfg: dict, ckpt: dict[str, torch.Tensor], recipe
         w.add_bq(f"{i}.mlp.down", f32(p + "mlp.down_proj.weight"), bits_of["mlp.down"], grid, device=device)
     w.add_bq("lm_head", f32("lm_head.weight") * gamma("norm.weight")[None, :], bits_of["lm_head"], grid, device=device)
     w.write(path)
+
+
+def write_random_planes_q38(path: str | Path, cfg: dict, recipe: str = "default", seed: int = 11,
+                            weight_std: float = 0.02) -> None:
+    """A benchmark-sized model without running the quantiser: every BQ tensor gets uniformly random codes
+    and scales chosen so that the dequantised weights have standard deviation `weight_std`. One layer's
+    random bytes are drawn per (role, bits) and reused by every layer of that kind: the engine still streams
+    every layer's own copy from HBM, only the byte values repeat. Throughput runs only — parity runs use
+    write_q38 with the real quantiser."""
+    import json
+    import struct
+
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    bits_of = bq.RECIPES[recipe]
+    H, V, I = cfg["hidden_size"], cfg["vocab_size"], cfg["intermediate_size"]
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    lk, lv = cfg["linear_num_key_heads"], cfg["linear_num_value_heads"]
+    conv_dim = 2 * lk * 128 + lv * 128
+    up = lambda x, a: (x + a - 1) // a * a
+    records, blobs, cursor = {}, [], 0
+
+    def place(blob: bytes) -> int:
+        nonlocal cursor
+        cursor = up(cursor, 256)
+        at = cursor
+        blobs.append((at, blob))
+        cursor += len(blob)
+        return at
+
+    cache: dict = {}
+
+    def bq_planes(role: str, rows: int, k: int):
+        bits = bits_of[role]
+        n = up(rows, 128)
+        key = (role, n, k, bits)
+        if key not in cache:
+            lo_b, hi_b, sc_b = bq.plane_bytes(n, k, bits)
+            lo = rng.integers(0, 256, size=lo_b, dtype=np.uint8).tobytes()
+            hi = rng.integers(0, 256, size=hi_b, dtype=np.uint8).tobytes() if hi_b else b""
+            s = weight_std * (12 ** 0.5) / (1 << bits)
+            sc = (torch.full((sc_b // 2,), s) * (0.75 + 0.5 * torch.rand(sc_b // 2))).to(torch.bfloat16)
+            cache[key] = (lo, hi, sc.view(torch.int16).numpy().tobytes())
+        return bits, n, cache[key]
+
+    def add_bq(name: str, role: str, rows: int, k: int):
+        bits, n, (lo, hi, sc) = bq_planes(role, rows, k)
+        planes = {"lo": [place(lo), len(lo)]}
+        if hi:
+            planes["hi"] = [place(hi), len(hi)]
+        planes["scales"] = [place(sc), len(sc)]
+        rec = {"dtype": f"bq{bits}", "shape": [n, k], "group_size": 64, "planes": planes}
+        if n != rows:
+            rec["rows"] = rows
+        records[name] = rec
+
+    def add_direct(name: str, t: torch.Tensor, dtype: str):
+        blob = (t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes() if dtype == "bf16"
+                else t.to(torch.float32).contiguous().numpy().tobytes())
+        records[name] = {"dtype": dtype, "shape": list(t.shape), "offset": place(blob), "bytes": len(blob)}
+
+    g = torch.Generator().manual_seed(seed)
+    base = torch.randn((min(V, 4096), H), generator=g) * weight_std
+    add_direct("embed", base.repeat((V + base.shape[0] - 1) // base.shape[0], 1)[:V], "bf16")
+    small = {
+        "q_norm": 1.0 + 0.2 * torch.randn(hd, generator=g), "k_norm": 1.0 + 0.2 * torch.randn(hd, generator=g),
+        "ab": torch.randn((2 * lv, H), generator=g) * weight_std, "conv": 0.4 * torch.randn((conv_dim, 4), generator=g),
+        "A": -torch.empty(lv).uniform_(0.5, 8.0, generator=g), "dt": 0.5 * torch.randn(lv, generator=g),
+        "norm": 1.0 + 0.2 * torch.randn(128, generator=g),
+    }
+    for i, kind in enumerate(cfg["layer_types"]):
+        if kind == "full_attention":
+            add_bq(f"{i}.attn.qkvg", "attn.qkvg", 2 * nq * hd + 2 * nkv * hd, H)
+            add_bq(f"{i}.attn.o", "attn.o", H, nq * hd)
+            add_direct(f"{i}.attn.q_norm", small["q_norm"], "f32")
+            add_direct(f"{i}.attn.k_norm", small["k_norm"], "f32")
+        else:
+            add_bq(f"{i}.gdn.qkvz", "gdn.qkvz", conv_dim + lv * 128, H)
+            add_direct(f"{i}.gdn.ab", small["ab"], "bf16")
+            add_direct(f"{i}.gdn.conv", small["conv"], "f32")
+            add_direct(f"{i}.gdn.A", small["A"], "f32")
+            add_direct(f"{i}.gdn.dt_bias", small["dt"], "f32")
+            add_direct(f"{i}.gdn.norm", small["norm"], "f32")
+            add_bq(f"{i}.gdn.out", "gdn.out", H, lv * 128)
+        add_bq(f"{i}.mlp.gate_up", "mlp.gate_up", 2 * I, H)
+        add_bq(f"{i}.mlp.down", "mlp.down", H, I)
+    add_bq("lm_head", "lm_head", V, H)
+
+    header = {"format": "qwen38-model", "format_version": 1, "config": cfg, "recipe": {"name": recipe},
+              "tensors": records, "resources": {},
+              "provenance": {"source": "synthetic random planes", "converter": "qwen38-b200 synth"}}
+    hb = json.dumps(header).encode("utf-8")
+    start = up(16 + len(hb), 4096)
+    tmp = Path(str(path) + ".partial")
+    with open(tmp, "wb") as f:
+        f.write(bq.MAGIC + struct.pack("<Q", len(hb)) + hb)
+        f.write(b"\0" * (start - f.tell()))
+        for at, blob in blobs:
+            f.seek(start + at)
+            f.write(blob)
+        f.seek(start + cursor)
+        f.truncate()
+    tmp.replace(path)
