@@ -8,6 +8,8 @@
 // exact bf16 subtraction, and one bf16 multiply by the group scale performs the single rounding.
 #pragma once
 
+#include <utility>
+
 #include "common.cuh"
 
 namespace q38 {
@@ -25,39 +27,64 @@ struct BqGeom {
 __device__ __forceinline__ uint32_t bf16x2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 bits_bf16x2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
+// Right / left shifts by a compile-time amount issued as integer multiplies: on this architecture the
+// multiplier shares the fp32 pipe, while shifts and logic ops compete for the half-rate integer pipe that
+// bounds the decoder (measured: integer pipe ~50 % busy at 30 % of HBM bandwidth with plain shifts).
+template <int SH>
+__device__ __forceinline__ uint32_t shr_mul(uint32_t x) {
+  if constexpr (SH == 0) return x;
+  else return __umulhi(x, 1u << (32 - SH));
+}
+template <int SH>
+__device__ __forceinline__ uint32_t shl_mul(uint32_t x) {
+  if constexpr (SH == 0) return x;
+  else return x * (1u << SH);
+}
+
+template <int BITS, int Q>
+__device__ __forceinline__ uint32_t decode_pair(const uint32_t (&lo)[4], const uint32_t (&hi)[4], uint32_t s2) {
+  constexpr uint32_t kMagic = 0x43004300u;  // bf16x2 (128, 128)
+  constexpr uint32_t kNib = 0x000F000Fu;
+  constexpr int p = Q & 3;
+  uint32_t v = (shr_mul<4 * p>(lo[Q >> 2]) & kNib) | kMagic;
+  __nv_bfloat162 c;
+  if constexpr (BITS == 4) {
+    c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43084308u));  // 136
+  } else if constexpr (BITS == 5) {
+    uint32_t h;
+    if constexpr (Q >= 4) h = shr_mul<Q - 4>(hi[0]);
+    else h = shl_mul<4 - Q>(hi[0]);
+    v |= h & 0x00100010u;
+    c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43104310u));  // 144
+  } else if constexpr (BITS == 6) {
+    constexpr int r = Q & 7;
+    uint32_t h;
+    if constexpr (2 * r >= 4) h = shr_mul<2 * r - 4>(hi[Q >> 3]);
+    else h = shl_mul<4 - 2 * r>(hi[Q >> 3]);
+    v |= h & 0x00300030u;
+    c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43204320u));  // 160
+  } else {
+    const uint32_t vh = (shr_mul<4 * p>(hi[Q >> 2]) & kNib) | kMagic;
+    // code = 16 * (hi - 8) + lo, every intermediate is a small integer (exact in bf16)
+    const __nv_bfloat162 top = __hsub2(bits_bf16x2(vh), bits_bf16x2(0x43084308u));
+    const __nv_bfloat162 low = __hsub2(bits_bf16x2(v), bits_bf16x2(kMagic));
+    c = __hfma2(top, bits_bf16x2(0x41804180u), low);  // 16.0
+  }
+  return bf16x2_bits(__hmul2(c, bits_bf16x2(s2)));
+}
+
+template <int BITS, int... Q>
+__device__ __forceinline__ void decode_all(const uint32_t (&lo)[4], const uint32_t (&hi)[4], const uint32_t (&s2)[8],
+                                           uint32_t (&w)[16], std::integer_sequence<int, Q...>) {
+  ((w[Q] = decode_pair<BITS, Q>(lo, hi, s2[Q >> 1])), ...);
+}
+
 // lo: the lane's four lo words. hi: the lane's hi words (BqGeom::kHiLaneWords of them are read).
 // s2[j]: the scale of column 8 j + g duplicated into both halves of a bf16x2.
 template <int BITS>
 __device__ __forceinline__ void decode_slab(const uint32_t (&lo)[4], const uint32_t (&hi)[4], const uint32_t (&s2)[8],
                                             uint32_t (&w)[16]) {
-  constexpr uint32_t kMagic = 0x43004300u;  // bf16x2 (128, 128)
-  constexpr uint32_t kNib = 0x000F000Fu;
-#pragma unroll
-  for (int q = 0; q < 16; ++q) {
-    const int p = q & 3;
-    uint32_t v = ((lo[q >> 2] >> (4 * p)) & kNib) | kMagic;
-    __nv_bfloat162 c;
-    if constexpr (BITS == 4) {
-      c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43084308u));  // 136
-    } else if constexpr (BITS == 5) {
-      const uint32_t h = q >= 4 ? (hi[0] >> (q - 4)) : (hi[0] << (4 - q));
-      v |= h & 0x00100010u;
-      c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43104310u));  // 144
-    } else if constexpr (BITS == 6) {
-      const int r = q & 7;
-      const uint32_t word = hi[q >> 3];
-      const uint32_t h = 2 * r >= 4 ? (word >> (2 * r - 4)) : (word << (4 - 2 * r));
-      v |= h & 0x00300030u;
-      c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43204320u));  // 160
-    } else {
-      const uint32_t vh = ((hi[q >> 2] >> (4 * p)) & kNib) | kMagic;
-      // code = 16 * (hi - 8) + lo, every intermediate is a small integer (exact in bf16)
-      const __nv_bfloat162 top = __hsub2(bits_bf16x2(vh), bits_bf16x2(0x43084308u));
-      const __nv_bfloat162 low = __hsub2(bits_bf16x2(v), bits_bf16x2(kMagic));
-      c = __hfma2(top, bits_bf16x2(0x41804180u), low);  // 16.0
-    }
-    w[q] = bf16x2_bits(__hmul2(c, bits_bf16x2(s2[q >> 1])));
-  }
+  decode_all<BITS>(lo, hi, s2, w, std::make_integer_sequence<int, 16>{});
 }
 
 // Expands the lane's eight scales (one 16-byte read: columns 8 j + g, j = 0..7) into duplicated pairs.

@@ -14,45 +14,56 @@ constexpr int kDk = 128, kDv = 128;
 
 // ---------------------------------------------------------------------------------------------------
 // gdn_ab: ab[m][j] = rs[m] * sum_k xbf[m][k] * w[j][k]  (fp32; rows j < nv are b, the rest a).
-// One CTA per token, one warp per output row (strided), 16-byte loads of both operands.
+// One CTA per (8 weight rows, 8 tokens): a warp owns one weight row and keeps 8 token accumulators, so every
+// 16-byte weight load is used 8 times; both operands stream from L2.
 // ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __restrict__ xbf, int hidden,
+constexpr int kAbTokens = 8;
+__global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __restrict__ xbf, int m, int hidden,
                                                      const __nv_bfloat16* __restrict__ w, int rows,
                                                      const float* __restrict__ partials_in, float eps,
                                                      float* __restrict__ ab_out) {
-  extern __shared__ __align__(16) uint8_t ab_smem[];
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ab_smem);
-  __shared__ float rs_sm;
-  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < hidden / 8; i += 256)
-    reinterpret_cast<uint4*>(xs)[i] = reinterpret_cast<const uint4*>(xbf + (size_t)m * hidden)[i];
-  if (tid == 0) {
-    float rs = 1.0f;
-    if (partials_in) {
-      const int blocks = hidden / 128;
-      float sum = 0.0f;
-      for (int b = 0; b < blocks; ++b) sum += partials_in[(size_t)m * blocks + b];
-      rs = 1.0f / sqrtf(sum / float(hidden) + eps);
-    }
-    rs_sm = rs;
-  }
-  __syncthreads();
-  for (int j = warp; j < rows; j += 8) {
-    const __nv_bfloat16* wr = w + (size_t)j * hidden;
-    float acc = 0.0f;
-    for (int c = lane; c < hidden / 8; c += 32) {
-      const uint4 wv = reinterpret_cast<const uint4*>(wr)[c];
-      const uint4 xv = reinterpret_cast<const uint4*>(xs)[c];
-      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
-      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j = blockIdx.x * 8 + warp, m0 = blockIdx.y * kAbTokens;
+  if (j >= rows) return;
+  const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)j * hidden);
+  float acc[kAbTokens];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc += __low2float(wp[i]) * __low2float(xp[i]);
-        acc += __high2float(wp[i]) * __high2float(xp[i]);
+  for (int t = 0; t < kAbTokens; ++t) acc[t] = 0.0f;
+  for (int c = lane; c < hidden / 8; c += 32) {
+    const uint4 wv = wr[c];
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    float wf[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wf[2 * i] = __low2float(wp[i]);
+      wf[2 * i + 1] = __high2float(wp[i]);
+    }
+#pragma unroll
+    for (int t = 0; t < kAbTokens; ++t) {
+      if (m0 + t < m) {
+        const uint4 xv = reinterpret_cast<const uint4*>(xbf + (size_t)(m0 + t) * hidden)[c];
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[t] += wf[2 * i] * __low2float(xp[i]);
+          acc[t] += wf[2 * i + 1] * __high2float(xp[i]);
+        }
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) ab_out[(size_t)m * rows + j] = acc * rs_sm;
+  }
+#pragma unroll
+  for (int t = 0; t < kAbTokens; ++t) {
+    const float total = warp_sum(acc[t]);
+    if (lane == 0 && m0 + t < m) {
+      float rs = 1.0f;
+      if (partials_in) {
+        const int blocks = hidden / 128;
+        float sum = 0.0f;
+        for (int b = 0; b < blocks; ++b) sum += partials_in[(size_t)(m0 + t) * blocks + b];
+        rs = 1.0f / sqrtf(sum / float(hidden) + eps);
+      }
+      ab_out[(size_t)(m0 + t) * rows + j] = total * rs;
+    }
   }
 }
 
@@ -221,13 +232,10 @@ extern "C" int q38_gdn_ab(const q38_bf16* xbf, int m, int hidden, const q38_bf16
   if (m == 0) return Q38_OK;
   Q38_REQUIRE(xbf && w_ab && ab_out, "gdn_ab: null argument");
   Q38_REQUIRE(m > 0 && hidden > 0 && hidden % 128 == 0 && rows > 0, "gdn_ab: m %d hidden %d rows %d", m, hidden, rows);
-  Q38_REQUIRE(hidden * 2 <= 96 * 1024, "gdn_ab: hidden %d too large for the shared-memory row", hidden);
-  static const cudaError_t attr =
-      cudaFuncSetAttribute(gdn_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-  Q38_CUDA_OK(attr);
-  gdn_ab_kernel<<<m, 256, size_t(hidden) * 2, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(xbf), hidden,
-                                                                  reinterpret_cast<const __nv_bfloat16*>(w_ab), rows,
-                                                                  partials_in, eps, ab_out);
+  const dim3 grid((rows + 7) / 8, (m + kAbTokens - 1) / kAbTokens);
+  gdn_ab_kernel<<<grid, 256, 0, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(xbf), m, hidden,
+                                                     reinterpret_cast<const __nv_bfloat16*>(w_ab), rows, partials_in, eps,
+                                                     ab_out);
   Q38_LAUNCH_OK("gdn_ab_kernel");
   return Q38_OK;
 }

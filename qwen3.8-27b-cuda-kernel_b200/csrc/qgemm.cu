@@ -13,22 +13,25 @@ namespace {
 struct ConfigInfo {
   const char* name;
   int tile_m;
+  bool umma;
 };
 constexpr ConfigInfo kConfigs[] = {
-    {"stream_m8", 8},
-    {"stream_m16", 16},
-    {"stream_m32", 32},
-    {"stream_m64", 64},
+    {"stream_m8", 8, false},   {"stream_m16", 16, false}, {"stream_m32", 32, false}, {"stream_m64", 64, false},
+    {"umma_t32", 32, true},    {"umma_t64", 64, true},    {"umma_t128", 128, true},  {"umma_t256", 256, true},
 };
 constexpr int kNumConfigs = int(sizeof(kConfigs) / sizeof(kConfigs[0]));
 
 q38_gemm_tuning_lookup g_tuning = nullptr;
 
+// Small batches stream the weights through mma.sync (tokens are the 8-wide operand); from 17 tokens on the
+// tcgen05 kernel keeps the accumulators in TMEM.
 int auto_config(int m) {
   if (m <= 8) return 0;
   if (m <= 16) return 1;
-  if (m <= 32) return 2;
-  return 3;
+  if (m <= 32) return 4;
+  if (m <= 64) return 5;
+  if (m <= 128) return 6;
+  return 7;
 }
 
 // One lane decodes one slab exactly as the GEMM does and writes the 32 weights to W[n][k] (bf16).
@@ -107,7 +110,8 @@ extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const
       e.out = static_cast<q38_bf16*>(e.out) + (size_t)r0 * e.ldo;
     }
     if (e.partials_in) e.partials_in += (size_t)r0 * (e.hidden / 128);
-    const int rc = qgemm_stream_launch(tm / 8, ap + (size_t)r0 * w->k, rows, *w, e, ws, s);
+    const int rc = kConfigs[config].umma ? qgemm_umma_launch(tm, ap + (size_t)r0 * w->k, rows, *w, e, ws, s)
+                                         : qgemm_stream_launch(tm / 8, ap + (size_t)r0 * w->k, rows, *w, e, ws, s);
     if (rc != Q38_OK) return rc;
   }
   return Q38_OK;

@@ -1,7 +1,549 @@
-// Prefill-sized BQ GEMM on the 5th-generation tensor cores (tcgen05 + TMEM). Under construction:
-// this translation unit currently only provides its device error word.
+// BQ GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for 17 <= M <= 256 tokens
+// per pass: large decode batches and prefill chunks. Same contract and epilogues as the streaming kernel
+// (qgemm_stream.cu); replaces kernels::qgemm of the reference (src/kernels/kernels.h:119-121) for these M.
+//
+// Orientation: the weights are the MMA's A operand (M_mma = 128 output columns = two 64-column BQ blocks),
+// the tokens are its N operand (N_mma = 32..256), so any token count fills the 128 TMEM lanes.
+// Warp roles of a CTA (one CTA per SM, persistent over a stream-K work list of (tile, 64-wide k-group)):
+//   warp 0      producer: 1-D bulk (TMA) copies of the raw BQ planes (contiguous per 64-column block) and
+//               2-D tensor-map loads of the activation k-slices (128-byte swizzle, rows >= M zero-filled)
+//               into a ring of stages (128 k each);
+//   warps 2-9   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> stored to
+//               the K-major, 128-byte-swizzled shared tile a UMMA descriptor reads (bank-conflict-free 4-byte
+//               stores); afterwards the same warps run the epilogue out of TMEM (tcgen05.ld);
+//   warp 1      one elected thread issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32) per 16-wide k step and
+//               tcgen05.commit to hand slices / stages / the accumulator back.
+// Partial tiles (stream-K) go through the caller's workspace; the last-arriving CTA sums them in CTA order, so
+// results are bit-reproducible. Every wait is bounded; TMEM is always released before the kernel ends.
+#include <algorithm>
+
+#include "bq_dequant.cuh"
 #include "common.cuh"
+#include "host_util.h"
+#include "qgemm.h"
 
 namespace q38 {
+namespace {
+
+constexpr int kTileN = 128;
+constexpr int kGroupsPerStage = 2;
+constexpr int kDecodeWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kSliceBytes = kTileN * 128;  // one [128 n][64 k] bf16 operand slice
+constexpr int kSmemBudget = 225 * 1024;
+
+template <int BITS, int TOK>
+struct UCfg {
+  using G = BqGeom<BITS>;
+  static constexpr int kXGroup = TOK * 128;
+  static constexpr int kXOff = 0;
+  static constexpr int kLoOff = kXOff + kGroupsPerStage * kXGroup;
+  static constexpr int kHiOff = kLoOff + 2 * kGroupsPerStage * G::kLoGroupBytes;
+  static constexpr int kScOff = kHiOff + 2 * kGroupsPerStage * G::kHiGroupBytes;
+  static constexpr int kStageRaw = kScOff + 2 * kGroupsPerStage * G::kScGroupBytes;
+  static constexpr int kStageBytes = (kStageRaw + 1023) / 1024 * 1024;
+  static constexpr int kTail = TOK * 4 + TOK * 4 * 4 + 512;  // row scales, per-quarter partial sums, barriers
+  static constexpr int kFit4 = (kSmemBudget - 1024 - kTail - 4 * kSliceBytes) / kStageBytes;
+  static constexpr int kStages = kFit4 >= 2 ? (kFit4 > 6 ? 6 : kFit4) : 2;
+  static constexpr int kSlices = kFit4 >= 2 ? 4 : (kSmemBudget - 1024 - kTail - 2 * kStageBytes) / kSliceBytes;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kSlices * kSliceBytes + kTail;
+  static constexpr int kTmemCols = TOK < 32 ? 32 : TOK;
+  static_assert(kSlices >= 2, "operand slice ring needs two slots");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+struct UmmaArgs {
+  const uint8_t* lo;
+  const uint8_t* hi;
+  const uint8_t* sc;
+  int n, k, m;
+  int kind;
+  void* out;
+  int ldo;
+  int n_store;
+  float* residual;
+  __nv_bfloat16* xbf;
+  float* partials_out;
+  const float* partials_in;
+  int hidden;
+  float eps;
+  float* ws;
+  int* counters;
+  int tiles, kg;
+  long long units;
+  int split;
+};
+
+__device__ __forceinline__ long long u_begin(const UmmaArgs& a, int cta, int grid) {
+  if (a.split) return (long long)cta * a.units / grid;
+  return ((long long)cta * a.tiles / grid) * a.kg;
+}
+
+__device__ __forceinline__ bool wait_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned site) {
+  if (*abort_flag) return false;
+  if (mbar_wait(bar, parity, site)) return true;
+  *abort_flag = 1;
+  return false;
+}
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = uint64_t((addr & 0x3FFFFu) >> 4);
+  d |= uint64_t(1) << 16;             // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t(1024 >> 4) << 32;     // stride byte offset between 8-row groups
+  d |= uint64_t(1) << 46;             // descriptor version of this architecture
+  d |= uint64_t(2) << 61;             // 128-byte swizzle
+  return d;
+}
+
+template <int BITS, int TOK>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
+  using C = UCfg<BITS, TOK>;
+  using G = BqGeom<BITS>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint8_t* stages = smem;
+  uint8_t* slices = smem + C::kStages * C::kStageBytes;
+  float* rs_sm = reinterpret_cast<float*>(slices + C::kSlices * kSliceBytes);
+  float* part_sm = rs_sm + TOK;  // [TOK][4]
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(part_sm + TOK * 4);
+  uint64_t* raw_empty = raw_full + C::kStages;
+  uint64_t* a_full = raw_empty + C::kStages;
+  uint64_t* a_empty = a_full + C::kSlices;
+  uint64_t* acc_full = a_empty + C::kSlices;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort, [1] last arriver
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grid = gridDim.x, cta = blockIdx.x;
+  const long long u0 = u_begin(a, cta, grid), u1 = u_begin(a, cta + 1, grid);
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], kDecodeWarps + 1);
+    }
+    for (int s = 0; s < C::kSlices; ++s) {
+      mbar_init(&a_full[s], 4);
+      mbar_init(&a_empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, kDecodeWarps);
+    flags[0] = 0;
+    flags[1] = 0;
+    mbar_fence_init();
+  }
+  if (tid < TOK) {
+    float rs = 1.0f;
+    if (a.partials_in && tid < a.m) {
+      const int blocks = a.hidden / 128;
+      float sum = 0.0f;
+      for (int b = 0; b < blocks; ++b) sum += a.partials_in[(size_t)tid * blocks + b];
+      rs = 1.0f / sqrtf(sum / float(a.hidden) + a.eps);
+    }
+    rs_sm[tid] = rs;
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first();
+      uint32_t it = 0;
+      for (long long u = u0; u < u1 && !flags[0];) {
+        const int tile = int(u / a.kg), kg_a = int(u % a.kg);
+        const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+        for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
+          const int s = it % C::kStages;
+          if (!wait_flag(&raw_empty[s], ((it / C::kStages) & 1) ^ 1, flags, 0x301)) break;
+          const int ng = min(kGroupsPerStage, kg_b - g);
+          uint8_t* st = stages + (size_t)s * C::kStageBytes;
+          mbar_expect_tx(&raw_full[s], uint32_t(ng) * (2u * (G::kLoGroupBytes + G::kHiGroupBytes + G::kScGroupBytes) +
+                                                       C::kXGroup));
+          for (int gi = 0; gi < ng; ++gi)
+            tma_load_2d(st + C::kXOff + gi * C::kXGroup, &xmap, (g + gi) * 64, 0, &raw_full[s]);
+#pragma unroll
+          for (int nbl = 0; nbl < 2; ++nbl) {
+            const size_t grp = (size_t)(tile * 2 + nbl) * a.kg + g;
+            bulk_g2s(st + C::kLoOff + nbl * kGroupsPerStage * G::kLoGroupBytes, a.lo + grp * G::kLoGroupBytes,
+                     ng * G::kLoGroupBytes, &raw_full[s], pol_w);
+            if constexpr (BITS != 4)
+              bulk_g2s(st + C::kHiOff + nbl * kGroupsPerStage * G::kHiGroupBytes, a.hi + grp * G::kHiGroupBytes,
+                       ng * G::kHiGroupBytes, &raw_full[s], pol_w);
+            bulk_g2s(st + C::kScOff + nbl * kGroupsPerStage * G::kScGroupBytes, a.sc + grp * G::kScGroupBytes,
+                     ng * G::kScGroupBytes, &raw_full[s], pol_w);
+          }
+        }
+        u += kg_b - kg_a;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TOK >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+      uint32_t it = 0, slice_ctr = 0, seg = 0;
+      bool alive = true;
+      for (long long u = u0; u < u1 && alive; ++seg) {
+        const int kg_a = int(u % a.kg);
+        const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+        alive = wait_flag(acc_empty, (seg & 1) ^ 1, flags, 0x302);
+        tc_fence_after();
+        uint32_t accumulate = 0;
+        for (int g = kg_a; g < kg_b && alive; g += kGroupsPerStage, ++it) {
+          const int s = it % C::kStages;
+          alive = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x303);
+          const int ng = min(kGroupsPerStage, kg_b - g);
+          const uint32_t x_addr = smem_u32(stages + (size_t)s * C::kStageBytes + C::kXOff);
+          for (int gi = 0; gi < ng && alive; ++gi, ++slice_ctr) {
+            const int sl = slice_ctr % C::kSlices;
+            alive = wait_flag(&a_full[sl], (slice_ctr / C::kSlices) & 1, flags, 0x304);
+            if (!alive) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(slices + (size_t)sl * kSliceBytes);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_bf16(tmem_base, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(x_addr + gi * C::kXGroup + ks * 32),
+                        idesc, accumulate);
+              accumulate = 1;
+            }
+            umma_commit(&a_empty[sl]);
+          }
+          umma_commit(&raw_empty[s]);
+        }
+        umma_commit(acc_full);
+        u += kg_b - kg_a;
+      }
+    }
+  } else {
+    // ------------------------------ decode + epilogue warps ------------------------------
+    const int dw = warp - 2;
+    const int dg = dw >> 2;            // k-group of the stage this warp decodes
+    const int dnb = (dw & 3) >> 1;     // 64-column block of the tile
+    const int dks = (dw & 1) * 2;      // first of its two k16 slabs
+    const int gl = lane >> 2, tl = lane & 3;
+    const int quarter = warp & 3;      // TMEM lanes this warp may read
+    const int col_half = dw >> 2;      // which half of the token columns it handles in the epilogue
+    const int et = tid - 64;           // 0..255 among the decode threads
+    uint32_t it = 0, slice_ctr = 0, seg = 0;
+    for (long long u = u0; u < u1; ++seg) {
+      const int tile = int(u / a.kg), kg_a = int(u % a.kg);
+      const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+      for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
+        const int s = it % C::kStages;
+        const int ng = min(kGroupsPerStage, kg_b - g);
+        bool ok = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x305);
+        if (dg < ng) {
+          const uint32_t sc = slice_ctr + dg;
+          const int sl = sc % C::kSlices;
+          ok = ok && wait_flag(&a_empty[sl], ((sc / C::kSlices) & 1) ^ 1, flags, 0x306);
+          if (ok) {
+            const uint8_t* st = stages + (size_t)s * C::kStageBytes;
+            const int slot = dnb * kGroupsPerStage + dg;
+            const uint8_t* lo_g = st + C::kLoOff + slot * G::kLoGroupBytes;
+            const uint8_t* hi_g = st + C::kHiOff + slot * G::kHiGroupBytes;
+            uint32_t s2[8];
+            expand_scales(*reinterpret_cast<const uint4*>(st + C::kScOff + slot * G::kScGroupBytes + 16 * gl), s2);
+            // destination of pair (j, h) of slab ks: row 64 dnb + 8 j + gl, 16-byte chunk (2 ks + h) ^ gl
+            uint8_t* row_a = slices + (size_t)sl * kSliceBytes + uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int ks = dks + e;
+              const uint4 lv = *reinterpret_cast<const uint4*>(lo_g + ks * 512 + lane * 16);
+              const uint32_t lo[4] = {lv.x, lv.y, lv.z, lv.w};
+              uint32_t hi[4] = {0, 0, 0, 0};
+              if constexpr (BITS == 5) {
+                hi[0] = *reinterpret_cast<const uint32_t*>(hi_g + ks * 128 + lane * 4);
+              } else if constexpr (BITS == 6) {
+                const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + ks * 256 + lane * 8);
+                hi[0] = hv.x;
+                hi[1] = hv.y;
+              } else if constexpr (BITS == 8) {
+                const uint4 hv = *reinterpret_cast<const uint4*>(hi_g + ks * 512 + lane * 16);
+                hi[0] = hv.x;
+                hi[1] = hv.y;
+                hi[2] = hv.z;
+                hi[3] = hv.w;
+              }
+              uint32_t w[16];
+              decode_slab<BITS>(lo, hi, s2, w);
+              uint8_t* c0 = row_a + (uint32_t((2 * ks) ^ gl) << 4);
+              uint8_t* c1 = row_a + (uint32_t((2 * ks + 1) ^ gl) << 4);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                *reinterpret_cast<uint32_t*>(c0 + j * 1024) = w[2 * j];
+                *reinterpret_cast<uint32_t*>(c1 + j * 1024) = w[2 * j + 1];
+              }
+            }
+            fence_async_smem();
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[sl]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[s]);
+        slice_ctr += ng;
+      }
+
+      // ---- epilogue of this tile segment ----
+      const bool got = __all_sync(0xffffffffu, wait_flag(acc_full, seg & 1, flags, 0x307));
+      tc_fence_after();
+      const bool whole = kg_a == 0 && kg_b == a.kg;
+      const int n_row = 32 * quarter + lane;  // row of the tile this thread reads from TMEM
+      const int n_glob = tile * kTileN + n_row;
+      const int n_lim = a.n_store > 0 ? a.n_store : a.n;
+      constexpr int kColsPerWarp = TOK / 2;
+      const int col_base = col_half * kColsPerWarp;
+      constexpr int kTileFloats = TOK * kTileN;
+
+      auto finish_chunk = [&](const float (&v)[16], int col0) {
+        if (a.kind == Q38_EPI_RESIDUAL) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = col0 + j;
+            float r = 0.0f;
+            if (col < a.m) {
+              float* rp = a.residual + (size_t)col * a.n + n_glob;
+              r = *rp + v[j];
+              *rp = r;
+              a.xbf[(size_t)col * a.n + n_glob] = __float2bfloat16_rn(r);
+            }
+            const float ss = warp_sum(r * r);
+            if (lane == 0) part_sm[col * 4 + quarter] = ss;
+          }
+          return;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int col = col0 + j;
+          const float x = v[j] * rs_sm[col];
+          if (a.kind == Q38_EPI_SWIGLU) {
+            const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+            if ((lane & 1) == 0 && col < a.m && n_glob < n_lim)
+              static_cast<__nv_bfloat16*>(a.out)[(size_t)col * a.ldo + n_glob / 2] = __float2bfloat16_rn(silu_f(x) * other);
+          } else if (col < a.m && n_glob < n_lim) {
+            if (a.kind == Q38_EPI_STORE_BF16)
+              static_cast<__nv_bfloat16*>(a.out)[(size_t)col * a.ldo + n_glob] = __float2bfloat16_rn(x);
+            else
+              static_cast<float*>(a.out)[(size_t)col * a.ldo + n_glob] = x;
+          }
+        }
+      };
+
+      bool run_epilogue = true;
+      if (whole) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+          uint32_t r[16];
+          float v[16];
+          if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = got ? __uint_as_float(r[j]) : 0.0f;
+          finish_chunk(v, col_base + c0);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);
+      } else {
+        // stream-K: publish this CTA's partial accumulator [token][128 n], then the last arriver reduces
+        float* mine = a.ws + ((size_t)cta * 2 + (kg_a != 0 ? 0 : 1)) * kTileFloats;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+          uint32_t r[16];
+          if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(size_t)(col_base + c0 + j) * kTileN + n_row] = got ? __uint_as_float(r[j]) : 0.0f;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);
+        __threadfence();
+        named_bar_sync(1, kDecodeThreads);
+        const long long t_begin = (long long)tile * a.kg, t_end = t_begin + a.kg;
+        int c_first = int(t_begin * grid / a.units);
+        while (c_first > 0 && u_begin(a, c_first, grid) > t_begin) --c_first;
+        while (u_begin(a, c_first + 1, grid) <= t_begin) ++c_first;
+        int c_last = c_first;
+        while (c_last + 1 < grid && u_begin(a, c_last + 1, grid) < t_end) ++c_last;
+        if (et == 0) {
+          const int prev = atomicAdd(&a.counters[tile], 1);
+          const int last = prev == c_last - c_first;
+          if (last) a.counters[tile] = 0;
+          flags[1] = last;
+        }
+        named_bar_sync(1, kDecodeThreads);
+        run_epilogue = flags[1] != 0;
+        if (run_epilogue) {
+          __threadfence();
+#pragma unroll 1
+          for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            for (int c = c_first; c <= c_last; ++c) {
+              const float* src = a.ws + ((size_t)c * 2 + (u_begin(a, c, grid) > t_begin ? 0 : 1)) * kTileFloats;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)(col_base + c0 + j) * kTileN + n_row);
+            }
+            finish_chunk(v, col_base + c0);
+          }
+        }
+      }
+      if (a.kind == Q38_EPI_RESIDUAL) {
+        named_bar_sync(2, kDecodeThreads);
+        if (run_epilogue && et < a.m && et < TOK) {
+          const float* p = part_sm + et * 4;
+          a.partials_out[(size_t)et * (a.n / 128) + tile] = (p[0] + p[1]) + (p[2] + p[3]);
+        }
+      }
+      named_bar_sync(2, kDecodeThreads);
+      u += kg_b - kg_a;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+template <int BITS, int TOK>
+int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
+               const q38_gemm_workspace* ws, cudaStream_t stream) {
+  using C = UCfg<BITS, TOK>;
+  static const cudaError_t attr =
+      cudaFuncSetAttribute(qgemm_umma_kernel<BITS, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  Q38_CUDA_OK(attr);
+  EncodeFn enc = encode_fn();
+  Q38_REQUIRE(enc != nullptr, "qgemm: cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap xmap;
+  const cuuint64_t dims[2] = {cuuint64_t(w.k), cuuint64_t(m)};
+  const cuuint64_t strides[1] = {cuuint64_t(w.k) * 2};
+  const cuuint32_t box[2] = {64, cuuint32_t(TOK)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(a_ptr), dims, strides,
+                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  Q38_REQUIRE(r == CUDA_SUCCESS, "qgemm: tensor map encode failed (%d)", int(r));
+
+  UmmaArgs a{};
+  a.lo = w.lo;
+  a.hi = w.hi;
+  a.sc = reinterpret_cast<const uint8_t*>(w.scales);
+  a.n = w.n;
+  a.k = w.k;
+  a.m = m;
+  a.kind = ep.kind;
+  a.out = ep.out;
+  a.ldo = ep.ldo;
+  a.n_store = ep.n_store;
+  a.residual = ep.residual;
+  a.xbf = reinterpret_cast<__nv_bfloat16*>(ep.xbf);
+  a.partials_out = ep.partials_out;
+  a.partials_in = ep.partials_in;
+  a.hidden = ep.hidden;
+  a.eps = ep.eps;
+  a.tiles = w.n / kTileN;
+  a.kg = w.k / 64;
+  a.units = (long long)a.tiles * a.kg;
+  const int sms = num_sms();
+  int grid = int(std::min<long long>(sms, std::max<long long>(1, a.units / 8)));
+  const size_t need = (size_t)grid * 2 * TOK * kTileN;
+  // stream-K pays a workspace round trip per CTA boundary: only worth it when the tiles alone cannot fill the SMs evenly
+  const bool want_split = a.tiles < 3 * sms || TOK <= 64;
+  a.split = want_split && ws && ws->partials && ws->counters && ws->partial_floats >= need && ws->num_counters >= a.tiles;
+  if (a.split) {
+    a.ws = ws->partials;
+    a.counters = ws->counters;
+  } else {
+    grid = std::min(sms, a.tiles);
+  }
+  qgemm_umma_kernel<BITS, TOK><<<grid, kThreads, C::kSmemBytes, stream>>>(xmap, a);
+  Q38_LAUNCH_OK("qgemm_umma_kernel");
+  return Q38_OK;
+}
+
+template <int BITS>
+int launch_bits(int tok, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
+                const q38_gemm_workspace* ws, cudaStream_t s) {
+  switch (tok) {
+    case 32: return launch_one<BITS, 32>(a, m, w, ep, ws, s);
+    case 64: return launch_one<BITS, 64>(a, m, w, ep, ws, s);
+    case 128: return launch_one<BITS, 128>(a, m, w, ep, ws, s);
+    default: return launch_one<BITS, 256>(a, m, w, ep, ws, s);
+  }
+}
+
+}  // namespace
+
+// m <= tok, tok in {32, 64, 128, 256}. Called by the dispatcher in qgemm.cu.
+int qgemm_umma_launch(int tok, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
+                      const q38_gemm_workspace* ws, cudaStream_t s) {
+  switch (w.bits) {
+    case 4: return launch_bits<4>(tok, a, m, w, ep, ws, s);
+    case 5: return launch_bits<5>(tok, a, m, w, ep, ws, s);
+    case 6: return launch_bits<6>(tok, a, m, w, ep, ws, s);
+    default: return launch_bits<8>(tok, a, m, w, ep, ws, s);
+  }
+}
+
 unsigned int qgemm_umma_error(bool clear) { return read_tu_error(clear); }
+
 }  // namespace q38
