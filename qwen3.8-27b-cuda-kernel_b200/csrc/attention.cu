@@ -304,6 +304,265 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_token_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Decode attention over int8 KV on tensor cores: one CTA per (split, kv head, sequence), two CTAs per SM.
+//   * a producer lane walks the sequence's block-table row and brings one (page, kv head) per stage with four
+//     1-D bulk copies: K 16 KB, V 16 KB and their two 512-byte scale rows are each contiguous in the page;
+//   * each of the 4 consumer warps owns 16 of the page's 64 tokens. S = K Q^T runs as m16n8k16 f16 MMAs with the
+//     tokens as rows and the (<= 8) query heads of the kv head as the 8 columns; the int8 bytes become exact
+//     fp16 integers in registers (byte permute into 0x64xx = 1024 + x, minus 1152), and the per-(token, 64-dim)
+//     K scale multiplies each 64-dim partial sum in fp32. The order of dims inside an MMA k-step is permuted
+//     so that a lane reads 16 contiguous bytes per token (Q fragments use the same permutation);
+//   * online softmax in the log2 domain on the accumulator fragments; P is scaled by the V scales, cast to
+//     fp16 and transposed in registers (movmatrix) to become the B operand of O^T = V^T P^T, whose A operand
+//     pairs two tokens of one dim (bytes of two V rows permuted together);
+//   * the warps' (m, l, O) are merged through shared memory; a single split finishes in place (normalise,
+//     sigmoid gate, bf16), otherwise the state goes to the scratch for attn_merge_kernel.
+// K/V bytes are read from HBM exactly once per GQA group (reference design point: attention_decode.cu).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kMmaWarps = 4;
+constexpr int kMmaThreads = (kMmaWarps + 1) * 32;
+constexpr int kMmaStages = 3;
+constexpr int kStageK = 0, kStageV = 16384, kStageKs = 32768, kStageVs = 33280, kStageBytes = 33792;
+constexpr int kMmaSmem = kMmaStages * kStageBytes + 256;
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+// two biased bytes (x + 128) of one word -> half2 (x0, x1)
+template <int SEL>
+__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t w) {
+  const uint32_t h = __byte_perm(w, 0x64646464u, SEL);
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half(0x6480)));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+// byte I of two words -> half2 (wa.byte, wb.byte)
+template <int I>
+__device__ __forceinline__ uint32_t byte_pair_to_half2(uint32_t wa, uint32_t wb) {
+  constexpr uint32_t sel = I | (I << 4) | ((4 + I) << 8) | (I << 12);
+  const uint32_t h = (__byte_perm(wa, wb, sel) & 0x00FF00FFu) | 0x64006400u;
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half(0x6480)));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+__global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
+    const __half* __restrict__ q, const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ out,
+    int nq, int group, int layer, float* __restrict__ scratch, int max_splits, int num_splits,
+    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0, KvView kv) {
+  extern __shared__ __align__(128) uint8_t dsm[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm + kMmaStages * kStageBytes);
+  uint64_t* empty = full + kMmaStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMmaStages);
+  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m = seq_start[row], slot = seq_slot[row], L = seq_pos0[row] + 1;
+  const int pages = (L + kPage - 1) / kPage;
+  const int pages_per_split = (pages + num_splits - 1) / num_splits;
+  const int p0 = min(pages, split * pages_per_split), p1 = min(pages, (split + 1) * pages_per_split);
+  if (tid == 0) {
+    for (int s = 0; s < kMmaStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kMmaWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kMmaWarps) {
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_first();
+      const int* table = kv.block_table + (size_t)slot * kv.max_pages_per_seq;
+      for (int p = p0, it = 0; p < p1; ++p, ++it) {
+        const int s = it % kMmaStages;
+        if (*abort_flag || !mbar_wait(&empty[s], ((it / kMmaStages) & 1) ^ 1, 0x211)) {
+          *abort_flag = 1;
+          break;
+        }
+        const int page = table[p];
+        if (page < 0 || page >= kv.num_pages) {
+          report_error(0x212);
+          *abort_flag = 1;
+          break;
+        }
+        const uint8_t* base = kv.pool + (size_t)layer * kv.layer_stride + (size_t)page * kv.page_bytes;
+        uint8_t* st = dsm + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full[s], 2 * 16384 + 2 * 512);
+        bulk_g2s(st + kStageK, base + kv.k_off(kvh, 0), 16384, &full[s], pol);
+        bulk_g2s(st + kStageV, base + kv.v_off(kvh, 0), 16384, &full[s], pol);
+        bulk_g2s(st + kStageKs, base + kv.ks_off(kvh, 0), 512, &full[s], pol);
+        bulk_g2s(st + kStageVs, base + kv.vs_off(kvh, 0), 512, &full[s], pol);
+      }
+    }
+    return;
+  }
+
+  const int g = lane >> 2, t = lane & 3;
+  // Q fragments: head g of the group, dims 64 grp + 16 t + 4 s + {0..3}
+  uint32_t qf[4][4][2];
+  {
+    const bool live = g < group;
+    const __half* qrow = q + ((size_t)m * nq + (size_t)kvh * group + (live ? g : 0)) * kHd;
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp)
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint2 v = *reinterpret_cast<const uint2*>(qrow + 64 * grp + 16 * t + 4 * s);
+        qf[grp][s][0] = live ? v.x : 0u;
+        qf[grp][s][1] = live ? v.y : 0u;
+      }
+  }
+  float o[16][4];
+#pragma unroll
+  for (int T = 0; T < 16; ++T)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[T][c] = 0.0f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // heads 2t and 2t + 1
+  constexpr float kScale = kLog2e / 16.0f;
+
+  for (int p = p0, it = 0; p < p1; ++p, ++it) {
+    const int s = it % kMmaStages;
+    bool ok = !*abort_flag && mbar_wait(&full[s], (it / kMmaStages) & 1, 0x213);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) *abort_flag = 1;
+    const int tok0 = 16 * warp, tbase = p * kPage + tok0;
+    if (ok && tbase < L) {
+      const uint8_t* st = dsm + (size_t)s * kStageBytes;
+      const uint8_t* Ks = st + kStageK + (size_t)tok0 * kHd;
+      const uint8_t* Vs = st + kStageV + (size_t)tok0 * kHd;
+      const __half* Ksc = reinterpret_cast<const __half*>(st + kStageKs) + tok0 * 4;
+      const __half* Vsc = reinterpret_cast<const __half*>(st + kStageVs) + tok0 * 4;
+      // ---- S = K Q^T ----
+      float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        const uint4 ka = *reinterpret_cast<const uint4*>(Ks + g * kHd + 64 * grp + 16 * t);
+        const uint4 kb = *reinterpret_cast<const uint4*>(Ks + (g + 8) * kHd + 64 * grp + 16 * t);
+        const uint32_t wa[4] = {ka.x ^ 0x80808080u, ka.y ^ 0x80808080u, ka.z ^ 0x80808080u, ka.w ^ 0x80808080u};
+        const uint32_t wb[4] = {kb.x ^ 0x80808080u, kb.y ^ 0x80808080u, kb.z ^ 0x80808080u, kb.w ^ 0x80808080u};
+        float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int ss = 0; ss < 4; ++ss)
+          mma_f16_16816(d, bytes_to_half2<0x4140>(wa[ss]), bytes_to_half2<0x4140>(wb[ss]),
+                        bytes_to_half2<0x4342>(wa[ss]), bytes_to_half2<0x4342>(wb[ss]), qf[grp][ss][0], qf[grp][ss][1]);
+        const float ksa = __half2float(Ksc[g * 4 + grp]), ksb = __half2float(Ksc[(g + 8) * 4 + grp]);
+        sacc[0] += ksa * d[0];
+        sacc[1] += ksa * d[1];
+        sacc[2] += ksb * d[2];
+        sacc[3] += ksb * d[3];
+      }
+      // ---- online softmax over the block's 16 tokens ----
+      const bool va = tbase + g < L, vb = tbase + g + 8 < L;
+      const float s0 = va ? sacc[0] * kScale : -INFINITY, s1 = va ? sacc[1] * kScale : -INFINITY;
+      const float s2 = vb ? sacc[2] * kScale : -INFINITY, s3 = vb ? sacc[3] * kScale : -INFINITY;
+      float bm0 = fmaxf(s0, s2), bm1 = fmaxf(s1, s3);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, off));
+        bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, off));
+      }
+      const float mn0 = fmaxf(m0, bm0), mn1 = fmaxf(m1, bm1);
+      const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+      const float pr0 = exp2f(s0 - mn0), pr1 = exp2f(s1 - mn1), pr2 = exp2f(s2 - mn0), pr3 = exp2f(s3 - mn1);
+      float ls0 = pr0 + pr2, ls1 = pr1 + pr3;
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        ls0 += __shfl_xor_sync(0xffffffffu, ls0, off);
+        ls1 += __shfl_xor_sync(0xffffffffu, ls1, off);
+      }
+      m0 = mn0;
+      m1 = mn1;
+      l0 = l0 * c0 + ls0;
+      l1 = l1 * c1 + ls1;
+#pragma unroll
+      for (int T = 0; T < 16; ++T) {
+        o[T][0] *= c0;
+        o[T][1] *= c1;
+        o[T][2] *= c0;
+        o[T][3] *= c1;
+      }
+      // ---- O^T += V^T P^T ----
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        const float vsa = __half2float(Vsc[g * 4 + grp]), vsb = __half2float(Vsc[(g + 8) * 4 + grp]);
+        const __half2 pa = __floats2half2_rn(pr0 * vsa, pr1 * vsa), pb = __floats2half2_rn(pr2 * vsb, pr3 * vsb);
+        const uint32_t b0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&pa));
+        const uint32_t b1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&pb));
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int J = 2 * grp + jj;
+          const uint8_t* vp = Vs + 32 * J + 4 * g;
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vp + (2 * t) * kHd) ^ 0x80808080u;
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 1) * kHd) ^ 0x80808080u;
+          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 8) * kHd) ^ 0x80808080u;
+          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 9) * kHd) ^ 0x80808080u;
+          mma_f16_16816(o[2 * J], byte_pair_to_half2<0>(w0, w1), byte_pair_to_half2<1>(w0, w1),
+                        byte_pair_to_half2<0>(w2, w3), byte_pair_to_half2<1>(w2, w3), b0, b1);
+          mma_f16_16816(o[2 * J + 1], byte_pair_to_half2<2>(w0, w1), byte_pair_to_half2<3>(w0, w1),
+                        byte_pair_to_half2<2>(w2, w3), byte_pair_to_half2<3>(w2, w3), b0, b1);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+
+  // ---- merge the four warps (shared memory aliases the drained stages) ----
+  named_bar_sync(1, kMmaWarps * 32);
+  float* sm_acc = reinterpret_cast<float*>(dsm);                       // [warp][8 heads][256]
+  float* sm_ml = sm_acc + kMmaWarps * 8 * kHd;                         // [warp][8 heads][2]
+#pragma unroll
+  for (int T = 0; T < 16; ++T)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int dim = 32 * (T >> 1) + 4 * g + 2 * (T & 1) + (c >> 1);
+      const int head = 2 * t + (c & 1);
+      sm_acc[((size_t)warp * 8 + head) * kHd + dim] = o[T][c];
+    }
+  if (g == 0) {
+    sm_ml[(warp * 8 + 2 * t) * 2] = m0;
+    sm_ml[(warp * 8 + 2 * t) * 2 + 1] = l0;
+    sm_ml[(warp * 8 + 2 * t + 1) * 2] = m1;
+    sm_ml[(warp * 8 + 2 * t + 1) * 2 + 1] = l1;
+  }
+  named_bar_sync(1, kMmaWarps * 32);
+  for (int idx = tid; idx < group * kHd; idx += kMmaWarps * 32) {
+    const int h = idx / kHd, d = idx % kHd;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) mm = fmaxf(mm, sm_ml[(w * 8 + h) * 2]);
+    float ll = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) {
+      const float mw = sm_ml[(w * 8 + h) * 2];
+      const float c = mw == -INFINITY ? 0.0f : exp2f(mw - mm);
+      ll += sm_ml[(w * 8 + h) * 2 + 1] * c;
+      acc += sm_acc[((size_t)w * 8 + h) * kHd + d] * c;
+    }
+    const int qh = kvh * group + h;
+    if (num_splits == 1) {
+      const float gt = __bfloat162float(gate[(size_t)m * ld_gate + (size_t)qh * kHd + d]);
+      out[(size_t)m * nq * kHd + (size_t)qh * kHd + d] = __float2bfloat16_rn(acc / ll * sigmoid_f(gt));
+    } else {
+      float* dst = scratch + (((size_t)row * nq + qh) * max_splits + split) * (kHd + 2);
+      dst[d] = acc;
+      if (d == 0) {
+        dst[kHd] = mm;
+        dst[kHd + 1] = ll;
+      }
+    }
+  }
+}
+
 // Merge of the splits + normalisation + sigmoid gate -> bf16 (reference attention_decode.cu:241-257).
 __global__ void __launch_bounds__(kHd) attn_merge_kernel(const float* __restrict__ scratch, int max_splits,
                                                          int num_splits, const __nv_bfloat16* __restrict__ gate,
@@ -422,7 +681,26 @@ extern "C" int q38_attention_decode(const q38_attention_params* p, const q38_bat
   Q38_REQUIRE(batch->num_tokens == batch->num_seqs, "attention_decode: one token per sequence expected");
   int splits = q38_attention_decode_splits(batch->num_seqs, p->num_kv_heads, num_sms(), p->max_splits);
   if (!p->split_scratch) splits = 1;
-  return dispatch_group(p->num_q_heads / p->num_kv_heads, *p, *batch, *kv, true, splits, as_stream(stream));
+  const int group = p->num_q_heads / p->num_kv_heads;
+  if (kv->dtype != Q38_KV_INT8) return dispatch_group(group, *p, *batch, *kv, true, splits, as_stream(stream));
+  Q38_REQUIRE(group >= 1 && group <= 8, "attention: GQA group %d is not implemented (1..8)", group);
+  static const cudaError_t attr =
+      cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+  Q38_CUDA_OK(attr);
+  const cudaStream_t s = as_stream(stream);
+  const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p->gate);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p->out);
+  attn_decode_mma_kernel<<<dim3(splits, p->num_kv_heads, batch->num_seqs), kMmaThreads, kMmaSmem, s>>>(
+      reinterpret_cast<const __half*>(p->q), gate, p->ld_gate, out, p->num_q_heads, group, p->attn_layer,
+      p->split_scratch, p->max_splits, splits, batch->seq_start, batch->seq_slot, batch->seq_pos0, make_view(*kv));
+  Q38_LAUNCH_OK("attn_decode_mma_kernel");
+  if (splits > 1) {
+    attn_merge_kernel<<<dim3(p->num_q_heads, batch->num_seqs), kHd, 0, s>>>(p->split_scratch, p->max_splits, splits, gate,
+                                                                           p->ld_gate, out, p->num_q_heads,
+                                                                           batch->seq_start);
+    Q38_LAUNCH_OK("attn_merge_kernel");
+  }
+  return Q38_OK;
 }
 
 extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_batch_desc* batch,

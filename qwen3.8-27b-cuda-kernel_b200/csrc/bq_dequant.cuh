@@ -27,18 +27,13 @@ struct BqGeom {
 __device__ __forceinline__ uint32_t bf16x2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 bits_bf16x2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
-// Right / left shifts by a compile-time amount issued as integer multiplies: on this architecture the
-// multiplier shares the fp32 pipe, while shifts and logic ops compete for the half-rate integer pipe that
-// bounds the decoder (measured: integer pipe ~50 % busy at 30 % of HBM bandwidth with plain shifts).
 template <int SH>
 __device__ __forceinline__ uint32_t shr_mul(uint32_t x) {
-  if constexpr (SH == 0) return x;
-  else return __umulhi(x, 1u << (32 - SH));
+  return x >> SH;
 }
 template <int SH>
 __device__ __forceinline__ uint32_t shl_mul(uint32_t x) {
-  if constexpr (SH == 0) return x;
-  else return x * (1u << SH);
+  return x << SH;
 }
 
 template <int BITS, int Q>

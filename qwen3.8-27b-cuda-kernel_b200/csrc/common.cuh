@@ -121,6 +121,24 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Folded-RMSNorm row scales rs[t] = rsqrt(sum_b partials[t][b] / hidden + eps) for t < rows, written to
+// shared memory by `nthreads` cooperating threads (thread index `tix`): eight lanes share a token so that all of a
+// token's partials are requested in one round trip to L2. Call from whole warps only.
+__device__ __forceinline__ void row_scales_to_smem(const float* __restrict__ partials, int rows, int cap, int hidden,
+                                                   float eps, float* rs_sm, int tix, int nthreads) {
+  const int blocks = hidden / 128;
+  for (int base = 0; base < cap; base += nthreads / 8) {
+    const int t = base + tix / 8, sub = tix & 7;
+    float sum = 0.0f;
+    if (partials && t < rows)
+      for (int b = sub; b < blocks; b += 8) sum += partials[(size_t)t * blocks + b];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if (sub == 0 && t < cap) rs_sm[t] = (partials && t < rows) ? 1.0f / sqrtf(sum / float(hidden) + eps) : 1.0f;
+  }
+}
+
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }

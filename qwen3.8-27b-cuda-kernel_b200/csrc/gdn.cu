@@ -14,47 +14,67 @@ constexpr int kDk = 128, kDv = 128;
 
 // ---------------------------------------------------------------------------------------------------
 // gdn_ab: ab[m][j] = rs[m] * sum_k xbf[m][k] * w[j][k]  (fp32; rows j < nv are b, the rest a).
-// One CTA per (8 weight rows, 8 tokens): a warp owns one weight row and keeps 8 token accumulators, so every
-// 16-byte weight load is used 8 times; both operands stream from L2.
+// One CTA per (8 weight rows, 8 tokens); the 8 warps split K, every lane issues 16 independent 16-byte loads
+// per step (8 weight rows + 8 token rows) for 512 FMAs, and the warps' partial sums meet in shared memory.
 // ---------------------------------------------------------------------------------------------------
-constexpr int kAbTokens = 8;
+constexpr int kAbRows = 8, kAbTokens = 8;
 __global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __restrict__ xbf, int m, int hidden,
                                                      const __nv_bfloat16* __restrict__ w, int rows,
                                                      const float* __restrict__ partials_in, float eps,
                                                      float* __restrict__ ab_out) {
+  __shared__ float red[8][kAbRows * kAbTokens];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int j = blockIdx.x * 8 + warp, m0 = blockIdx.y * kAbTokens;
-  if (j >= rows) return;
-  const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)j * hidden);
-  float acc[kAbTokens];
+  const int j0 = blockIdx.x * kAbRows, m0 = blockIdx.y * kAbTokens;
+  float acc[kAbRows][kAbTokens];
 #pragma unroll
-  for (int t = 0; t < kAbTokens; ++t) acc[t] = 0.0f;
-  for (int c = lane; c < hidden / 8; c += 32) {
-    const uint4 wv = wr[c];
-    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
-    float wf[8];
+  for (int r = 0; r < kAbRows; ++r)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      wf[2 * i] = __low2float(wp[i]);
-      wf[2 * i + 1] = __high2float(wp[i]);
+    for (int t = 0; t < kAbTokens; ++t) acc[r][t] = 0.0f;
+  for (int c = warp * 32 + lane; c < hidden / 8; c += 256) {
+    float wf[kAbRows][8], xf[kAbTokens][8];
+#pragma unroll
+    for (int r = 0; r < kAbRows; ++r) {
+      const int j = min(j0 + r, rows - 1);
+      const uint4 v = reinterpret_cast<const uint4*>(w + (size_t)j * hidden)[c];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        wf[r][2 * i] = __low2float(p[i]);
+        wf[r][2 * i + 1] = __high2float(p[i]);
+      }
     }
 #pragma unroll
     for (int t = 0; t < kAbTokens; ++t) {
-      if (m0 + t < m) {
-        const uint4 xv = reinterpret_cast<const uint4*>(xbf + (size_t)(m0 + t) * hidden)[c];
-        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const int mm = min(m0 + t, m - 1);
+      const uint4 v = reinterpret_cast<const uint4*>(xbf + (size_t)mm * hidden)[c];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[t] += wf[2 * i] * __low2float(xp[i]);
-          acc[t] += wf[2 * i + 1] * __high2float(xp[i]);
-        }
+      for (int i = 0; i < 4; ++i) {
+        xf[t][2 * i] = __low2float(p[i]);
+        xf[t][2 * i + 1] = __high2float(p[i]);
       }
     }
+#pragma unroll
+    for (int r = 0; r < kAbRows; ++r)
+#pragma unroll
+      for (int t = 0; t < kAbTokens; ++t)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[r][t] += wf[r][i] * xf[t][i];
   }
 #pragma unroll
-  for (int t = 0; t < kAbTokens; ++t) {
-    const float total = warp_sum(acc[t]);
-    if (lane == 0 && m0 + t < m) {
+  for (int r = 0; r < kAbRows; ++r)
+#pragma unroll
+    for (int t = 0; t < kAbTokens; ++t) {
+      const float v = warp_sum(acc[r][t]);
+      if (lane == 0) red[warp][r * kAbTokens + t] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < kAbRows * kAbTokens) {
+    const int r = threadIdx.x / kAbTokens, t = threadIdx.x % kAbTokens;
+    if (j0 + r < rows && m0 + t < m) {
+      float total = 0.0f;
+#pragma unroll
+      for (int wi = 0; wi < 8; ++wi) total += red[wi][threadIdx.x];
       float rs = 1.0f;
       if (partials_in) {
         const int blocks = hidden / 128;
@@ -62,7 +82,7 @@ __global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __rest
         for (int b = 0; b < blocks; ++b) sum += partials_in[(size_t)(m0 + t) * blocks + b];
         rs = 1.0f / sqrtf(sum / float(hidden) + eps);
       }
-      ab_out[(size_t)(m0 + t) * rows + j] = total * rs;
+      ab_out[(size_t)(m0 + t) * rows + j0 + r] = total * rs;
     }
   }
 }
@@ -232,7 +252,7 @@ extern "C" int q38_gdn_ab(const q38_bf16* xbf, int m, int hidden, const q38_bf16
   if (m == 0) return Q38_OK;
   Q38_REQUIRE(xbf && w_ab && ab_out, "gdn_ab: null argument");
   Q38_REQUIRE(m > 0 && hidden > 0 && hidden % 128 == 0 && rows > 0, "gdn_ab: m %d hidden %d rows %d", m, hidden, rows);
-  const dim3 grid((rows + 7) / 8, (m + kAbTokens - 1) / kAbTokens);
+  const dim3 grid((rows + kAbRows - 1) / kAbRows, (m + kAbTokens - 1) / kAbTokens);
   gdn_ab_kernel<<<grid, 256, 0, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(xbf), m, hidden,
                                                      reinterpret_cast<const __nv_bfloat16*>(w_ab), rows, partials_in, eps,
                                                      ab_out);

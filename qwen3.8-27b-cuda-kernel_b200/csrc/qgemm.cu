@@ -16,8 +16,8 @@ struct ConfigInfo {
   bool umma;
 };
 constexpr ConfigInfo kConfigs[] = {
-    {"stream_m8", 8, false},   {"stream_m16", 16, false}, {"stream_m32", 32, false}, {"stream_m64", 64, false},
-    {"umma_t32", 32, true},    {"umma_t64", 64, true},    {"umma_t128", 128, true},  {"umma_t256", 256, true},
+    {"stream_m8", 8, false}, {"stream_m16", 16, false}, {"umma_t32", 32, true},
+    {"umma_t64", 64, true},  {"umma_t128", 128, true},  {"umma_t256", 256, true},
 };
 constexpr int kNumConfigs = int(sizeof(kConfigs) / sizeof(kConfigs[0]));
 
@@ -28,10 +28,10 @@ q38_gemm_tuning_lookup g_tuning = nullptr;
 int auto_config(int m) {
   if (m <= 8) return 0;
   if (m <= 16) return 1;
-  if (m <= 32) return 4;
-  if (m <= 64) return 5;
-  if (m <= 128) return 6;
-  return 7;
+  if (m <= 32) return 2;
+  if (m <= 64) return 3;
+  if (m <= 128) return 4;
+  return 5;
 }
 
 // One lane decodes one slab exactly as the GEMM does and writes the 32 weights to W[n][k] (bf16).

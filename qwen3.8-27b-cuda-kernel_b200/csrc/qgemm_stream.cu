@@ -14,10 +14,11 @@
 //     full/empty pairs, one producer warp). Weights carry an L2 evict-first policy: they are read once.
 //   * The activation chunk of a stage arrives through a 2-D tensor map with the 128-byte swizzle, rows
 //     beyond M zero-filled by the TMA unit.
-//   * 8 consumer warps = 2 column blocks x 4 k-groups of a stage. A lane's 16 bytes of a slab are
+//   * 16 consumer warps = 2 column blocks x 8 k-groups of a stage (the decode chain is latency-bound per warp,
+//     so four warps per scheduler are needed to keep the issue slots busy). A lane's 16 bytes of a slab are
 //     decoded in registers (bq_dequant.cuh) and are directly the A fragment (16 columns x 16 k) of
 //     mma.sync.m16n8k16 with the tokens as the 8-wide N operand, so M <= 8 costs 4 MMAs per slab.
-//   * A tile segment ends with a fixed-order reduction of the 4 k-warps into a shared C tile; segments
+//   * A tile segment ends with a fixed-order reduction of the 8 k-warps into a shared C tile; segments
 //     that do not cover all of K go to the workspace and the last-arriving CTA sums them in CTA order
 //     (self-resetting counter): results are bit-reproducible from run to run.
 #include "bq_dequant.cuh"
@@ -29,8 +30,9 @@ namespace q38 {
 namespace {
 
 constexpr int kTileN = 128;
-constexpr int kGroupsPerStage = 4;
-constexpr int kConsumerWarps = 8;
+constexpr int kGroupsPerStage = 8;
+constexpr int kConsumerWarps = 16;
+constexpr int kKWarps = kConsumerWarps / 2;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;
 constexpr int kLdc = 132;  // floats per row of the shared C tile (bank-conflict-free fragment stores)
@@ -50,7 +52,7 @@ struct Cfg {
   static constexpr int kCBytes = kMpad * kLdc * 4;
   static constexpr int kTailBytes = kCBytes + kMpad * 4 + 256;  // C tile, row scales, barriers + flags
   static constexpr int kStagesFit = (kSmemBudget - 1024 - kTailBytes) / kStageBytes;
-  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr int kStages = kStagesFit > 6 ? 6 : kStagesFit;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kTailBytes;
   static_assert(kStages >= 2, "pipeline needs two stages");
 };
@@ -118,58 +120,60 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
     flags[1] = 0;
     mbar_fence_init();
   }
-  // folded-RMSNorm row scales, summed in block order like the oracle (src/ref/ops.cpp:10-14)
-  if (tid < C::kMpad) {
-    float rs = 1.0f;
-    if (a.partials_in && tid < a.m) {
-      const int blocks = a.hidden / 128;
-      float sum = 0.0f;
-      for (int b = 0; b < blocks; ++b) sum += a.partials_in[(size_t)tid * blocks + b];
-      rs = 1.0f / sqrtf(sum / float(a.hidden) + a.eps);
-    }
-    rs_sm[tid] = rs;
-  }
   __syncthreads();
 
   if (warp == kConsumerWarps) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      const uint64_t pol_w = policy_evict_first();
-      uint32_t it = 0;
-      for (long long u = u0; u < u1;) {
-        const int tile = int(u / a.kg), kg_a = int(u % a.kg);
-        const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
-        for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
-          const int s = it % C::kStages;
-          const uint32_t ph = (it / C::kStages) & 1;
-          if (!wait_or_abort(&empty[s], ph ^ 1, flags, 0x101)) break;
-          const int ng = min(kGroupsPerStage, kg_b - g);
-          uint8_t* st = stages + (size_t)s * C::kStageBytes;
-          const uint32_t bytes =
-              uint32_t(ng) * (2u * (G::kLoGroupBytes + G::kHiGroupBytes + G::kScGroupBytes) + C::kXGroup);
-          mbar_expect_tx(&full[s], bytes);
-          for (int gi = 0; gi < ng; ++gi)
-            tma_load_2d(st + C::kXOff + gi * C::kXGroup, &xmap, (g + gi) * 64, 0, &full[s]);
-#pragma unroll
-          for (int nbl = 0; nbl < 2; ++nbl) {
-            const size_t grp = (size_t)(tile * 2 + nbl) * a.kg + g;
+    // Lane 0 waits for the slot and posts the byte count; then each copy of the stage is issued by its own lane.
+    const uint64_t pol_w = policy_evict_first();
+    uint32_t it = 0;
+    bool alive = true;
+    for (long long u = u0; u < u1 && alive;) {
+      const int tile = int(u / a.kg), kg_a = int(u % a.kg);
+      const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+      for (int g = kg_a; g < kg_b && alive; g += kGroupsPerStage, ++it) {
+        const int s = it % C::kStages;
+        const int ng = min(kGroupsPerStage, kg_b - g);
+        int ok = 1;
+        if (lane == 0) {
+          ok = wait_or_abort(&empty[s], ((it / C::kStages) & 1) ^ 1, flags, 0x101) ? 1 : 0;
+          if (ok)
+            mbar_expect_tx(&full[s], uint32_t(ng) * (2u * (G::kLoGroupBytes + G::kHiGroupBytes + G::kScGroupBytes) + C::kXGroup));
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          alive = false;
+          break;
+        }
+        uint8_t* st = stages + (size_t)s * C::kStageBytes;
+        if (lane < ng) {
+          tma_load_2d(st + C::kXOff + lane * C::kXGroup, &xmap, (g + lane) * 64, 0, &full[s]);
+        } else if (lane < ng + 6) {
+          const int op = lane - ng, nbl = op / 3, kind = op % 3;
+          const size_t grp = (size_t)(tile * 2 + nbl) * a.kg + g;
+          if (kind == 0)
             bulk_g2s(st + C::kLoOff + nbl * kGroupsPerStage * G::kLoGroupBytes, a.lo + grp * G::kLoGroupBytes,
                      ng * G::kLoGroupBytes, &full[s], pol_w);
+          else if (kind == 1) {
             if constexpr (BITS != 4)
               bulk_g2s(st + C::kHiOff + nbl * kGroupsPerStage * G::kHiGroupBytes, a.hi + grp * G::kHiGroupBytes,
                        ng * G::kHiGroupBytes, &full[s], pol_w);
+          } else
             bulk_g2s(st + C::kScOff + nbl * kGroupsPerStage * G::kScGroupBytes, a.sc + grp * G::kScGroupBytes,
                      ng * G::kScGroupBytes, &full[s], pol_w);
-          }
         }
-        if (flags[0]) break;
-        u += kg_b - kg_a;
+        __syncwarp();
       }
+      u += kg_b - kg_a;
     }
     return;
   }
 
   // ------------------------------ consumers ------------------------------
+  // row scales of the folded RMSNorm: needed only by the epilogue, so they are fetched while the producer
+  // already fills the ring
+  row_scales_to_smem(a.partials_in, a.m, C::kMpad, a.hidden, a.eps, rs_sm, tid, kConsumers);
+  named_bar_sync(1, kConsumers);
   const int wn = warp & 1, wk = warp >> 1;
   const int gl = lane >> 2, tl = lane & 3;
   uint32_t it = 0;
@@ -187,7 +191,10 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
     for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
       const int s = it % C::kStages;
       const uint32_t ph = (it / C::kStages) & 1;
-      const bool ok = wait_or_abort(&full[s], ph, flags, 0x102);
+      bool ok = wait_or_abort(&full[s], ph, flags, 0x102);
+#ifdef Q38_DBG_NO_COMPUTE
+      ok = false;
+#endif
       if (ok && g + wk < kg_b) {
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
         const int slot = wn * kGroupsPerStage + wk;
@@ -240,9 +247,9 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
       if (lane == 0) mbar_arrive(&empty[s]);
     }
 
-    // ---- fixed-order reduction of the four k-warps into the shared C tile ----
+    // ---- fixed-order reduction of the k-warps into the shared C tile ----
 #pragma unroll 1
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < kKWarps; ++r) {
       if (wk == r) {
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj)
@@ -413,17 +420,12 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
 template <int BITS>
 int launch_bits(int mt, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
                 const q38_gemm_workspace* ws, cudaStream_t s) {
-  switch (mt) {
-    case 1: return launch_one<BITS, 1>(a, m, w, ep, ws, s);
-    case 2: return launch_one<BITS, 2>(a, m, w, ep, ws, s);
-    case 4: return launch_one<BITS, 4>(a, m, w, ep, ws, s);
-    default: return launch_one<BITS, 8>(a, m, w, ep, ws, s);
-  }
+  return mt == 1 ? launch_one<BITS, 1>(a, m, w, ep, ws, s) : launch_one<BITS, 2>(a, m, w, ep, ws, s);
 }
 
 }  // namespace
 
-// m <= 8 * mt. Called by the dispatcher in qgemm.cu.
+// m <= 8 * mt, mt in {1, 2}. Called by the dispatcher in qgemm.cu.
 int qgemm_stream_launch(int mt, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
                         const q38_gemm_workspace* ws, cudaStream_t s) {
   switch (w.bits) {

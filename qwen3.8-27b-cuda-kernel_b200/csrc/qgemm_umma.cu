@@ -170,16 +170,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     flags[1] = 0;
     mbar_fence_init();
   }
-  if (tid < TOK) {
-    float rs = 1.0f;
-    if (a.partials_in && tid < a.m) {
-      const int blocks = a.hidden / 128;
-      float sum = 0.0f;
-      for (int b = 0; b < blocks; ++b) sum += a.partials_in[(size_t)tid * blocks + b];
-      rs = 1.0f / sqrtf(sum / float(a.hidden) + a.eps);
-    }
-    rs_sm[tid] = rs;
-  }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -265,6 +255,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     const int quarter = warp & 3;      // TMEM lanes this warp may read
     const int col_half = dw >> 2;      // which half of the token columns it handles in the epilogue
     const int et = tid - 64;           // 0..255 among the decode threads
+    row_scales_to_smem(a.partials_in, a.m, TOK, a.hidden, a.eps, rs_sm, et, kDecodeThreads);
+    named_bar_sync(1, kDecodeThreads);
     uint32_t it = 0, slice_ctr = 0, seg = 0;
     for (long long u = u0; u < u1; ++seg) {
       const int tile = int(u / a.kg), kg_a = int(u % a.kg);

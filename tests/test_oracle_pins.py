@@ -112,8 +112,7 @@ def test_oracle_model_reproduces_reference_logits_and_tokens(tag):
         seq = model.new_sequence()
         full = np.concatenate([prompt, gen])
         logits = model.forward(seq, full, all_logits=True)
-        assert np.array_equal(logits[-8:], gold[f"logits_last{tag}{i}"])
-        assert np.array_equal(logits.astype(np.float16), gold[f"logits{tag}{i}"])
+        assert np.array_equal(logits, gold[f"logits{tag}{i}"])
         for j, t in enumerate(gen):
             assert greedy(logits[len(prompt) - 1 + j]) == int(t)
 
