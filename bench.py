@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--max-context", type=int, default=8192 + 512 + 1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=3)
+    ap.add_argument("--skip-prefill", action="store_true",
+                    help="profiling aid: reserve the KV pages but leave them zero-filled (the line is then not a bench value)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -287,7 +289,7 @@ def main():
     for s in range(B):
         runner.reset_slot(s)
         assert runner.kv_ensure(s, int(ctx[s]) + args.steps + args.warmup + 8 + args.profile_steps)
-    todo = [[s, 0] for s in range(B)]
+    todo = [] if args.skip_prefill else [[s, 0] for s in range(B)]
     prefill_tokens, prefill_ms = 0, 0.0
     while todo:
         rows, budget = [], 512
@@ -380,7 +382,7 @@ def main():
         "clocks": clock_summary, "roofline": roofline,
         "step_bytes_algorithmic": step_bytes, "step_hbm_frac": step_bytes / (core_s / args.steps) / 1e9 / peak,
         "prefill_tok_per_s": prefill_tokens / max(prefill_ms, 1e-3) * 1000.0,
-        "context_tokens_per_gpu": int(sum(pos)),
+        "context_tokens_per_gpu": int(sum(pos)), "state": "unfilled (profiling run)" if args.skip_prefill else "prefilled",
         "per_op_ms": {k: round(v, 4) for k, v in sorted(per_step.items())},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
