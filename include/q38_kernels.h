@@ -108,6 +108,13 @@ int q38_qgemm_config_tile_m(int config);
 /* C[M][N] = A[M][K] * W^T; A bf16 row-major with leading dimension K. (kernels::qgemm, kernels.h:120-121) */
 int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep,
               const q38_gemm_workspace* ws, void* stream, int config);
+/* The same GEMM for callers that cannot allocate device memory (no counterpart in the reference, whose launcher
+ * always receives a caller-owned GemmWorkspace). The stream-K workspace is a fixed array inside the library
+ * (about 3.2 MB of device memory per GPU that loads it). Limits: 1 <= m <= 16, n <= 524288, at most 192 SMs;
+ * anything larger is rejected with Q38_ERR_INVALID. The first call on a device looks the array's address up
+ * (cudaGetSymbolAddress) and should therefore be made before any stream capture starts. Every call on a device
+ * uses the same array: calls that may overlap on the GPU must be serialised by the caller. Allocates nothing. */
+int q38_qgemm_static(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep, void* stream);
 typedef int (*q38_gemm_tuning_lookup)(int bits, int n, int k, int m);
 void q38_set_qgemm_tuning(q38_gemm_tuning_lookup lookup); /* kernels::set_qgemm_tuning, kernels.h:124-125 */
 

@@ -109,6 +109,7 @@ KERNEL_API = {
     "q38_qgemm_config_tile_m": (C.c_int, [C.c_int]),
     "q38_qgemm": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(BQWeight), C.POINTER(GemmEpilogue),
                             C.POINTER(GemmWorkspace), C.c_void_p, C.c_int]),
+    "q38_qgemm_static": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(BQWeight), C.POINTER(GemmEpilogue), C.c_void_p]),
     "q38_set_qgemm_tuning": (None, [C.c_void_p]),
     "q38_bq_dequant": (C.c_int, [C.POINTER(BQWeight), C.c_void_p, C.c_void_p]),
     "q38_embed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

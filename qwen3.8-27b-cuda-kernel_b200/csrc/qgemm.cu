@@ -137,6 +137,71 @@ extern "C" int q38_bq_dequant(const q38_bq_weight* w, q38_bf16* out, void* strea
   return Q38_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// q38_qgemm_static: the decode GEMM for callers that cannot allocate device memory.
+//
+// q38_qgemm needs a caller-provided stream-K workspace (partial tiles + arrival counters). Some hosts have no
+// way to provide one: a plugin that is only handed its input and output buffers, a runtime whose memory pool is
+// closed once serving starts, code running inside a region where cudaMalloc is forbidden. For them the workspace
+// lives in this library as a fixed array in device memory (about 3.2 MB, held by every GPU that loads the library
+// until the process exits). Limits that follow from the fixed size: m <= 16 tokens (the streaming kernel),
+// n <= 128 * kStaticCounters columns, and a GPU with at most kStaticCtas SMs. All calls on a device share the one
+// array: calls that overlap on the GPU (different streams, or graphs replayed concurrently) race on it and
+// must be serialised by the caller. The arrival counters have to be zero when a launch starts, so every call
+// clears them on `stream` first (a memset node, no allocation).
+// ---------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kStaticCtas = 192;        // persistent CTAs (= SMs) the partial-tile area is sized for
+constexpr int kStaticM = 16;            // largest token count served
+constexpr int kStaticCounters = 4096;   // 128-column tiles: n <= 524288
+constexpr size_t kStaticPartialFloats = size_t(kStaticCtas) * 2 * kStaticM * 128;
+
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+static __device__ __align__(256) int g_static_counters[kStaticCounters];
+
+struct StaticWs {
+  float* partials = nullptr;
+  int* counters = nullptr;
+};
+constexpr int kMaxDevices = 64;
+StaticWs g_static_ws[kMaxDevices];
+
+// The array names above are host-side stand-ins; the device addresses come from cudaGetSymbolAddress, looked up
+// once per device with that device current.
+int static_ws_for_current_device(StaticWs* out) {
+  int dev = 0;
+  Q38_CUDA_OK(cudaGetDevice(&dev));
+  Q38_REQUIRE(dev >= 0 && dev < kMaxDevices, "qgemm_static: device index %d out of range", dev);
+  StaticWs& ws = g_static_ws[dev];
+  if (ws.partials == nullptr) {
+    float* p = nullptr;
+    int* c = nullptr;
+    Q38_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials));
+    Q38_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&c), g_static_counters));
+    ws.counters = c;
+    ws.partials = p;
+  }
+  *out = ws;
+  return Q38_OK;
+}
+}  // namespace
+
+extern "C" int q38_qgemm_static(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep,
+                                void* stream) {
+  Q38_REQUIRE(a && w && ep, "qgemm_static: null argument");
+  Q38_REQUIRE(m > 0 && m <= kStaticM, "qgemm_static: m = %d is outside the built-in workspace (1..%d tokens)", m,
+              kStaticM);
+  Q38_REQUIRE(w->n > 0 && w->n / 128 <= kStaticCounters, "qgemm_static: n = %d exceeds the built-in workspace (%d columns)",
+              w->n, 128 * kStaticCounters);
+  Q38_REQUIRE(num_sms() <= kStaticCtas, "qgemm_static: %d SMs exceed the built-in workspace (%d)", num_sms(), kStaticCtas);
+  StaticWs sws;
+  const int rc = static_ws_for_current_device(&sws);
+  if (rc != Q38_OK) return rc;
+  Q38_CUDA_OK(cudaMemsetAsync(sws.counters, 0, sizeof(int) * kStaticCounters, as_stream(stream)));
+  const q38_gemm_workspace ws{sws.partials, kStaticPartialFloats, sws.counters, kStaticCounters};
+  return q38_qgemm(a, m, w, ep, &ws, stream, Q38_GEMM_CONFIG_AUTO);
+}
+
 namespace q38 {
 unsigned int qgemm_dispatch_error(bool clear) { return read_tu_error(clear); }
 }
