@@ -8,7 +8,7 @@
 
 namespace q38 {
 
-// Weight-streaming kernel for m <= 8 * mt, mt in {1, 2, 4, 8} (qgemm_stream.cu).
+// Weight-streaming kernel for m <= 8 * mt, mt in {1, 2} (qgemm_stream.cu).
 int qgemm_stream_launch(int mt, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
                         const q38_gemm_workspace* ws, cudaStream_t s);
 unsigned int qgemm_stream_error(bool clear);

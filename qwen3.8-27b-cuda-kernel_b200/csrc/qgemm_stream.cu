@@ -1,4 +1,4 @@
-// Decode-sized BQ GEMM (M <= 64): a weight-streaming kernel bound by HBM bandwidth.
+// Decode-sized BQ GEMM (M <= 16 tokens per pass): a weight-streaming kernel.
 //
 //   C[M][N] = A[M][K] (bf16) * W^T, W in BQ 4/5/6/8-bit planes; fused epilogues StoreBF16 / SwiGLU /
 //   Residual (+ bf16 copy + next-norm partial sums) / StoreF32 with the folded-RMSNorm row scale.
@@ -191,10 +191,7 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
     for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
       const int s = it % C::kStages;
       const uint32_t ph = (it / C::kStages) & 1;
-      bool ok = wait_or_abort(&full[s], ph, flags, 0x102);
-#ifdef Q38_DBG_NO_COMPUTE
-      ok = false;
-#endif
+      const bool ok = wait_or_abort(&full[s], ph, flags, 0x102);
       if (ok && g + wk < kg_b) {
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
         const int slot = wn * kGroupsPerStage + wk;

@@ -4,15 +4,22 @@
 //
 // Orientation: the weights are the MMA's A operand (M_mma = 128 output columns = two 64-column BQ blocks),
 // the tokens are its N operand (N_mma = 32..256), so any token count fills the 128 TMEM lanes.
-// Warp roles of a CTA (one CTA per SM, persistent over a stream-K work list of (tile, 64-wide k-group)):
-//   warp 0      producer: 1-D bulk (TMA) copies of the raw BQ planes (contiguous per 64-column block) and
-//               2-D tensor-map loads of the activation k-slices (128-byte swizzle, rows >= M zero-filled)
-//               into a ring of stages (128 k each);
-//   warps 2-9   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> stored to
-//               the K-major, 128-byte-swizzled shared tile a UMMA descriptor reads (bank-conflict-free 4-byte
-//               stores); afterwards the same warps run the epilogue out of TMEM (tcgen05.ld);
-//   warp 1      one elected thread issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32) per 16-wide k step and
-//               tcgen05.commit to hand slices / stages / the accumulator back.
+// One persistent CTA per SM walks a stream-K work list of (tile, 64-wide k-group). Three independent rings:
+//   raw ring     the BQ planes of 4 k-groups per stage (contiguous per 64-column block: 1-D bulk copies, L2
+//                evict-first). It is as deep as shared memory allows (about 100 KB in flight per SM), because the
+//                achieved HBM rate of this kernel is set by the bytes in flight;
+//   x ring       one activation k-slice [TOK][64] bf16 per slot (2-D tensor map, 128-byte swizzle, rows >= M
+//                zero-filled), L2-resident, so a few slots suffice;
+//   slice ring   decoded bf16 operand slices [128 n][64 k] in the K-major 128-byte-swizzled layout a UMMA
+//                descriptor reads.
+// Warp roles:
+//   warp 0       raw producer (six copies per stage, one lane each);
+//   warp 1       one elected thread issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32) per 16-wide k step and
+//                tcgen05.commit to hand slices / x slots / the accumulator back;
+//   warp 2       activation producer;  warp 3 idle (keeps the decode warps aligned to the TMEM lane quarters);
+//   warps 4-19   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> 4-byte
+//                bank-conflict-free stores into a slice; 8 warps fill one slice, two slices per pass. The same
+//                warps run the epilogue out of TMEM (tcgen05.ld).
 // Partial tiles (stream-K) go through the caller's workspace; the last-arriving CTA sums them in CTA order, so
 // results are bit-reproducible. Every wait is bounded; TMEM is always released before the kernel ends.
 #include <algorithm>
@@ -26,30 +33,38 @@ namespace q38 {
 namespace {
 
 constexpr int kTileN = 128;
-constexpr int kGroupsPerStage = 2;
-constexpr int kDecodeWarps = 8;
+constexpr int kGroupsPerStage = 4;
+constexpr int kDecodeWarps = 16;
+constexpr int kFirstDecodeWarp = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
+constexpr int kWarpsPerSlice = 8;
 constexpr int kSliceBytes = kTileN * 128;  // one [128 n][64 k] bf16 operand slice
-constexpr int kSmemBudget = 225 * 1024;
+constexpr int kSmemBudget = 226 * 1024;
 
 template <int BITS, int TOK>
 struct UCfg {
   using G = BqGeom<BITS>;
-  static constexpr int kXGroup = TOK * 128;
-  static constexpr int kXOff = 0;
-  static constexpr int kLoOff = kXOff + kGroupsPerStage * kXGroup;
+  // operand unit: what one barrier round trip hands to the MMA thread = kSpu decoded slices + their activations
+  static constexpr int kSpu = TOK <= 128 ? 2 : 1;
+  static constexpr int kUnits = TOK <= 64 ? 3 : TOK <= 128 ? 2 : 3;
+  static constexpr int kXBytes = TOK * 128;  // activation k-slice [TOK][64] bf16
+  static constexpr int kUnitBytes = kSpu * (kSliceBytes + kXBytes);
+  static constexpr int kLoOff = 0;
   static constexpr int kHiOff = kLoOff + 2 * kGroupsPerStage * G::kLoGroupBytes;
   static constexpr int kScOff = kHiOff + 2 * kGroupsPerStage * G::kHiGroupBytes;
-  static constexpr int kStageRaw = kScOff + 2 * kGroupsPerStage * G::kScGroupBytes;
-  static constexpr int kStageBytes = (kStageRaw + 1023) / 1024 * 1024;
-  static constexpr int kTail = TOK * 4 + TOK * 4 * 4 + 512;  // row scales, per-quarter partial sums, barriers
-  static constexpr int kFit4 = (kSmemBudget - 1024 - kTail - 4 * kSliceBytes) / kStageBytes;
-  static constexpr int kStages = kFit4 >= 2 ? (kFit4 > 6 ? 6 : kFit4) : 2;
-  static constexpr int kSlices = kFit4 >= 2 ? 4 : (kSmemBudget - 1024 - kTail - 2 * kStageBytes) / kSliceBytes;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kSlices * kSliceBytes + kTail;
+  static constexpr int kStageBytes = kScOff + 2 * kGroupsPerStage * G::kScGroupBytes;  // a multiple of 1024
+  static constexpr int kTail = TOK * 4 + TOK * 4 * 4 + 1024;  // row scales, per-quarter partial sums, barriers
+  static constexpr int kFit = (kSmemBudget - 1024 - kTail - kUnits * kUnitBytes) / kStageBytes;
+  static constexpr int kStages = kFit > 8 ? 8 : kFit;
+  static constexpr int kUnitOff = kStages * kStageBytes;
+  static constexpr int kTailOff = kUnitOff + kUnits * kUnitBytes;
+  static constexpr int kSmemBytes = 1024 + kTailOff + kTail;
   static constexpr int kTmemCols = TOK < 32 ? 32 : TOK;
-  static_assert(kSlices >= 2, "operand slice ring needs two slots");
+  static constexpr int kEpiChunks = TOK >= 64 ? 4 : 2;  // decode warps per TMEM lane quarter that run the epilogue
+  static constexpr int kColsPerWarp = TOK / kEpiChunks;
+  static_assert(kStageBytes % 1024 == 0, "x slots and slices need 1024-byte alignment");
+  static_assert(kStages >= 2, "raw ring needs two stages");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
@@ -80,9 +95,15 @@ __device__ __forceinline__ long long u_begin(const UmmaArgs& a, int cta, int gri
   return ((long long)cta * a.tiles / grid) * a.kg;
 }
 
+// Bounded wait that also gives up once another thread of the CTA has given up (the flag is polled only on the slow
+// path, so a wait that is already satisfied costs one try_wait).
 __device__ __forceinline__ bool wait_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned site) {
-  if (*abort_flag) return false;
-  if (mbar_wait(bar, parity, site)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  report_error(site);
   *abort_flag = 1;
   return false;
 }
@@ -139,17 +160,18 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   uint8_t* stages = smem;
-  uint8_t* slices = smem + C::kStages * C::kStageBytes;
-  float* rs_sm = reinterpret_cast<float*>(slices + C::kSlices * kSliceBytes);
+  uint8_t* units = smem + C::kUnitOff;  // per unit: kSpu decoded slices, then kSpu activation slices
+  float* rs_sm = reinterpret_cast<float*>(smem + C::kTailOff);
   float* part_sm = rs_sm + TOK;  // [TOK][4]
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(part_sm + TOK * 4);
   uint64_t* raw_empty = raw_full + C::kStages;
-  uint64_t* a_full = raw_empty + C::kStages;
-  uint64_t* a_empty = a_full + C::kSlices;
-  uint64_t* acc_full = a_empty + C::kSlices;
+  uint64_t* op_full = raw_empty + C::kStages;
+  uint64_t* op_empty = op_full + C::kUnits;
+  uint64_t* acc_full = op_empty + C::kUnits;
   uint64_t* acc_empty = acc_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort, [1] last arriver
+  static_assert((2 * C::kStages + 2 * C::kUnits + 2) * 8 + 16 <= 1024, "barrier area");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grid = gridDim.x, cta = blockIdx.x;
@@ -158,11 +180,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   if (tid == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], kDecodeWarps + 1);
+      mbar_init(&raw_empty[s], kDecodeWarps);
     }
-    for (int s = 0; s < C::kSlices; ++s) {
-      mbar_init(&a_full[s], 4);
-      mbar_init(&a_empty[s], 1);
+    for (int s = 0; s < C::kUnits; ++s) {
+      mbar_init(&op_full[s], kWarpsPerSlice * C::kSpu + 1);  // decode warps + the activation copies' expect_tx
+      mbar_init(&op_empty[s], 1);
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, kDecodeWarps);
@@ -177,42 +199,75 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      const uint64_t pol_w = policy_evict_first();
-      uint32_t it = 0;
-      for (long long u = u0; u < u1 && !flags[0];) {
-        const int tile = int(u / a.kg), kg_a = int(u % a.kg);
-        const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
-        for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
-          const int s = it % C::kStages;
-          if (!wait_flag(&raw_empty[s], ((it / C::kStages) & 1) ^ 1, flags, 0x301)) break;
-          const int ng = min(kGroupsPerStage, kg_b - g);
-          uint8_t* st = stages + (size_t)s * C::kStageBytes;
-          mbar_expect_tx(&raw_full[s], uint32_t(ng) * (2u * (G::kLoGroupBytes + G::kHiGroupBytes + G::kScGroupBytes) +
-                                                       C::kXGroup));
-          for (int gi = 0; gi < ng; ++gi)
-            tma_load_2d(st + C::kXOff + gi * C::kXGroup, &xmap, (g + gi) * 64, 0, &raw_full[s]);
-#pragma unroll
-          for (int nbl = 0; nbl < 2; ++nbl) {
-            const size_t grp = (size_t)(tile * 2 + nbl) * a.kg + g;
+    // ------------------------------ raw-plane producer ------------------------------
+    // Lane 0 waits for the slot and posts the byte count; then each copy of the stage is issued by its own lane.
+    const uint64_t pol_w = policy_evict_first();
+    uint32_t it = 0;
+    bool alive = true;
+    for (long long u = u0; u < u1 && alive;) {
+      const int tile = int(u / a.kg), kg_a = int(u % a.kg);
+      const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+      for (int g = kg_a; g < kg_b && alive; g += kGroupsPerStage, ++it) {
+        const int s = it % C::kStages;
+        const int ng = min(kGroupsPerStage, kg_b - g);
+        int ok = 1;
+        if (lane == 0) {
+          ok = wait_flag(&raw_empty[s], ((it / C::kStages) & 1) ^ 1, flags, 0x301) ? 1 : 0;
+          if (ok)
+            mbar_expect_tx(&raw_full[s], uint32_t(ng) * 2u * (G::kLoGroupBytes + G::kHiGroupBytes + G::kScGroupBytes));
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          alive = false;
+          break;
+        }
+        uint8_t* st = stages + (size_t)s * C::kStageBytes;
+        if (lane < 6) {
+          const int nbl = lane / 3, kind = lane % 3;
+          const size_t grp = (size_t)(tile * 2 + nbl) * a.kg + g;
+          if (kind == 0)
             bulk_g2s(st + C::kLoOff + nbl * kGroupsPerStage * G::kLoGroupBytes, a.lo + grp * G::kLoGroupBytes,
                      ng * G::kLoGroupBytes, &raw_full[s], pol_w);
+          else if (kind == 1) {
             if constexpr (BITS != 4)
               bulk_g2s(st + C::kHiOff + nbl * kGroupsPerStage * G::kHiGroupBytes, a.hi + grp * G::kHiGroupBytes,
                        ng * G::kHiGroupBytes, &raw_full[s], pol_w);
+          } else
             bulk_g2s(st + C::kScOff + nbl * kGroupsPerStage * G::kScGroupBytes, a.sc + grp * G::kScGroupBytes,
                      ng * G::kScGroupBytes, &raw_full[s], pol_w);
-          }
+        }
+        __syncwarp();
+      }
+      u += kg_b - kg_a;
+    }
+  } else if (warp == 2) {
+    // ------------------------------ activation producer ------------------------------
+    if (lane == 0) {
+      uint32_t uc = 0;
+      bool alive = true;
+      for (long long u = u0; u < u1 && alive;) {
+        const int kg_a = int(u % a.kg);
+        const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+        for (int g = kg_a; g < kg_b; g += C::kSpu, ++uc) {
+          const int slot = uc % C::kUnits;
+          const int nu = min(C::kSpu, kg_b - g);
+          alive = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x308);
+          if (!alive) break;
+          uint8_t* xs = units + (size_t)slot * C::kUnitBytes + C::kSpu * kSliceBytes;
+          mbar_expect_tx(&op_full[slot], uint32_t(nu) * C::kXBytes);
+          for (int gi = 0; gi < nu; ++gi) tma_load_2d(xs + gi * C::kXBytes, &xmap, (g + gi) * 64, 0, &op_full[slot]);
         }
         u += kg_b - kg_a;
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
+    // One thread; its serial work per unit is one barrier wait, 4 MMAs per slice with precomputed descriptors,
+    // and one commit, because at small TOK the tensor work per slice is shorter than any of those round trips.
     if (lane == 0) {
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TOK >> 3) << 17) | (uint32_t(128 >> 4) << 24);
-      uint32_t it = 0, slice_ctr = 0, seg = 0;
+      const uint64_t desc0 = smem_desc_sw128(smem_u32(units));
+      uint32_t uc = 0, seg = 0;
       bool alive = true;
       for (long long u = u0; u < u1 && alive; ++seg) {
         const int kg_a = int(u % a.kg);
@@ -220,67 +275,73 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         alive = wait_flag(acc_empty, (seg & 1) ^ 1, flags, 0x302);
         tc_fence_after();
         uint32_t accumulate = 0;
-        for (int g = kg_a; g < kg_b && alive; g += kGroupsPerStage, ++it) {
-          const int s = it % C::kStages;
-          alive = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x303);
-          const int ng = min(kGroupsPerStage, kg_b - g);
-          const uint32_t x_addr = smem_u32(stages + (size_t)s * C::kStageBytes + C::kXOff);
-          for (int gi = 0; gi < ng && alive; ++gi, ++slice_ctr) {
-            const int sl = slice_ctr % C::kSlices;
-            alive = wait_flag(&a_full[sl], (slice_ctr / C::kSlices) & 1, flags, 0x304);
-            if (!alive) break;
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(slices + (size_t)sl * kSliceBytes);
+        for (int g = kg_a; g < kg_b && alive; g += C::kSpu, ++uc) {
+          const int slot = uc % C::kUnits;
+          const int nu = min(C::kSpu, kg_b - g);
+          alive = wait_flag(&op_full[slot], (uc / C::kUnits) & 1, flags, 0x303);
+          if (!alive) break;
+          tc_fence_after();
+          const uint64_t da = desc0 + uint64_t((uint32_t(slot) * C::kUnitBytes) >> 4);
+          const uint64_t dx = da + uint64_t((C::kSpu * kSliceBytes) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              umma_bf16(tmem_base, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(x_addr + gi * C::kXGroup + ks * 32),
-                        idesc, accumulate);
-              accumulate = 1;
+          for (int gi = 0; gi < C::kSpu; ++gi) {
+            if (gi < nu) {
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                umma_bf16(tmem_base, da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
+                          dx + uint64_t((gi * C::kXBytes + ks * 32) >> 4), idesc, accumulate);
+                accumulate = 1;
+              }
             }
-            umma_commit(&a_empty[sl]);
           }
-          umma_commit(&raw_empty[s]);
+          umma_commit(&op_empty[slot]);
         }
         umma_commit(acc_full);
         u += kg_b - kg_a;
       }
     }
-  } else {
+  } else if (warp >= kFirstDecodeWarp) {
     // ------------------------------ decode + epilogue warps ------------------------------
-    const int dw = warp - 2;
-    const int dg = dw >> 2;            // k-group of the stage this warp decodes
-    const int dnb = (dw & 3) >> 1;     // 64-column block of the tile
-    const int dks = (dw & 1) * 2;      // first of its two k16 slabs
+    const int dw = warp - kFirstDecodeWarp;
+    const int dgl = dw >> 3;           // which of the two k-groups of a pass this warp decodes
+    const int dnb = (dw >> 2) & 1;     // 64-column block of the tile
+    const int ks = dw & 3;             // its k16 slab of the group
     const int gl = lane >> 2, tl = lane & 3;
-    const int quarter = warp & 3;      // TMEM lanes this warp may read
-    const int col_half = dw >> 2;      // which half of the token columns it handles in the epilogue
-    const int et = tid - 64;           // 0..255 among the decode threads
+    const int quarter = dw & 3;        // TMEM lanes this warp may read (warp index modulo 4)
+    const int cchunk = dw >> 2;        // which chunk of the token columns it handles in the epilogue
+    const bool epi_active = cchunk < C::kEpiChunks;
+    const int et = tid - kFirstDecodeWarp * 32;  // 0..511 among the decode threads
     row_scales_to_smem(a.partials_in, a.m, TOK, a.hidden, a.eps, rs_sm, et, kDecodeThreads);
     named_bar_sync(1, kDecodeThreads);
-    uint32_t it = 0, slice_ctr = 0, seg = 0;
+    // destination of pair (j, h) of slab ks: row 64 dnb + 8 j + gl, 16-byte chunk (2 ks + h) ^ gl
+    const uint32_t row_off = uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
+    const uint32_t c0_off = row_off + (uint32_t((2 * ks) ^ gl) << 4);
+    const uint32_t c1_off = row_off + (uint32_t((2 * ks + 1) ^ gl) << 4);
+    uint32_t it = 0, unit_ctr = 0, seg = 0;
     for (long long u = u0; u < u1; ++seg) {
       const int tile = int(u / a.kg), kg_a = int(u % a.kg);
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
       for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
         const int s = it % C::kStages;
         const int ng = min(kGroupsPerStage, kg_b - g);
-        bool ok = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x305);
-        if (dg < ng) {
-          const uint32_t sc = slice_ctr + dg;
-          const int sl = sc % C::kSlices;
-          ok = ok && wait_flag(&a_empty[sl], ((sc / C::kSlices) & 1) ^ 1, flags, 0x306);
-          if (ok) {
-            const uint8_t* st = stages + (size_t)s * C::kStageBytes;
-            const int slot = dnb * kGroupsPerStage + dg;
-            const uint8_t* lo_g = st + C::kLoOff + slot * G::kLoGroupBytes;
-            const uint8_t* hi_g = st + C::kHiOff + slot * G::kHiGroupBytes;
-            uint32_t s2[8];
-            expand_scales(*reinterpret_cast<const uint4*>(st + C::kScOff + slot * G::kScGroupBytes + 16 * gl), s2);
-            // destination of pair (j, h) of slab ks: row 64 dnb + 8 j + gl, 16-byte chunk (2 ks + h) ^ gl
-            uint8_t* row_a = slices + (size_t)sl * kSliceBytes + uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
+        const bool ok = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x305);
+        const uint8_t* st = stages + (size_t)s * C::kStageBytes;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int ks = dks + e;
+        for (int p = 0; p < kGroupsPerStage / 2; ++p) {
+          const int dg = 2 * p + dgl;                       // this warp's k-group of the stage
+          const int first = C::kSpu == 2 ? 2 * p : dg;      // first k-group of the unit it belongs to
+          if (first < ng) {
+            const uint32_t uc = unit_ctr + uint32_t(C::kSpu == 2 ? p : dg);
+            const int slot = uc % C::kUnits;
+            const bool have = ok && dg < ng;  // an odd tail leaves the second slice of a unit without data
+            uint32_t w[16];
+            if (have) {
+              // the raw bytes do not depend on the operand slot: fetch and decode them before waiting for it
+              const int rslot = dnb * kGroupsPerStage + dg;
+              const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes;
+              const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
+              uint32_t s2[8];
+              expand_scales(*reinterpret_cast<const uint4*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl), s2);
               const uint4 lv = *reinterpret_cast<const uint4*>(lo_g + ks * 512 + lane * 16);
               const uint32_t lo[4] = {lv.x, lv.y, lv.z, lv.w};
               uint32_t hi[4] = {0, 0, 0, 0};
@@ -297,24 +358,25 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                 hi[2] = hv.z;
                 hi[3] = hv.w;
               }
-              uint32_t w[16];
               decode_slab<BITS>(lo, hi, s2, w);
-              uint8_t* c0 = row_a + (uint32_t((2 * ks) ^ gl) << 4);
-              uint8_t* c1 = row_a + (uint32_t((2 * ks + 1) ^ gl) << 4);
+            }
+            const bool free_slot = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x306);
+            if (have && free_slot) {
+              uint8_t* base = units + (size_t)slot * C::kUnitBytes + (C::kSpu == 2 ? dgl : 0) * kSliceBytes;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                *reinterpret_cast<uint32_t*>(c0 + j * 1024) = w[2 * j];
-                *reinterpret_cast<uint32_t*>(c1 + j * 1024) = w[2 * j + 1];
+                *reinterpret_cast<uint32_t*>(base + c0_off + j * 1024) = w[2 * j];
+                *reinterpret_cast<uint32_t*>(base + c1_off + j * 1024) = w[2 * j + 1];
               }
+              fence_async_smem();
             }
-            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&op_full[slot]);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&a_full[sl]);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[s]);
-        slice_ctr += ng;
+        unit_ctr += uint32_t((ng + C::kSpu - 1) / C::kSpu);
       }
 
       // ---- epilogue of this tile segment ----
@@ -324,8 +386,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       const int n_row = 32 * quarter + lane;  // row of the tile this thread reads from TMEM
       const int n_glob = tile * kTileN + n_row;
       const int n_lim = a.n_store > 0 ? a.n_store : a.n;
-      constexpr int kColsPerWarp = TOK / 2;
-      const int col_base = col_half * kColsPerWarp;
+      constexpr int kColsPerWarp = C::kColsPerWarp;
+      const int col_base = cchunk * kColsPerWarp;
       constexpr int kTileFloats = TOK * kTileN;
 
       auto finish_chunk = [&](const float (&v)[16], int col0) {
@@ -364,14 +426,16 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
 
       bool run_epilogue = true;
       if (whole) {
+        if (epi_active) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
-          uint32_t r[16];
-          float v[16];
-          if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
+          for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+            uint32_t r[16];
+            float v[16];
+            if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = got ? __uint_as_float(r[j]) : 0.0f;
-          finish_chunk(v, col_base + c0);
+            for (int j = 0; j < 16; ++j) v[j] = got ? __uint_as_float(r[j]) : 0.0f;
+            finish_chunk(v, col_base + c0);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -379,12 +443,15 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       } else {
         // stream-K: publish this CTA's partial accumulator [token][128 n], then the last arriver reduces
         float* mine = a.ws + ((size_t)cta * 2 + (kg_a != 0 ? 0 : 1)) * kTileFloats;
+        if (epi_active) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
-          uint32_t r[16];
-          if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
+          for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+            uint32_t r[16];
+            if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[(size_t)(col_base + c0 + j) * kTileN + n_row] = got ? __uint_as_float(r[j]) : 0.0f;
+            for (int j = 0; j < 16; ++j)
+              mine[(size_t)(col_base + c0 + j) * kTileN + n_row] = got ? __uint_as_float(r[j]) : 0.0f;
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -405,7 +472,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         }
         named_bar_sync(1, kDecodeThreads);
         run_epilogue = flags[1] != 0;
-        if (run_epilogue) {
+        if (run_epilogue && epi_active) {
           __threadfence();
 #pragma unroll 1
           for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
