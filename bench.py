@@ -291,6 +291,7 @@ def main():
         assert runner.kv_ensure(s, int(ctx[s]) + args.steps + args.warmup + 8 + args.profile_steps)
     todo = [] if args.skip_prefill else [[s, 0] for s in range(B)]
     prefill_tokens, prefill_ms = 0, 0.0
+    prefill_prof, prefill_prof_steps = {}, 0
     while todo:
         rows, budget = [], 512
         for item in list(todo):
@@ -306,6 +307,13 @@ def main():
         runner.prefill(rows)
         prefill_ms += runner.last_step_ms()
         prefill_tokens += 512 - budget
+        # per-op split of the prefill step: a few full 512-token steps in the middle of the run, eager with
+        # CUDA events between kernels (their step times are slightly inflated by the events)
+        if prefill_tokens == 512 * 40:
+            runner.set_profiling(True)
+        elif prefill_tokens == 512 * 44:
+            prefill_prof, prefill_prof_steps = runner.profile(clear=True), 4
+            runner.set_profiling(False)
     torch.cuda.synchronize()
     log(f"bench[{rank}]: prefilled {prefill_tokens} tokens in {time.time() - t0:.1f} s "
         f"({prefill_tokens / max(prefill_ms, 1e-3) * 1000:.0f} tok/s device-timed)")
@@ -384,6 +392,8 @@ def main():
         "prefill_tok_per_s": prefill_tokens / max(prefill_ms, 1e-3) * 1000.0,
         "context_tokens_per_gpu": int(sum(pos)), "state": "unfilled (profiling run)" if args.skip_prefill else "prefilled",
         "per_op_ms": {k: round(v, 4) for k, v in sorted(per_step.items())},
+        "prefill_per_op_ms": {k: round(v[0] / max(1, prefill_prof_steps), 3) for k, v in sorted(prefill_prof.items())
+                              if k != "start"},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         base = cpu_reference_sample(args.recipe)

@@ -36,12 +36,33 @@ __device__ __forceinline__ uint32_t shl_mul(uint32_t x) {
   return x << SH;
 }
 
+// Bit masks of the decoder, handed to the kernels as launch arguments. A three-input logic instruction takes one
+// immediate at most; with the masks as compile-time constants the compiler spends two instructions on
+// (x & nibble) | magic, with the masks in registers (values it cannot see) it spends one.
+struct DecodeConsts {
+  uint32_t nib;     // 0x000F000F
+  uint32_t magic;   // 0x43004300: bf16x2 (128, 128)
+  uint32_t himask;  // 0x00100010 (5 bit) / 0x00300030 (6 bit)
+};
+inline DecodeConsts decode_consts(int bits) { return DecodeConsts{0x000F000Fu, 0x43004300u, bits == 6 ? 0x00300030u : 0x00100010u}; }
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {  // (a & b) | c
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t b, uint32_t c) {  // a | (b & c)
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xF8;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 template <int BITS, int Q>
-__device__ __forceinline__ uint32_t decode_pair(const uint32_t (&lo)[4], const uint32_t (&hi)[4], uint32_t s2) {
+__device__ __forceinline__ uint32_t decode_pair(const uint32_t (&lo)[4], const uint32_t (&hi)[4], uint32_t s2,
+                                                const DecodeConsts& dc) {
   constexpr uint32_t kMagic = 0x43004300u;  // bf16x2 (128, 128)
-  constexpr uint32_t kNib = 0x000F000Fu;
   constexpr int p = Q & 3;
-  uint32_t v = (shr_mul<4 * p>(lo[Q >> 2]) & kNib) | kMagic;
+  uint32_t v = lop3_and_or(shr_mul<4 * p>(lo[Q >> 2]), dc.nib, dc.magic);
   __nv_bfloat162 c;
   if constexpr (BITS == 4) {
     c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43084308u));  // 136
@@ -49,17 +70,17 @@ __device__ __forceinline__ uint32_t decode_pair(const uint32_t (&lo)[4], const u
     uint32_t h;
     if constexpr (Q >= 4) h = shr_mul<Q - 4>(hi[0]);
     else h = shl_mul<4 - Q>(hi[0]);
-    v |= h & 0x00100010u;
+    v = lop3_or_and(v, h, dc.himask);
     c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43104310u));  // 144
   } else if constexpr (BITS == 6) {
     constexpr int r = Q & 7;
     uint32_t h;
     if constexpr (2 * r >= 4) h = shr_mul<2 * r - 4>(hi[Q >> 3]);
     else h = shl_mul<4 - 2 * r>(hi[Q >> 3]);
-    v |= h & 0x00300030u;
+    v = lop3_or_and(v, h, dc.himask);
     c = __hsub2(bits_bf16x2(v), bits_bf16x2(0x43204320u));  // 160
   } else {
-    const uint32_t vh = (shr_mul<4 * p>(hi[Q >> 2]) & kNib) | kMagic;
+    const uint32_t vh = lop3_and_or(shr_mul<4 * p>(hi[Q >> 2]), dc.nib, dc.magic);
     // code = 16 * (hi - 8) + lo, every intermediate is a small integer (exact in bf16)
     const __nv_bfloat162 top = __hsub2(bits_bf16x2(vh), bits_bf16x2(0x43084308u));
     const __nv_bfloat162 low = __hsub2(bits_bf16x2(v), bits_bf16x2(kMagic));
@@ -70,16 +91,17 @@ __device__ __forceinline__ uint32_t decode_pair(const uint32_t (&lo)[4], const u
 
 template <int BITS, int... Q>
 __device__ __forceinline__ void decode_all(const uint32_t (&lo)[4], const uint32_t (&hi)[4], const uint32_t (&s2)[8],
-                                           uint32_t (&w)[16], std::integer_sequence<int, Q...>) {
-  ((w[Q] = decode_pair<BITS, Q>(lo, hi, s2[Q >> 1])), ...);
+                                           uint32_t (&w)[16], const DecodeConsts& dc,
+                                           std::integer_sequence<int, Q...>) {
+  ((w[Q] = decode_pair<BITS, Q>(lo, hi, s2[Q >> 1], dc)), ...);
 }
 
 // lo: the lane's four lo words. hi: the lane's hi words (BqGeom::kHiLaneWords of them are read).
 // s2[j]: the scale of column 8 j + g duplicated into both halves of a bf16x2.
 template <int BITS>
 __device__ __forceinline__ void decode_slab(const uint32_t (&lo)[4], const uint32_t (&hi)[4], const uint32_t (&s2)[8],
-                                            uint32_t (&w)[16]) {
-  decode_all<BITS>(lo, hi, s2, w, std::make_integer_sequence<int, 16>{});
+                                            uint32_t (&w)[16], const DecodeConsts& dc) {
+  decode_all<BITS>(lo, hi, s2, w, dc, std::make_integer_sequence<int, 16>{});
 }
 
 // Expands the lane's eight scales (one 16-byte read: columns 8 j + g, j = 0..7) into duplicated pairs.

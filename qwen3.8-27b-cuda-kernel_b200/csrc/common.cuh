@@ -15,7 +15,7 @@ namespace q38 {
 // Every spin-wait in this library gives up after this many polls, records the site in the error word
 // and lets the kernel run to its end (results of that launch are then meaningless, the context stays
 // usable). The host reads the word through q38_device_error().
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
 // One error word per translation unit; each .cu exports a reader that c_abi.cu sums up.
 static __device__ unsigned int g_tu_error = 0;
@@ -45,14 +45,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One poll of the barrier phase. The hint lets the hardware park the thread for up to about a microsecond while the
+// phase is incomplete (it resumes as soon as the phase completes), so that waiting warps do not take issue slots from
+// the warps that compute.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
       : "memory");
   return ok != 0;
 }

@@ -4,6 +4,8 @@
 // (src/kernels/kernels.h:184-228, src/kernels/gdn.cu). State layouts (reference docs/FORMAT.md 3.2):
 // recurrent fp32 [slot][gdn_layer][v_head][128 dv][128 dk]; conv bf16 [slot][gdn_layer][3][conv_dim],
 // tap 0 oldest.
+#include <algorithm>
+
 #include "common.cuh"
 #include "host_util.h"
 
@@ -239,6 +241,177 @@ __global__ void __launch_bounds__(kRecWarps * 32, 1) gdn_recurrence_kernel(
   for (int r = 0; r < kRowsPerWarp; ++r) *reinterpret_cast<float4*>(S + (size_t)(row0 + r) * kDk + 4 * lane) = st[r];
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// gdn_recurrence for decode batches (every sequence advances by at most one token): the step is a pure
+// stream over the recurrent state (64 KB read + 64 KB written per (sequence, head), a few hundred FMAs per
+// thread), so it is organised around the memory pipeline instead of one CTA per (sequence, head):
+//   * one persistent CTA per SM walks the (sequence, head) items cta, cta + grid, ...;
+//   * a producer warp brings each item's state and its token's q / k / v / z rows into a three-slot
+//     shared-memory ring with 1-D bulk (TMA) copies, so up to three states per SM are in flight while
+//     a fourth is being computed;
+//   * 16 compute warps take the state into registers (a slot is handed back as soon as it has been read),
+//     run exactly the arithmetic of gdn_recurrence_kernel for one token, and write the new state straight
+//     from registers with 16-byte stores.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kDecSlots = 3;
+constexpr int kDecStateBytes = kDv * kDk * 4;
+constexpr int kDecQOff = kDecStateBytes, kDecKOff = kDecQOff + 512, kDecVOff = kDecKOff + 512, kDecZOff = kDecVOff + 512;
+constexpr int kDecSlotBytes = kDecStateBytes + 2048;
+constexpr int kDecTxBytes = kDecStateBytes + 3 * 512 + 256;
+constexpr int kDecSmemBytes = 128 + kDecSlots * kDecSlotBytes + (kDv + kRecWarps) * 4 + 2 * kDecSlots * 8 + 16;
+constexpr int kDecThreads = (kRecWarps + 1) * 32;
+
+__global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
+    const float* __restrict__ qkv, int conv_dim, const float* __restrict__ ab, const float* __restrict__ A,
+    const float* __restrict__ dt_bias, const __nv_bfloat16* __restrict__ z, int ld_z,
+    const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
+    int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+    int num_seqs) {
+  extern __shared__ uint8_t dec_smem_raw[];
+  uint8_t* smem = dec_smem_raw + ((128 - (smem_u32(dec_smem_raw) & 127)) & 127);
+  uint8_t* slots = smem;
+  float* o_sm = reinterpret_cast<float*>(smem + kDecSlots * kDecSlotBytes);
+  float* red = o_sm + kDv;
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + kRecWarps);
+  uint64_t* empty = full + kDecSlots;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kDecSlots);  // [0] compute warps, [1] producer
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int items = num_seqs * nv;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecSlots; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kRecWarps);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kRecWarps) {
+    // ------------------------------ producer ------------------------------
+    const uint64_t pol = policy_evict_first();
+    uint32_t it = 0;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int b = item / nv, vh = item - b * nv;
+      const int m = seq_start[b];
+      if (seq_start[b + 1] <= m) continue;
+      const int slot = it % kDecSlots;
+      int ok = 1;
+      if (lane == 0) {
+        ok = (!abort_flag[0] && mbar_wait(&empty[slot], ((it / kDecSlots) & 1) ^ 1, 0x401)) ? 1 : 0;
+        if (ok) mbar_expect_tx(&full[slot], kDecTxBytes);
+        else abort_flag[1] = 1;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      uint8_t* dst = slots + (size_t)slot * kDecSlotBytes;
+      const float* S = recurrent + (((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv * kDk;
+      const float* row = qkv + (size_t)m * conv_dim;
+      const int kh = vh / (nv / nk);
+      if (lane < 4)
+        bulk_g2s(dst + lane * (kDecStateBytes / 4), reinterpret_cast<const uint8_t*>(S) + lane * (kDecStateBytes / 4),
+                 kDecStateBytes / 4, &full[slot], pol);
+      else if (lane == 4)
+        bulk_g2s(dst + kDecQOff, row + (size_t)kh * kDk, 512, &full[slot], pol);
+      else if (lane == 5)
+        bulk_g2s(dst + kDecKOff, row + (size_t)nk * kDk + (size_t)kh * kDk, 512, &full[slot], pol);
+      else if (lane == 6)
+        bulk_g2s(dst + kDecVOff, row + (size_t)2 * nk * kDk + (size_t)vh * kDv, 512, &full[slot], pol);
+      else if (lane == 7)
+        bulk_g2s(dst + kDecZOff, z + (size_t)m * ld_z + (size_t)vh * kDv, 256, &full[slot], pol);
+      __syncwarp();
+      ++it;
+    }
+    return;
+  }
+
+  // ------------------------------ compute warps ------------------------------
+  const int row0 = warp * kRowsPerWarp;
+  const int tid = threadIdx.x;
+  uint32_t it = 0;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int b = item / nv, vh = item - b * nv;
+    const int m = seq_start[b];
+    if (seq_start[b + 1] <= m) continue;
+    const int slot = it % kDecSlots;
+    // scalars of this (token, head): requested before the wait so that their latency hides behind it
+    const float bb = ab[(size_t)m * 2 * nv + vh], aa = ab[(size_t)m * 2 * nv + nv + vh];
+    const float a_h = A[vh], dt_h = dt_bias[vh];
+    const float nw = tid < kDv ? norm_w[tid] : 0.0f;
+    float* S = recurrent + (((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv * kDk;
+    // a wait that runs out marks the launch as failed; the warps leave the loop together below
+    const bool ok = mbar_wait(&full[slot], (it / kDecSlots) & 1, 0x402);
+    if (!ok) abort_flag[0] = 1;
+    const uint8_t* src = slots + (size_t)slot * kDecSlotBytes;
+    float4 st[kRowsPerWarp];
+    float vv[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+      st[r] = *reinterpret_cast<const float4*>(src + (size_t)(row0 + r) * kDk * 4 + 16 * lane);
+      vv[r] = *reinterpret_cast<const float*>(src + kDecVOff + 4 * (row0 + r));
+    }
+    const float4 q4 = *reinterpret_cast<const float4*>(src + kDecQOff + 16 * lane);
+    const float4 k4 = *reinterpret_cast<const float4*>(src + kDecKOff + 16 * lane);
+    const float zz = tid < kDv ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src + kDecZOff + 2 * tid)) : 0.0f;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[slot]);  // everything of the slot is in registers now
+
+    const float beta = 1.0f / (1.0f + expf(-bb));
+    const float xsp = aa + dt_h;
+    const float sp = xsp > 20.0f ? xsp : log1pf(expf(xsp));
+    const float decay = expf(a_h * sp);
+    float ov[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+      float4 sv = st[r];
+      sv.x *= decay;
+      sv.y *= decay;
+      sv.z *= decay;
+      sv.w *= decay;
+      const float kv = warp_sum(sv.x * k4.x + sv.y * k4.y + sv.z * k4.z + sv.w * k4.w);
+      const float delta = beta * (vv[r] - kv);
+      sv.x += delta * k4.x;
+      sv.y += delta * k4.y;
+      sv.z += delta * k4.z;
+      sv.w += delta * k4.w;
+      st[r] = sv;
+      ov[r] = warp_sum(sv.x * q4.x + sv.y * q4.y + sv.z * q4.z + sv.w * q4.w);
+    }
+    if (ok) {
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r)
+        *reinterpret_cast<float4*>(S + (size_t)(row0 + r) * kDk + 4 * lane) = st[r];
+    }
+    // gated RMSNorm over the 128 outputs of the head
+    float ss = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) ss += ov[r] * ov[r];
+    if (lane == 0) red[warp] = ss;
+    if (lane < kRowsPerWarp) {
+      float mine = ov[0];
+#pragma unroll
+      for (int r = 1; r < kRowsPerWarp; ++r)
+        if (lane == r) mine = ov[r];
+      o_sm[row0 + lane] = mine;
+    }
+    named_bar_sync(1, kRecWarps * 32);
+    const int stop = abort_flag[0];  // written only before the barrier above: the same value in every compute warp
+    if (tid < kDv && ok) {
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kRecWarps; ++w) total += red[w];
+      const float r = 1.0f / sqrtf(total / float(kDv) + eps);
+      out[(size_t)m * nv * kDv + (size_t)vh * kDv + tid] = __float2bfloat16_rn(o_sm[tid] * r * nw * silu_f(zz));
+    }
+    named_bar_sync(1, kRecWarps * 32);
+    if (stop) break;
+    ++it;
+  }
+}
+
 }  // namespace
 
 unsigned int gdn_error(bool clear) { return read_tu_error(clear); }
@@ -286,6 +459,21 @@ extern "C" int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_
   Q38_REQUIRE(d->num_k_heads > 0 && d->num_v_heads % d->num_k_heads == 0, "gdn_recurrence: head ratio");
   Q38_REQUIRE(p->qkv && p->ab && p->A && p->dt_bias && p->z && p->norm_w && p->out && st->recurrent,
               "gdn_recurrence: null pointer");
+  if (batch->max_tokens_per_seq == 1) {
+    static const cudaError_t attr = cudaFuncSetAttribute(gdn_recurrence_decode_kernel,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
+    Q38_CUDA_OK(attr);
+    Q38_REQUIRE(d->conv_dim % 4 == 0 && p->ld_z % 8 == 0 && reinterpret_cast<uintptr_t>(p->qkv) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(p->z) % 16 == 0 && reinterpret_cast<uintptr_t>(st->recurrent) % 16 == 0,
+                "gdn_recurrence: rows of qkv, z and the state must be 16-byte aligned");
+    const int items = batch->num_seqs * d->num_v_heads;
+    gdn_recurrence_decode_kernel<<<std::min(num_sms(), items), kDecThreads, kDecSmemBytes, as_stream(stream)>>>(
+        p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w,
+        p->eps, reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads,
+        d->num_v_heads, st->recurrent, batch->seq_start, batch->seq_slot, batch->num_seqs);
+    Q38_LAUNCH_OK("gdn_recurrence_decode_kernel");
+    return Q38_OK;
+  }
   gdn_recurrence_kernel<<<dim3(d->num_v_heads, batch->num_seqs), kRecWarps * 32, 0, as_stream(stream)>>>(
       p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w,
       p->eps, reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads,

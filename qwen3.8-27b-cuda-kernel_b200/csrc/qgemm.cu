@@ -54,7 +54,7 @@ __global__ void bq_dequant_kernel(const uint8_t* __restrict__ lo, const uint8_t*
   uint32_t s2[8];
   expand_scales(*reinterpret_cast<const uint4*>(sc + (nb * (k / 64) + kb / 4) * 128 + 16 * g), s2);
   uint32_t w[16];
-  decode_slab<BITS>(lw, hw, s2, w);
+  decode_slab<BITS>(lw, hw, s2, w, DecodeConsts{0x000F000Fu, 0x43004300u, BITS == 6 ? 0x00300030u : 0x00100010u});
 #pragma unroll
   for (int q = 0; q < 16; ++q) {
     const int j = q >> 1, h = q & 1;

@@ -77,6 +77,7 @@ struct StreamArgs {
   int tiles, kg;
   long long units;
   int split;
+  DecodeConsts dc;
 };
 
 __device__ __forceinline__ long long cta_begin(const StreamArgs& a, int cta, int grid) {
@@ -176,6 +177,7 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
   named_bar_sync(1, kConsumers);
   const int wn = warp & 1, wk = warp >> 1;
   const int gl = lane >> 2, tl = lane & 3;
+  const DecodeConsts dc = a.dc;
   uint32_t it = 0;
   for (long long u = u0; u < u1;) {
     const int tile = int(u / a.kg), kg_a = int(u % a.kg);
@@ -230,7 +232,7 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
               hi[3] = hv.w;
             }
             uint32_t w[16];
-            decode_slab<BITS>(lo, hi, s2, w);
+            decode_slab<BITS>(lo, hi, s2, w, dc);
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
               const uint32_t af[4] = {w[4 * jj], w[4 * jj + 2], w[4 * jj + 1], w[4 * jj + 3]};
@@ -399,6 +401,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.tiles = w.n / kTileN;
   a.kg = w.k / 64;
   a.units = (long long)a.tiles * a.kg;
+  a.dc = decode_consts(BITS);
   const int sms = num_sms();
   int grid = int(std::min<long long>(sms, std::max<long long>(1, a.units / 8)));
   const size_t need = (size_t)grid * 2 * C::kMpad * kTileN;

@@ -88,6 +88,7 @@ struct UmmaArgs {
   int tiles, kg;
   long long units;
   int split;
+  DecodeConsts dc;
 };
 
 __device__ __forceinline__ long long u_begin(const UmmaArgs& a, int cta, int grid) {
@@ -183,7 +184,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       mbar_init(&raw_empty[s], kDecodeWarps);
     }
     for (int s = 0; s < C::kUnits; ++s) {
-      mbar_init(&op_full[s], kWarpsPerSlice * C::kSpu + 1);  // decode warps + the activation copies' expect_tx
+      mbar_init(&op_full[s], kWarpsPerSlice + 1);  // eight decode warps + the activation copies' expect_tx
       mbar_init(&op_empty[s], 1);
     }
     mbar_init(acc_full, 1);
@@ -303,10 +304,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   } else if (warp >= kFirstDecodeWarp) {
     // ------------------------------ decode + epilogue warps ------------------------------
     const int dw = warp - kFirstDecodeWarp;
-    const int dgl = dw >> 3;           // which of the two k-groups of a pass this warp decodes
+    const int half = dw >> 3;          // which pair of the stage's four k-groups this warp decodes
     const int dnb = (dw >> 2) & 1;     // 64-column block of the tile
     const int ks = dw & 3;             // its k16 slab of the group
     const int gl = lane >> 2, tl = lane & 3;
+    const DecodeConsts dc = a.dc;
     const int quarter = dw & 3;        // TMEM lanes this warp may read (warp index modulo 4)
     const int cchunk = dw >> 2;        // which chunk of the token columns it handles in the epilogue
     const bool epi_active = cchunk < C::kEpiChunks;
@@ -317,6 +319,41 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     const uint32_t row_off = uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
     const uint32_t c0_off = row_off + (uint32_t((2 * ks) ^ gl) << 4);
     const uint32_t c1_off = row_off + (uint32_t((2 * ks + 1) ^ gl) << 4);
+    // One raw stage (4 k-groups) is decoded in one pass: warps 0-7 take k-groups 0-1, warps 8-15 k-groups 2-3, each
+    // warp the same (column block, k16 slab) in both groups, so the slot wait, the proxy fence and the barrier
+    // arrival are paid once per two slabs; the two halves run out of phase, which keeps the schedulers fed.
+    auto load_raw = [&](const uint8_t* st, int dg, uint32_t (&lo)[4], uint32_t (&hi)[4], uint4& sv) {
+      const int rslot = dnb * kGroupsPerStage + dg;
+      const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes;
+      const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
+      sv = *reinterpret_cast<const uint4*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl);
+      const uint4 lv = *reinterpret_cast<const uint4*>(lo_g + ks * 512 + lane * 16);
+      lo[0] = lv.x;
+      lo[1] = lv.y;
+      lo[2] = lv.z;
+      lo[3] = lv.w;
+      hi[0] = hi[1] = hi[2] = hi[3] = 0;
+      if constexpr (BITS == 5) {
+        hi[0] = *reinterpret_cast<const uint32_t*>(hi_g + ks * 128 + lane * 4);
+      } else if constexpr (BITS == 6) {
+        const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + ks * 256 + lane * 8);
+        hi[0] = hv.x;
+        hi[1] = hv.y;
+      } else if constexpr (BITS == 8) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(hi_g + ks * 512 + lane * 16);
+        hi[0] = hv.x;
+        hi[1] = hv.y;
+        hi[2] = hv.z;
+        hi[3] = hv.w;
+      }
+    };
+    auto store_slice = [&](uint8_t* base, const uint32_t (&w)[16]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        *reinterpret_cast<uint32_t*>(base + c0_off + j * 1024) = w[2 * j];
+        *reinterpret_cast<uint32_t*>(base + c1_off + j * 1024) = w[2 * j + 1];
+      }
+    };
     uint32_t it = 0, unit_ctr = 0, seg = 0;
     for (long long u = u0; u < u1; ++seg) {
       const int tile = int(u / a.kg), kg_a = int(u % a.kg);
@@ -326,52 +363,49 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         const int ng = min(kGroupsPerStage, kg_b - g);
         const bool ok = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x305);
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
-#pragma unroll
-        for (int p = 0; p < kGroupsPerStage / 2; ++p) {
-          const int dg = 2 * p + dgl;                       // this warp's k-group of the stage
-          const int first = C::kSpu == 2 ? 2 * p : dg;      // first k-group of the unit it belongs to
-          if (first < ng) {
-            const uint32_t uc = unit_ctr + uint32_t(C::kSpu == 2 ? p : dg);
+        const int g0 = 2 * half;  // first of this warp's two k-groups of the stage
+        if (g0 < ng) {
+          const bool two = g0 + 1 < ng;
+          uint32_t lo0[4] = {0, 0, 0, 0}, hi0[4] = {0, 0, 0, 0}, lo1[4] = {0, 0, 0, 0}, hi1[4] = {0, 0, 0, 0};
+          uint4 sv0 = make_uint4(0, 0, 0, 0), sv1 = sv0;
+          if (ok) {
+            load_raw(st, g0, lo0, hi0, sv0);
+            if (two) load_raw(st, g0 + 1, lo1, hi1, sv1);
+          }
+          uint32_t s2[8], w[16];
+          expand_scales(sv0, s2);
+          decode_slab<BITS>(lo0, hi0, s2, w, dc);
+          if constexpr (C::kSpu == 2) {
+            const uint32_t uc = unit_ctr + uint32_t(half);
             const int slot = uc % C::kUnits;
-            const bool have = ok && dg < ng;  // an odd tail leaves the second slice of a unit without data
-            uint32_t w[16];
-            if (have) {
-              // the raw bytes do not depend on the operand slot: fetch and decode them before waiting for it
-              const int rslot = dnb * kGroupsPerStage + dg;
-              const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes;
-              const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
-              uint32_t s2[8];
-              expand_scales(*reinterpret_cast<const uint4*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl), s2);
-              const uint4 lv = *reinterpret_cast<const uint4*>(lo_g + ks * 512 + lane * 16);
-              const uint32_t lo[4] = {lv.x, lv.y, lv.z, lv.w};
-              uint32_t hi[4] = {0, 0, 0, 0};
-              if constexpr (BITS == 5) {
-                hi[0] = *reinterpret_cast<const uint32_t*>(hi_g + ks * 128 + lane * 4);
-              } else if constexpr (BITS == 6) {
-                const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + ks * 256 + lane * 8);
-                hi[0] = hv.x;
-                hi[1] = hv.y;
-              } else if constexpr (BITS == 8) {
-                const uint4 hv = *reinterpret_cast<const uint4*>(hi_g + ks * 512 + lane * 16);
-                hi[0] = hv.x;
-                hi[1] = hv.y;
-                hi[2] = hv.z;
-                hi[3] = hv.w;
-              }
-              decode_slab<BITS>(lo, hi, s2, w);
-            }
             const bool free_slot = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x306);
-            if (have && free_slot) {
-              uint8_t* base = units + (size_t)slot * C::kUnitBytes + (C::kSpu == 2 ? dgl : 0) * kSliceBytes;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                *reinterpret_cast<uint32_t*>(base + c0_off + j * 1024) = w[2 * j];
-                *reinterpret_cast<uint32_t*>(base + c1_off + j * 1024) = w[2 * j + 1];
-              }
-              fence_async_smem();
+            uint8_t* base = units + (size_t)slot * C::kUnitBytes;
+            if (ok && free_slot) store_slice(base, w);
+            if (two) {
+              expand_scales(sv1, s2);
+              decode_slab<BITS>(lo1, hi1, s2, w, dc);
+              if (ok && free_slot) store_slice(base + kSliceBytes, w);
             }
+            fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&op_full[slot]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              if (e == 0 || two) {
+                if (e == 1) {
+                  expand_scales(sv1, s2);
+                  decode_slab<BITS>(lo1, hi1, s2, w, dc);
+                }
+                const uint32_t uc = unit_ctr + uint32_t(g0 + e);
+                const int slot = uc % C::kUnits;
+                const bool free_slot = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x306);
+                if (ok && free_slot) store_slice(units + (size_t)slot * C::kUnitBytes, w);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&op_full[slot]);
+              }
+            }
           }
         }
         __syncwarp();
@@ -562,6 +596,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.tiles = w.n / kTileN;
   a.kg = w.k / 64;
   a.units = (long long)a.tiles * a.kg;
+  a.dc = decode_consts(BITS);
   const int sms = num_sms();
   int grid = int(std::min<long long>(sms, std::max<long long>(1, a.units / 8)));
   const size_t need = (size_t)grid * 2 * TOK * kTileN;

@@ -391,6 +391,50 @@ def test_gdn_matches_oracle(nk, nv):
     assert float(rec[0].abs().sum()) == 0 and float(rec[:, 0].abs().sum()) == 0, "other slots / layers untouched"
 
 
+def test_gdn_decode_kernel_equals_general_kernel():
+    """Batches in which every sequence advances by one token take the persistent state-streaming kernel; it must
+    reproduce the general kernel bit for bit (outputs and states), also with an empty sequence in the batch and
+    with more (sequence, head) items than SMs."""
+    rng = np.random.default_rng(21)
+    nk, nv, layers, layer, slots = 2, 4, 2, 1, 70
+    conv_dim = 2 * nk * 128 + nv * 128
+    ld = conv_dim + nv * 128
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    A_d = dev((-rng.uniform(0.5, 8, nv)).astype(np.float32))
+    dt_d = dev((0.5 * rng.standard_normal(nv)).astype(np.float32))
+    nw_d = dev((1 + 0.2 * rng.standard_normal(128)).astype(np.float32))
+    rec0 = torch.from_numpy(rng.standard_normal((slots, layers, nv, 128, 128)).astype(np.float32) * 0.1).cuda()
+    seqs = [(slot, 5, 0 if slot == 17 else 1) for slot in range(2, 66)]
+    n = sum(c for _, _, c in seqs)
+    dims = pkg.GdnDims(nk, nv, conv_dim, ld)
+    results = []
+    for force_general in (False, True):
+        rec = rec0.clone()
+        conv = torch.zeros((slots, layers, 3, conv_dim), dtype=torch.bfloat16, device="cuda")
+        st = pkg.GdnStateDesc(pkg.ptr(rec), pkg.ptr(conv), layers)
+        outs = []
+        step_rng = np.random.default_rng(22)
+        for step in range(3):
+            batch = tl.Batch(seqs)
+            if force_general:
+                batch.desc.max_tokens_per_seq = 2
+            qkv = dev(step_rng.standard_normal((n, conv_dim)).astype(np.float32) * 0.3)
+            ab = dev(step_rng.standard_normal((n, 2 * nv)).astype(np.float32))
+            proj_d = tl.to_dev_bf16(tl.bf16_round(step_rng.standard_normal((n, ld))))
+            out = torch.zeros((n, nv * 128), dtype=torch.bfloat16, device="cuda")
+            rp = pkg.GdnRecurrenceParams(pkg.ptr(qkv), pkg.ptr(ab), pkg.ptr(A_d), pkg.ptr(dt_d),
+                                         pkg.ptr(proj_d) + conv_dim * 2, ld, pkg.ptr(nw_d), 1e-6, pkg.ptr(out), layer)
+            pkg.check(K().q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
+            sync_ok()
+            outs.append(out.view(torch.int16).cpu().numpy())
+        results.append((outs, rec.cpu().numpy()))
+    for a, b in zip(results[0][0], results[1][0]):
+        assert np.array_equal(a, b)
+    assert np.array_equal(results[0][1], results[1][1])
+    assert np.array_equal(results[0][1][17], rec0[17].cpu().numpy()), "the empty sequence's state is untouched"
+    assert not np.array_equal(results[0][1][2, layer], rec0[2, layer].cpu().numpy())
+
+
 # ---------------------------------------------------------------------------------------------------
 # sampling
 # ---------------------------------------------------------------------------------------------------
