@@ -18,6 +18,7 @@ struct ConfigInfo {
 constexpr ConfigInfo kConfigs[] = {
     {"stream_m8", 8, false}, {"stream_m16", 16, false}, {"umma_t32", 32, true},
     {"umma_t64", 64, true},  {"umma_t128", 128, true},  {"umma_t256", 256, true},
+    {"umma_t512", 512, true},
 };
 constexpr int kNumConfigs = int(sizeof(kConfigs) / sizeof(kConfigs[0]));
 
@@ -25,13 +26,17 @@ q38_gemm_tuning_lookup g_tuning = nullptr;
 
 // Small batches stream the weights through mma.sync (tokens are the 8-wide operand); from 17 tokens on the
 // tcgen05 kernel keeps the accumulators in TMEM.
-int auto_config(int m) {
+// Above 256 tokens one pass over 512 of them halves the decode work per token; it needs the larger stream-K
+// workspace (2 * SMs * 128 * 512 floats) and is not built for 8-bit weights.
+int auto_config(int m, const q38_bq_weight& w, const q38_gemm_workspace* ws) {
   if (m <= 8) return 0;
   if (m <= 16) return 1;
   if (m <= 32) return 2;
   if (m <= 64) return 3;
   if (m <= 128) return 4;
-  return 5;
+  if (m <= 256 || w.bits == 8) return 5;
+  const bool roomy = ws && ws->partials && ws->partial_floats >= size_t(2) * size_t(num_sms()) * 128 * 512;
+  return roomy || w.n / 128 >= 3 * num_sms() ? 6 : 5;
 }
 
 // One lane decodes one slab exactly as the GEMM does and writes the 32 weights to W[n][k] (bf16).
@@ -93,7 +98,7 @@ extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const
     const int t = g_tuning(w->bits, w->n, w->k, m);
     if (t >= 0 && t < kNumConfigs) config = t;
   }
-  if (config < 0) config = auto_config(m);
+  if (config < 0) config = auto_config(m, *w, ws);
   const int tm = kConfigs[config].tile_m;
   const cudaStream_t s = as_stream(stream);
   const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(a);

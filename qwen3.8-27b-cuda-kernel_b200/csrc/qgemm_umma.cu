@@ -47,7 +47,7 @@ struct UCfg {
   using G = BqGeom<BITS>;
   // operand unit: what one barrier round trip hands to the MMA thread = kSpu decoded slices + their activations
   static constexpr int kSpu = TOK <= 128 ? 2 : 1;
-  static constexpr int kUnits = TOK <= 64 ? 3 : TOK <= 128 ? 2 : 3;
+  static constexpr int kUnits = TOK <= 64 ? 3 : TOK <= 128 ? 2 : TOK <= 256 ? 3 : 2;
   static constexpr int kXBytes = TOK * 128;  // activation k-slice [TOK][64] bf16
   static constexpr int kUnitBytes = kSpu * (kSliceBytes + kXBytes);
   static constexpr int kLoOff = 0;
@@ -61,6 +61,7 @@ struct UCfg {
   static constexpr int kTailOff = kUnitOff + kUnits * kUnitBytes;
   static constexpr int kSmemBytes = 1024 + kTailOff + kTail;
   static constexpr int kTmemCols = TOK < 32 ? 32 : TOK;
+  static constexpr int kMmaN = TOK < 256 ? TOK : 256;  // tokens per MMA instruction and per activation box
   static constexpr int kEpiChunks = TOK >= 64 ? 4 : 2;  // decode warps per TMEM lane quarter that run the epilogue
   static constexpr int kColsPerWarp = TOK / kEpiChunks;
   static_assert(kStageBytes % 1024 == 0, "x slots and slices need 1024-byte alignment");
@@ -122,17 +123,25 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Both are called by a whole, converged warp with warp-uniform arguments; one elected lane issues. Keeping the
+// issuing code warp-uniform lets the descriptors live in uniform registers, which the instruction reads directly.
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      "{\n\t.reg .pred p, leader;\n\t"
+      "elect.sync _|leader, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@leader tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+  asm volatile(
+      "{\n\t.reg .pred leader;\n\t"
+      "elect.sync _|leader, 0xffffffff;\n\t"
+      "@leader tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar))
+      : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -256,30 +265,35 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           if (!alive) break;
           uint8_t* xs = units + (size_t)slot * C::kUnitBytes + C::kSpu * kSliceBytes;
           mbar_expect_tx(&op_full[slot], uint32_t(nu) * C::kXBytes);
-          for (int gi = 0; gi < nu; ++gi) tma_load_2d(xs + gi * C::kXBytes, &xmap, (g + gi) * 64, 0, &op_full[slot]);
+          for (int gi = 0; gi < nu; ++gi)
+#pragma unroll
+            for (int nh = 0; nh < TOK / C::kMmaN; ++nh)
+              tma_load_2d(xs + gi * C::kXBytes + nh * C::kMmaN * 128, &xmap, (g + gi) * 64, nh * C::kMmaN, &op_full[slot]);
         }
         u += kg_b - kg_a;
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    // One thread; its serial work per unit is one barrier wait, 4 MMAs per slice with precomputed descriptors,
-    // and one commit, because at small TOK the tensor work per slice is shorter than any of those round trips.
-    if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(TOK >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+    // The warp stays converged and one elected lane issues; the serial work per unit is one barrier wait, 4 MMAs
+    // per slice with precomputed descriptors, and one commit, because at small TOK the tensor work per slice is
+    // shorter than any of those round trips.
+    {
+      constexpr uint32_t idesc =
+          (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(C::kMmaN >> 3) << 17) | (uint32_t(128 >> 4) << 24);
       const uint64_t desc0 = smem_desc_sw128(smem_u32(units));
       uint32_t uc = 0, seg = 0;
       bool alive = true;
       for (long long u = u0; u < u1 && alive; ++seg) {
         const int kg_a = int(u % a.kg);
         const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
-        alive = wait_flag(acc_empty, (seg & 1) ^ 1, flags, 0x302);
+        alive = __all_sync(0xffffffffu, wait_flag(acc_empty, (seg & 1) ^ 1, flags, 0x302));
         tc_fence_after();
         uint32_t accumulate = 0;
         for (int g = kg_a; g < kg_b && alive; g += C::kSpu, ++uc) {
           const int slot = uc % C::kUnits;
           const int nu = min(C::kSpu, kg_b - g);
-          alive = wait_flag(&op_full[slot], (uc / C::kUnits) & 1, flags, 0x303);
+          alive = __all_sync(0xffffffffu, wait_flag(&op_full[slot], (uc / C::kUnits) & 1, flags, 0x303));
           if (!alive) break;
           tc_fence_after();
           const uint64_t da = desc0 + uint64_t((uint32_t(slot) * C::kUnitBytes) >> 4);
@@ -289,8 +303,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
             if (gi < nu) {
 #pragma unroll
               for (int ks = 0; ks < 4; ++ks) {
-                umma_bf16(tmem_base, da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
-                          dx + uint64_t((gi * C::kXBytes + ks * 32) >> 4), idesc, accumulate);
+#pragma unroll
+                for (int nh = 0; nh < TOK / C::kMmaN; ++nh)
+                  umma_bf16(tmem_base + uint32_t(nh * C::kMmaN), da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
+                            dx + uint64_t((gi * C::kXBytes + nh * C::kMmaN * 128 + ks * 32) >> 4), idesc, accumulate);
                 accumulate = 1;
               }
             }
@@ -319,9 +335,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     const uint32_t row_off = uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
     const uint32_t c0_off = row_off + (uint32_t((2 * ks) ^ gl) << 4);
     const uint32_t c1_off = row_off + (uint32_t((2 * ks + 1) ^ gl) << 4);
-    // One raw stage (4 k-groups) is decoded in one pass: warps 0-7 take k-groups 0-1, warps 8-15 k-groups 2-3, each
-    // warp the same (column block, k16 slab) in both groups, so the slot wait, the proxy fence and the barrier
-    // arrival are paid once per two slabs; the two halves run out of phase, which keeps the schedulers fed.
+    // One raw stage (4 k-groups) is decoded in one pass, each warp the same (column block, k16 slab) in two groups.
+    // Two-slice units: warps 0-7 take k-groups 0-1 (one unit), warps 8-15 k-groups 2-3, so the slot wait, the proxy
+    // fence and the barrier arrival are paid once per two slabs. One-slice units: warps 0-7 take k-groups 0 and 2,
+    // warps 8-15 k-groups 1 and 3. Either way a warp's successive units are two apart, so with a ring of two or
+    // more units the phase it waits for is never more than one ahead of the barrier (a parity wait cannot tell
+    // phases two apart); across a segment boundary the accumulator barrier has seen every earlier commit.
     auto load_raw = [&](const uint8_t* st, int dg, uint32_t (&lo)[4], uint32_t (&hi)[4], uint4& sv) {
       const int rslot = dnb * kGroupsPerStage + dg;
       const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes;
@@ -363,14 +382,15 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         const int ng = min(kGroupsPerStage, kg_b - g);
         const bool ok = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x305);
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
-        const int g0 = 2 * half;  // first of this warp's two k-groups of the stage
+        const int g0 = C::kSpu == 2 ? 2 * half : half;  // first of this warp's two k-groups of the stage
+        constexpr int kGStep = C::kSpu == 2 ? 1 : 2;      // distance to its second one
         if (g0 < ng) {
-          const bool two = g0 + 1 < ng;
+          const bool two = g0 + kGStep < ng;
           uint32_t lo0[4] = {0, 0, 0, 0}, hi0[4] = {0, 0, 0, 0}, lo1[4] = {0, 0, 0, 0}, hi1[4] = {0, 0, 0, 0};
           uint4 sv0 = make_uint4(0, 0, 0, 0), sv1 = sv0;
           if (ok) {
             load_raw(st, g0, lo0, hi0, sv0);
-            if (two) load_raw(st, g0 + 1, lo1, hi1, sv1);
+            if (two) load_raw(st, g0 + kGStep, lo1, hi1, sv1);
           }
           uint32_t s2[8], w[16];
           expand_scales(sv0, s2);
@@ -397,7 +417,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                   expand_scales(sv1, s2);
                   decode_slab<BITS>(lo1, hi1, s2, w, dc);
                 }
-                const uint32_t uc = unit_ctr + uint32_t(g0 + e);
+                const uint32_t uc = unit_ctr + uint32_t(g0 + kGStep * e);
                 const int slot = uc % C::kUnits;
                 const bool free_slot = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x306);
                 if (ok && free_slot) store_slice(units + (size_t)slot * C::kUnitBytes, w);
@@ -569,7 +589,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   CUtensorMap xmap;
   const cuuint64_t dims[2] = {cuuint64_t(w.k), cuuint64_t(m)};
   const cuuint64_t strides[1] = {cuuint64_t(w.k) * 2};
-  const cuuint32_t box[2] = {64, cuuint32_t(TOK)};
+  const cuuint32_t box[2] = {64, cuuint32_t(C::kMmaN)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(a_ptr), dims, strides,
                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -621,13 +641,20 @@ int launch_bits(int tok, const __nv_bfloat16* a, int m, const q38_bq_weight& w, 
     case 32: return launch_one<BITS, 32>(a, m, w, ep, ws, s);
     case 64: return launch_one<BITS, 64>(a, m, w, ep, ws, s);
     case 128: return launch_one<BITS, 128>(a, m, w, ep, ws, s);
-    default: return launch_one<BITS, 256>(a, m, w, ep, ws, s);
+    case 256: return launch_one<BITS, 256>(a, m, w, ep, ws, s);
+    default:
+      if constexpr (BITS == 8) {
+        set_error("qgemm: the 512-token configuration is not built for 8-bit weights");
+        return Q38_ERR_INVALID;
+      } else {
+        return launch_one<BITS, 512>(a, m, w, ep, ws, s);
+      }
   }
 }
 
 }  // namespace
 
-// m <= tok, tok in {32, 64, 128, 256}. Called by the dispatcher in qgemm.cu.
+// m <= tok, tok in {32, 64, 128, 256, 512}. Called by the dispatcher in qgemm.cu.
 int qgemm_umma_launch(int tok, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
                       const q38_gemm_workspace* ws, cudaStream_t s) {
   switch (w.bits) {

@@ -71,7 +71,7 @@ class Planes:
 
 
 class Workspace:
-    def __init__(self, pkg, tokens_per_pass=256):
+    def __init__(self, pkg, tokens_per_pass=512):
         sms = pkg.kernels().q38_num_sms()
         self.partials = torch.empty(2 * sms * 128 * tokens_per_pass, dtype=torch.float32, device="cuda")
         self.counters = torch.zeros(8192, dtype=torch.int32, device="cuda")
@@ -109,14 +109,15 @@ def time_gemm(pkg, copies, ws, m, config, iters=20):
     return e0.elapsed_time(e1) / iters * 1e3  # microseconds per launch
 
 
-def configs_for(pkg, m):
+def configs_for(pkg, bits):
+    """Every tile configuration built for this bit width (the 512-token pass does not exist for 8-bit weights)."""
     K = pkg.kernels()
-    return [c for c in range(K.q38_qgemm_num_configs())]
+    return [c for c in range(K.q38_qgemm_num_configs()) if not (bits == 8 and K.q38_qgemm_config_tile_m(c) == 512)]
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--m", default="1,8,16,32,64,128,256", help="comma-separated token counts")
+    ap.add_argument("--m", default="1,8,16,32,64,128,256,512", help="comma-separated token counts")
     ap.add_argument("--shapes", default="", help="comma-separated shape names (default: all of the 27B geometry)")
     ap.add_argument("--config", type=int, default=-1, help="tile configuration id (-1: the dispatcher's choice)")
     ap.add_argument("--sweep", action="store_true", help="time every configuration and report the best")
@@ -156,7 +157,7 @@ def main(argv=None):
         one = sum(plane_bytes(n, k, bits))
         copies = [Planes(pkg, n, k, bits) for _ in range(max(2, -(-2 * L2_BYTES // one)))]
         for m in ms:
-            cands = configs_for(pkg, m) if args.sweep else [args.config]
+            cands = configs_for(pkg, bits) if args.sweep else [args.config]
             best = None
             for c in cands:
                 us = time_gemm(pkg, copies, ws, m, c)

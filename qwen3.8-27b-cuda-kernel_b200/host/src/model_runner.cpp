@@ -230,7 +230,7 @@ void ModelRunner::Impl::setup() {
   const size_t T = size_t(max_tokens), R = size_t(max_rows);
   const size_t mixer_w = size_t(std::max(cfg.q_dim(), cfg.gdn_value_dim()));
   const size_t nv2 = 2 * size_t(std::max(1, cfg.linear_num_value_heads));
-  const size_t gemm_partials = size_t(2) * 3 * size_t(dev.num_sms) * 128 * 128;
+  const size_t gemm_partials = size_t(2) * size_t(dev.num_sms) * 128 * 512;  // stream-K partial tiles of a 512-token pass
   meta = MetaMap(max_tokens, max_rows);
   const size_t sizes[] = {
       T * H * 4, T * H * 2, T * size_t(cfg.norm_blocks()) * 4, T * size_t(proj_ld) * 2, T * nv2 * 4,

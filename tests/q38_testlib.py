@@ -185,7 +185,7 @@ def make_bq(n: int, k: int, bits: int, seed: int, std: float = 0.02, grid: int =
 
 
 class Workspace:
-    def __init__(self, floats: int = 2 * 3 * 148 * 128 * 128, counters: int = 65536, device="cuda"):
+    def __init__(self, floats: int = 2 * 148 * 128 * 512, counters: int = 65536, device="cuda"):
         self.partials = torch.empty(floats, dtype=torch.float32, device=device)
         self.counters = torch.zeros(counters, dtype=torch.int32, device=device)
         self.desc = pkg.GemmWorkspace(pkg.ptr(self.partials), floats, pkg.ptr(self.counters), counters)

@@ -61,13 +61,17 @@ def test_qgemm_matches_oracle_all_configs(bits):
         p = tl.make_bq(n, k, bits, seed=bits * 100 + n, std=0.05, fast=(n > 256))
         w = tl.DeviceBQ(p)
         wd = tl.oracle().dequant(p)
-        for m in (1, 3, 16, 17, 40, 64, 130):
+        for m in (1, 3, 16, 17, 40, 64, 130, 300, 512):
             a = tl.bf16_round(rng.standard_normal((m, k)))
             a_dev = tl.to_dev_bf16(a)
             want = np.zeros((m, n), np.float32)
             tl.oracle().qgemm(a, wd, None, 3, out=want, ldo=n)
             mag = np.abs(a).astype(np.float64) @ np.abs(wd).astype(np.float64).T
             for cfg in range(K().q38_qgemm_num_configs()):
+                if bits == 8 and K().q38_qgemm_config_tile_m(cfg) == 512:
+                    with pytest.raises(pkg.KernelError):  # not built: shared memory cannot hold two raw stages
+                        run_gemm_f32(a_dev, m, w, ws.desc, cfg)
+                    continue
                 for use_ws in (True, False):
                     got = run_gemm_f32(a_dev, m, w, ws.desc if use_ws else None, cfg)
                     err = np.abs(got.cpu().numpy().astype(np.float64) - want)
