@@ -204,6 +204,17 @@ typedef struct q38_gdn_recurrence_params {
 int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d, const q38_batch_desc* batch,
                        const q38_gdn_state_desc* st, void* stream);
 
+/* The same operation in the chunked (64-token WY) form for prefill-sized runs: token-parallel preparation plus a
+ * per-chunk state scan instead of a token-by-token loop; results agree with q38_gdn_recurrence to fp32 rounding.
+ * Any run lengths are accepted (short runs are padded to a chunk, so q38_gdn_recurrence is the better choice when
+ * batch->max_tokens_per_seq is small). `scratch` holds q38_gdn_chunk_scratch_floats(num_tokens, num_seqs,
+ * num_v_heads) floats, 16-byte aligned, and may be reused by the next call on the same stream.
+ * No counterpart in the reference, whose gdn_recurrence (kernels.h:212-228) is token-sequential. */
+size_t q38_gdn_chunk_scratch_floats(int max_tokens, int max_seqs, int num_v_heads);
+int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d,
+                               const q38_batch_desc* batch, const q38_gdn_state_desc* st, float* scratch,
+                               size_t scratch_floats, void* stream);
+
 /* kernels::SamplingParamsDev / SamplingArgs / sample / target_logprobs, kernels.h:233-260 */
 typedef struct q38_sampling_params_dev {
   float temperature;

@@ -126,6 +126,9 @@ KERNEL_API = {
                                C.POINTER(GdnStateDesc), C.c_void_p]),
     "q38_gdn_recurrence": (C.c_int, [C.POINTER(GdnRecurrenceParams), C.POINTER(GdnDims), C.POINTER(BatchDesc),
                                      C.POINTER(GdnStateDesc), C.c_void_p]),
+    "q38_gdn_chunk_scratch_floats": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "q38_gdn_recurrence_chunked": (C.c_int, [C.POINTER(GdnRecurrenceParams), C.POINTER(GdnDims), C.POINTER(BatchDesc),
+                                             C.POINTER(GdnStateDesc), C.c_void_p, C.c_size_t, C.c_void_p]),
     "q38_sample": (C.c_int, [C.POINTER(SamplingArgs), C.c_int, C.c_void_p]),
     "q38_target_logprobs": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "q38_pack_ragged": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,

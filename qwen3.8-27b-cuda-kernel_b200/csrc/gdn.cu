@@ -412,6 +412,347 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// gdn_recurrence for prefill chunks: the chunked (WY) form of the gated delta rule. The token recurrence
+//     S_t = a_t S_{t-1} + beta_t (v_t - a_t S_{t-1} k_t) k_t^T,   o_t = S_t q_t        (S is [dv][dk])
+// is sequential in t; over a chunk of C = 64 tokens with lg_i = sum_{t<=i} log a_t it is equivalent to
+//     A[i][j] = beta_i e^{lg_i - lg_j} (k_i . k_j)  (j < i)          P[i][j] = e^{lg_i - lg_j} (q_i . k_j)  (j <= i)
+//     (I + A) U0 = diag(beta) V         (I + A) W = diag(beta e^{lg}) K                       (prep, no state)
+//     U = U0 - W S_0^T      O = diag(e^{lg}) Q S_0^T + P U      S_C = e^{lg_C} S_0 + U^T diag(e^{lg_C - lg}) K
+// so everything that does not touch the state is computed for all chunks in parallel (gdn_chunk_prep_kernel,
+// one CTA per (chunk, v head, sequence)), and the sequential part is four small matrix products per chunk with
+// the state resident in shared memory (gdn_chunk_scan_kernel, one CTA per (v head, sequence)). All arithmetic
+// is fp32 on the CUDA cores; every exponent is <= 0, so nothing overflows however strong the decay is.
+// Tokens beyond a sequence's ragged tail are treated as beta = 0, log a = 0, q = k = v = 0 (no effect).
+// Scratch per (chunk slot, v head): U0 [64][128], W [64][128], P [64][64], lg [64] floats; the chunk slots of
+// sequence b start at seq_start[b] / 64 + b (never fewer than the chunks before it, so slots do not collide).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kCh = 64;
+constexpr int kLd = 132;   // padded row stride (floats) of 128-wide shared tiles: 16-byte reads of 8 rows hit 32 banks
+constexpr int kLdP = 68;   // the same for 64-wide tiles
+constexpr int kChunkFloats = 2 * kCh * 128 + kCh * kCh + kCh;
+constexpr int kChunkThreads = 512;
+
+__device__ __forceinline__ void token_gates(const float* __restrict__ ab, int m, int nv, int vh, float a_h, float dt_h,
+                                            float& beta, float& log_decay) {
+  const float bb = ab[(size_t)m * 2 * nv + vh], aa = ab[(size_t)m * 2 * nv + nv + vh];
+  beta = 1.0f / (1.0f + expf(-bb));
+  const float xsp = aa + dt_h;
+  const float sp = xsp > 20.0f ? xsp : log1pf(expf(xsp));
+  log_decay = a_h * sp;
+}
+
+// rows [0, nc) of a [.][128] fp32 row block -> shared [64][kLd], rows >= nc zero; optional per-row scale
+__device__ __forceinline__ void load_rows_128(float* dst, const float* __restrict__ src, size_t ld, int nc,
+                                              const float* row_scale, int tid) {
+  for (int i = tid; i < kCh * 32; i += kChunkThreads) {
+    const int r = i >> 5, c4 = i & 31;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nc) {
+      v = *reinterpret_cast<const float4*>(src + (size_t)r * ld + 4 * c4);
+      if (row_scale) {
+        const float sc = row_scale[r];
+        v.x *= sc;
+        v.y *= sc;
+        v.z *= sc;
+        v.w *= sc;
+      }
+    }
+    *reinterpret_cast<float4*>(dst + r * kLd + 4 * c4) = v;
+  }
+}
+
+constexpr int kPrepSmemBytes = (2 * kCh * kLd + kCh * kLdP + 3 * kCh) * 4;
+
+__global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_prep_kernel(
+    const float* __restrict__ qkv, int conv_dim, const float* __restrict__ ab, const float* __restrict__ A,
+    const float* __restrict__ dt_bias, int nk, int nv, const int* __restrict__ seq_start, float* __restrict__ scratch) {
+  extern __shared__ float prep_sm[];
+  float* Ks = prep_sm;
+  float* Qs = Ks + kCh * kLd;
+  float* As = Qs + kCh * kLd;  // [64][kLdP]
+  float* beta_s = As + kCh * kLdP;
+  float* lg_s = beta_s + kCh;
+  float* la_s = lg_s + kCh;
+  const int c = blockIdx.x, vh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x;
+  const int s0 = seq_start[b], n = seq_start[b + 1] - s0;
+  if (c * kCh >= n) return;
+  const int nc = min(kCh, n - c * kCh), m0 = s0 + c * kCh;
+  const int kh = vh / (nv / nk);
+  float* out = scratch + ((size_t)(s0 / kCh + b + c) * nv + vh) * kChunkFloats;
+  float* U0g = out;
+  float* Wg = out + kCh * 128;
+  float* Pg = out + 2 * kCh * 128;
+  float* lgg = Pg + kCh * kCh;
+
+  const float* rows = qkv + (size_t)m0 * conv_dim;
+  load_rows_128(Qs, rows + (size_t)kh * kDk, conv_dim, nc, nullptr, tid);
+  load_rows_128(Ks, rows + (size_t)nk * kDk + (size_t)kh * kDk, conv_dim, nc, nullptr, tid);
+  if (tid < kCh) {
+    float be = 0.0f, la = 0.0f;
+    if (tid < nc) token_gates(ab, m0 + tid, nv, vh, A[vh], dt_bias[vh], be, la);
+    beta_s[tid] = be;
+    la_s[tid] = la;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float run = 0.0f;
+    for (int i = 0; i < kCh; ++i) {
+      run += la_s[i];
+      lg_s[i] = run;
+    }
+  }
+  __syncthreads();
+  if (tid < kCh) lgg[tid] = lg_s[tid];
+
+  // ---- G = K K^T and Q K^T: thread = rows {2 ty, 2 ty + 1} x columns {tx + 16 jj} ----
+  {
+    const int ty = tid >> 4, tx = tid & 15;
+    float ag[2][4], ap[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) ag[i][jj] = ap[i][jj] = 0.0f;
+#pragma unroll 4
+    for (int kk = 0; kk < 128; kk += 4) {
+      float4 ak[2], aq[2], bk[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        ak[i] = *reinterpret_cast<const float4*>(Ks + (2 * ty + i) * kLd + kk);
+        aq[i] = *reinterpret_cast<const float4*>(Qs + (2 * ty + i) * kLd + kk);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) bk[jj] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * jj) * kLd + kk);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          ag[i][jj] += ak[i].x * bk[jj].x + ak[i].y * bk[jj].y + ak[i].z * bk[jj].z + ak[i].w * bk[jj].w;
+          ap[i][jj] += aq[i].x * bk[jj].x + aq[i].y * bk[jj].y + aq[i].z * bk[jj].z + aq[i].w * bk[jj].w;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int r = 2 * ty + i, col = tx + 16 * jj;
+        const float e = col <= r ? expf(lg_s[r] - lg_s[col]) : 0.0f;
+        As[r * kLdP + col] = col < r ? beta_s[r] * e * ag[i][jj] : 0.0f;
+        Pg[r * kCh + col] = e * ap[i][jj];
+      }
+  }
+  __syncthreads();
+
+  // ---- forward substitution (I + A) X = RHS: one thread per column of [diag(beta) V | diag(beta e^lg) K] ----
+  if (tid < 256) {
+    float x[kCh];
+    if (tid < 128) {
+      const float* vcol = rows + (size_t)2 * nk * kDk + (size_t)vh * kDv + tid;
+#pragma unroll
+      for (int i = 0; i < kCh; ++i) x[i] = i < nc ? beta_s[i] * vcol[(size_t)i * conv_dim] : 0.0f;
+    } else {
+#pragma unroll
+      for (int i = 0; i < kCh; ++i) x[i] = beta_s[i] * expf(lg_s[i]) * Ks[i * kLd + tid - 128];
+    }
+#pragma unroll
+    for (int i = 1; i < kCh; ++i) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int j0 = 0; j0 < i; j0 += 4) {
+        const float4 a4 = *reinterpret_cast<const float4*>(As + i * kLdP + j0);  // entries at j >= i are zero
+        acc += a4.x * x[j0];
+        if (j0 + 1 < i) acc += a4.y * x[j0 + 1];
+        if (j0 + 2 < i) acc += a4.z * x[j0 + 2];
+        if (j0 + 3 < i) acc += a4.w * x[j0 + 3];
+      }
+      x[i] -= acc;
+    }
+    float* dst = tid < 128 ? U0g + tid : Wg + (tid - 128);
+#pragma unroll
+    for (int i = 0; i < kCh; ++i) dst[i * 128] = x[i];
+  }
+}
+
+constexpr int kScanSmemBytes = (128 * kLd + 4 * kCh * kLd + kCh * kLdP + 3 * kCh) * 4;
+
+__global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
+    const float* __restrict__ qkv, int conv_dim, const __nv_bfloat16* __restrict__ z, int ld_z,
+    const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
+    int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+    const float* __restrict__ scratch) {
+  extern __shared__ float scan_sm[];
+  float* Ss = scan_sm;               // [128 v][kLd]
+  float* Ws = Ss + 128 * kLd;        // [64][kLd]
+  float* Qs = Ws + kCh * kLd;
+  float* Kd = Qs + kCh * kLd;        // K rows scaled by e^{lg_C - lg_j}
+  float* Us = Kd + kCh * kLd;        // U0, then U
+  float* Ps = Us + kCh * kLd;        // [64][kLdP]
+  float* lg_s = Ps + kCh * kLdP;
+  float* eg_s = lg_s + kCh;          // e^{lg_t}
+  float* kd_s = eg_s + kCh;          // e^{lg_C - lg_j}
+  const int vh = blockIdx.x, b = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int s0 = seq_start[b], n = seq_start[b + 1] - s0;
+  if (n <= 0) return;
+  const int kh = vh / (nv / nk);
+  float* S = recurrent + (((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv * kDk;
+  for (int i = tid; i < 128 * 32; i += kChunkThreads)
+    *reinterpret_cast<float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31)) = *reinterpret_cast<const float4*>(S + (size_t)i * 4);
+  const int chunks = (n + kCh - 1) / kCh;
+  const float nw0 = norm_w[lane], nw1 = norm_w[lane + 32], nw2 = norm_w[lane + 64], nw3 = norm_w[lane + 96];
+  const float nw[4] = {nw0, nw1, nw2, nw3};
+
+  for (int c = 0; c < chunks; ++c) {
+    const int nc = min(kCh, n - c * kCh), m0 = s0 + c * kCh;
+    const float* in = scratch + ((size_t)(s0 / kCh + b + c) * nv + vh) * kChunkFloats;
+    __syncthreads();  // the previous chunk's state update (or the initial state load) is complete
+    if (tid < kCh) {
+      const float lg = in[2 * kCh * 128 + kCh * kCh + tid], lgc = in[2 * kCh * 128 + kCh * kCh + kCh - 1];
+      lg_s[tid] = lg;
+      eg_s[tid] = expf(lg);
+      kd_s[tid] = expf(lgc - lg);
+    }
+    __syncthreads();
+    const float* rows = qkv + (size_t)m0 * conv_dim;
+    load_rows_128(Us, in, 128, kCh, nullptr, tid);
+    load_rows_128(Ws, in + kCh * 128, 128, kCh, nullptr, tid);
+    load_rows_128(Qs, rows + (size_t)kh * kDk, conv_dim, nc, nullptr, tid);
+    load_rows_128(Kd, rows + (size_t)nk * kDk + (size_t)kh * kDk, conv_dim, nc, kd_s, tid);
+    for (int i = tid; i < kCh * 16; i += kChunkThreads)
+      *reinterpret_cast<float4*>(Ps + (i >> 4) * kLdP + 4 * (i & 15)) =
+          *reinterpret_cast<const float4*>(in + 2 * kCh * 128 + (size_t)i * 4);
+    __syncthreads();
+
+    // thread tile of the [64 tokens][128 v] products: tokens 4 warp + i, v = lane + 32 jj
+    const int t0 = 4 * warp;
+    float acc[4][4];
+    // ---- (a) U = U0 - W S0^T ----
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+#pragma unroll 2
+    for (int kk = 0; kk < 128; kk += 4) {
+      float4 av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(Ws + (t0 + i) * kLd + kk);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          acc[i][jj] += av[i].x * bv[jj].x + av[i].y * bv[jj].y + av[i].z * bv[jj].z + av[i].w * bv[jj].w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) Us[(t0 + i) * kLd + lane + 32 * jj] -= acc[i][jj];
+    __syncthreads();
+
+    // ---- (b) Y = diag(e^lg) Q S0^T, (c) O = Y + P U ----
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+#pragma unroll 2
+    for (int kk = 0; kk < 128; kk += 4) {
+      float4 av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(Qs + (t0 + i) * kLd + kk);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          acc[i][jj] += av[i].x * bv[jj].x + av[i].y * bv[jj].y + av[i].z * bv[jj].z + av[i].w * bv[jj].w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) acc[i][jj] *= eg_s[t0 + i];
+#pragma unroll 2
+    for (int j = 0; j < kCh; j += 4) {
+      float4 pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (t0 + i) * kLdP + j);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float uv[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) uv[jj] = Us[(j + q) * kLd + lane + 32 * jj];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float pij = q == 0 ? pv[i].x : q == 1 ? pv[i].y : q == 2 ? pv[i].z : pv[i].w;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) acc[i][jj] += pij * uv[jj];
+        }
+      }
+    }
+    // gated RMSNorm over the 128 outputs of each token (a warp holds whole tokens)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float ss = warp_sum(acc[i][0] * acc[i][0] + acc[i][1] * acc[i][1] + acc[i][2] * acc[i][2] + acc[i][3] * acc[i][3]);
+      const int t = t0 + i;
+      if (t < nc) {
+        const float r = 1.0f / sqrtf(ss / float(kDv) + eps);
+        const size_t m = (size_t)(m0 + t);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int d = lane + 32 * jj;
+          const float zz = __bfloat162float(z[m * ld_z + (size_t)vh * kDv + d]);
+          out[m * nv * kDv + (size_t)vh * kDv + d] = __float2bfloat16_rn(acc[i][jj] * r * nw[jj] * silu_f(zz));
+        }
+      }
+    }
+    __syncthreads();  // every read of S0 is done
+
+    // ---- (d) S = e^{lg_C} S0 + U^T Kd: thread tile v = 4 vq + i, k = 4 ko + {0..3} and 64 + 4 ko + {0..3} ----
+    {
+      const int vq = tid >> 4, ko = tid & 15;
+      float sacc[4][8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sacc[i][e] = 0.0f;
+#pragma unroll 4
+      for (int j = 0; j < kCh; ++j) {
+        const float4 u4 = *reinterpret_cast<const float4*>(Us + j * kLd + 4 * vq);
+        const float4 k0 = *reinterpret_cast<const float4*>(Kd + j * kLd + 4 * ko);
+        const float4 k1 = *reinterpret_cast<const float4*>(Kd + j * kLd + 64 + 4 * ko);
+        const float uu[4] = {u4.x, u4.y, u4.z, u4.w};
+        const float kk8[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sacc[i][e] += uu[i] * kk8[e];
+      }
+      const float gC = eg_s[kCh - 1];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float* r0 = Ss + (4 * vq + i) * kLd + 4 * ko;
+        float4 a = *reinterpret_cast<float4*>(r0), bq = *reinterpret_cast<float4*>(r0 + 64);
+        a.x = gC * a.x + sacc[i][0];
+        a.y = gC * a.y + sacc[i][1];
+        a.z = gC * a.z + sacc[i][2];
+        a.w = gC * a.w + sacc[i][3];
+        bq.x = gC * bq.x + sacc[i][4];
+        bq.y = gC * bq.y + sacc[i][5];
+        bq.z = gC * bq.z + sacc[i][6];
+        bq.w = gC * bq.w + sacc[i][7];
+        *reinterpret_cast<float4*>(r0) = a;
+        *reinterpret_cast<float4*>(r0 + 64) = bq;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < 128 * 32; i += kChunkThreads)
+    *reinterpret_cast<float4*>(S + (size_t)i * 4) = *reinterpret_cast<const float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31));
+}
+
 }  // namespace
 
 unsigned int gdn_error(bool clear) { return read_tu_error(clear); }
@@ -479,5 +820,42 @@ extern "C" int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_
       p->eps, reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads,
       d->num_v_heads, st->recurrent, batch->seq_start, batch->seq_slot);
   Q38_LAUNCH_OK("gdn_recurrence_kernel");
+  return Q38_OK;
+}
+
+extern "C" size_t q38_gdn_chunk_scratch_floats(int max_tokens, int max_seqs, int num_v_heads) {
+  return (size_t)(max_tokens / kCh + max_seqs) * (size_t)num_v_heads * kChunkFloats;
+}
+
+extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d,
+                                          const q38_batch_desc* batch, const q38_gdn_state_desc* st, float* scratch,
+                                          size_t scratch_floats, void* stream) {
+  Q38_REQUIRE(p && d && batch && st, "gdn_recurrence_chunked: null argument");
+  if (batch->num_tokens == 0) return Q38_OK;
+  Q38_REQUIRE(d->num_k_heads > 0 && d->num_v_heads % d->num_k_heads == 0, "gdn_recurrence_chunked: head ratio");
+  Q38_REQUIRE(p->qkv && p->ab && p->A && p->dt_bias && p->z && p->norm_w && p->out && st->recurrent && scratch,
+              "gdn_recurrence_chunked: null pointer");
+  Q38_REQUIRE(d->conv_dim % 4 == 0 && reinterpret_cast<uintptr_t>(p->qkv) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(scratch) % 16 == 0 && reinterpret_cast<uintptr_t>(st->recurrent) % 16 == 0,
+              "gdn_recurrence_chunked: qkv rows, scratch and state must be 16-byte aligned");
+  Q38_REQUIRE(batch->max_tokens_per_seq >= 1, "gdn_recurrence_chunked: max_tokens_per_seq %d", batch->max_tokens_per_seq);
+  const size_t need = q38_gdn_chunk_scratch_floats(batch->num_tokens, batch->num_seqs, d->num_v_heads);
+  Q38_REQUIRE(scratch_floats >= need, "gdn_recurrence_chunked: scratch of %zu floats, %zu needed", scratch_floats, need);
+  static const cudaError_t attr1 =
+      cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
+  static const cudaError_t attr2 =
+      cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  Q38_CUDA_OK(attr1);
+  Q38_CUDA_OK(attr2);
+  const cudaStream_t s = as_stream(stream);
+  const int max_chunks = (batch->max_tokens_per_seq + kCh - 1) / kCh;
+  gdn_chunk_prep_kernel<<<dim3(max_chunks, d->num_v_heads, batch->num_seqs), kChunkThreads, kPrepSmemBytes, s>>>(
+      p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, d->num_k_heads, d->num_v_heads, batch->seq_start, scratch);
+  Q38_LAUNCH_OK("gdn_chunk_prep_kernel");
+  gdn_chunk_scan_kernel<<<dim3(d->num_v_heads, batch->num_seqs), kChunkThreads, kScanSmemBytes, s>>>(
+      p->qkv, d->conv_dim, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w, p->eps,
+      reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads, d->num_v_heads,
+      st->recurrent, batch->seq_start, batch->seq_slot, scratch);
+  Q38_LAUNCH_OK("gdn_chunk_scan_kernel");
   return Q38_OK;
 }

@@ -229,6 +229,19 @@ inline void gdn_recurrence(const GdnRecurrenceParams& p, const GdnDims& d, const
   const q38_gdn_state_desc cs{st.recurrent, reinterpret_cast<q38_bf16*>(st.conv), st.num_gdn_layers};
   detail::ok(q38_gdn_recurrence(&cp, &cd, &cb, &cs, stream));
 }
+// Chunked (64-token) form of gdn_recurrence for prefill-sized runs; extension, no counterpart in the reference.
+inline size_t gdn_chunk_scratch_floats(int max_tokens, int max_seqs, int num_v_heads) {
+  return q38_gdn_chunk_scratch_floats(max_tokens, max_seqs, num_v_heads);
+}
+inline void gdn_recurrence_chunked(const GdnRecurrenceParams& p, const GdnDims& d, const BatchDesc& batch,
+                                   const GdnStateDesc& st, float* scratch, size_t scratch_floats, cudaStream_t stream) {
+  const q38_gdn_recurrence_params cp{p.qkv, p.ab, p.A, p.dt_bias, reinterpret_cast<const q38_bf16*>(p.z), p.ld_z,
+                                     p.norm_w, p.eps, reinterpret_cast<q38_bf16*>(p.out), p.gdn_layer};
+  const q38_gdn_dims cd{d.num_k_heads, d.num_v_heads, d.conv_dim, d.ld_proj};
+  const q38_batch_desc cb = batch.c();
+  const q38_gdn_state_desc cs{st.recurrent, reinterpret_cast<q38_bf16*>(st.conv), st.num_gdn_layers};
+  detail::ok(q38_gdn_recurrence_chunked(&cp, &cd, &cb, &cs, scratch, scratch_floats, stream));
+}
 
 using SamplingParamsDev = q38_sampling_params_dev;
 struct SamplingArgs {

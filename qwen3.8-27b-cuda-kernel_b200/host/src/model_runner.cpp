@@ -17,6 +17,9 @@ namespace {
 
 constexpr size_t kMiB = 1024 * 1024;
 constexpr int kMaxSplits = 64;
+// From this run length on, a step's GDN layers use the chunked recurrence: a 64-token chunk costs about as much as
+// a dozen sequential token updates.
+constexpr int kGdnChunkedMinRun = 16;
 constexpr int kBuckets[] = {1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256};
 
 size_t up256(size_t x) { return (x + 255) / 256 * 256; }
@@ -104,6 +107,8 @@ struct ModelRunner::Impl {
   __nv_bfloat16* lm_x = nullptr;   // gathered rows for the LM head of ragged prefill steps
   float* lm_partials = nullptr;
   kernels::GemmWorkspace gemm_ws;
+  float* gdn_scratch = nullptr;    // chunked GDN recurrence (prefill): per-chunk U0 / W / P
+  size_t gdn_scratch_floats = 0;
   int32_t* history = nullptr;
   int* history_len = nullptr;
   int32_t* tokens_out = nullptr;
@@ -232,13 +237,16 @@ void ModelRunner::Impl::setup() {
   const size_t nv2 = 2 * size_t(std::max(1, cfg.linear_num_value_heads));
   const size_t gemm_partials = size_t(2) * size_t(dev.num_sms) * 128 * 512;  // stream-K partial tiles of a 512-token pass
   meta = MetaMap(max_tokens, max_rows);
+  gdn_scratch_floats = cfg.linear_num_value_heads > 0 && max_tokens >= kGdnChunkedMinRun
+                           ? kernels::gdn_chunk_scratch_floats(max_tokens, max_rows, cfg.linear_num_value_heads)
+                           : 0;
   const size_t sizes[] = {
       T * H * 4, T * H * 2, T * size_t(cfg.norm_blocks()) * 4, T * size_t(proj_ld) * 2, T * nv2 * 4,
       T * size_t(std::max(128, cfg.gdn_conv_dim())) * 4, T * mixer_w * 2, T * size_t(cfg.intermediate_size) * 2,
       T * size_t(std::max(256, cfg.q_dim())) * 2, R * size_t(V) * 4,
       R * size_t(std::max(1, cfg.num_attention_heads)) * kMaxSplits * (kernels::kHeadDim + 2) * 4, T * 4,
       R * size_t(H) * 2, R * size_t(cfg.norm_blocks()) * 4, gemm_partials * 4, 65536 * 4,
-      R * size_t(opt.history_cap) * 4, R * 4, R * 4, R * 4, T * 4, meta.bytes};
+      R * size_t(opt.history_cap) * 4, R * 4, R * 4, R * 4, T * 4, meta.bytes, gdn_scratch_floats * 4};
   size_t w = 4096;
   for (size_t s : sizes) w += up256(s);
   plan.workspace = w;
@@ -279,6 +287,7 @@ void ModelRunner::Impl::setup() {
   gemm_ws.partials = ws.allocate_array<float>(gemm_partials);
   gemm_ws.partial_floats = gemm_partials;
   gemm_ws.counters = ws.allocate_array<int>(65536);
+  if (gdn_scratch_floats) gdn_scratch = ws.allocate_array<float>(gdn_scratch_floats);
   gemm_ws.num_counters = 65536;
   history = ws.allocate_array<int32_t>(R * size_t(opt.history_cap));
   history_len = ws.allocate_array<int>(R);
@@ -380,7 +389,11 @@ void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool dec
       rp.eps = eps;
       rp.out = mixer;
       rp.gdn_layer = gdn_i;
-      kernels::gdn_recurrence(rp, gd, batch, sd, s);
+      // runs of prefill length take the chunked form (token-parallel preparation + per-chunk state scan)
+      if (gdn_scratch && batch.max_tokens_per_seq >= kGdnChunkedMinRun)
+        kernels::gdn_recurrence_chunked(rp, gd, batch, sd, gdn_scratch, gdn_scratch_floats, s);
+      else
+        kernels::gdn_recurrence(rp, gd, batch, sd, s);
       mark("gdn.recurrence");
       ++gdn_i;
     }

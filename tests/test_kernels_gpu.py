@@ -330,8 +330,9 @@ def test_attention_ragged_batch_gqa4_long_context():
 # ---------------------------------------------------------------------------------------------------
 # Gated DeltaNet
 # ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("nk,nv", [(2, 6), (2, 2)])
-def test_gdn_matches_oracle(nk, nv):
+def test_gdn_matches_oracle(nk, nv, chunked):
     """Chunk lengths {37, 64, 1, 1, 100, 1, 17} on slot 1 of 3, GDN layer 1 of 2; a second sequence runs in
     the same ragged batch on slot 2 with its own lengths."""
     rng = np.random.default_rng(5)
@@ -354,7 +355,7 @@ def test_gdn_matches_oracle(nk, nv):
     ref_state = {1: (np.zeros(nv * 128 * 128, np.float32), np.zeros(3 * conv_dim, np.float32)),
                  2: (np.zeros(nv * 128 * 128, np.float32), np.zeros(3 * conv_dim, np.float32))}
     pos = {1: 0, 2: 0}
-    for n1, n2 in zip((37, 64, 1, 1, 100, 1, 17), (1, 2, 3, 70, 1, 1, 1)):
+    for n1, n2 in zip((37, 64, 1, 1, 100, 1, 17, 300), (1, 2, 3, 70, 1, 1, 1, 129)):
         seqs = [(1, pos[1], n1), (2, pos[2], n2)]
         batch = tl.Batch(seqs)
         n = n1 + n2
@@ -371,7 +372,13 @@ def test_gdn_matches_oracle(nk, nv):
         pkg.check(K().q38_gdn_conv(C.byref(cp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
         rp = pkg.GdnRecurrenceParams(pkg.ptr(qkv), pkg.ptr(ab), pkg.ptr(A_d), pkg.ptr(dt_d), pkg.ptr(proj_d) + conv_dim * 2,
                                      ld, pkg.ptr(nw_d), 1e-6, pkg.ptr(out), layer)
-        pkg.check(K().q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
+        if chunked:  # the 64-token chunked form, also for the short runs (they are padded to a chunk)
+            need = K().q38_gdn_chunk_scratch_floats(n, len(seqs), nv)
+            scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+            pkg.check(K().q38_gdn_recurrence_chunked(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st),
+                                                     pkg.ptr(scratch), need, None))
+        else:
+            pkg.check(K().q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
         sync_ok()
         ab_got = ab.cpu().numpy()
         rs = np.array([o.norm_row_scale(partials[i], H, 1e-6) for i in range(n)], np.float32)
