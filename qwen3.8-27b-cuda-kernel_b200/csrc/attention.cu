@@ -356,15 +356,19 @@ __device__ __forceinline__ uint32_t byte_pair_to_half2(uint32_t wa, uint32_t wb)
 
 __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
     const __half* __restrict__ q, const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ out,
-    int nq, int group, int layer, float* __restrict__ scratch, int max_splits, int num_splits,
-    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0, KvView kv) {
+    int nq, int group, int layer, float* __restrict__ scratch, int max_splits, int num_splits, int decode_rows,
+    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, KvView kv) {
   extern __shared__ __align__(128) uint8_t dsm[];
   uint64_t* full = reinterpret_cast<uint64_t*>(dsm + kMmaStages * kStageBytes);
   uint64_t* empty = full + kMmaStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMmaStages);
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m = seq_start[row], slot = seq_slot[row], L = seq_pos0[row] + 1;
+  // a row is a sequence's single new token (decode) or one prompt token of a chunk with its causal length (prefill)
+  const int m = decode_rows ? seq_start[row] : row;
+  const int slot = decode_rows ? seq_slot[row] : seq_slot[tok_seq[row]];
+  const int L = (decode_rows ? seq_pos0[row] : tok_pos[row]) + 1;
   const int pages = (L + kPage - 1) / kPage;
   const int pages_per_split = (pages + num_splits - 1) / num_splits;
   const int p0 = min(pages, split * pages_per_split), p1 = min(pages, (split + 1) * pages_per_split);
@@ -380,7 +384,8 @@ __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
 
   if (warp == kMmaWarps) {
     if (lane == 0) {
-      const uint64_t pol = policy_evict_first();
+      // decode reads every page once; the prompt tokens of a chunk re-read each other's pages out of L2
+      const uint64_t pol = decode_rows ? policy_evict_first() : policy_evict_normal();
       const int* table = kv.block_table + (size_t)slot * kv.max_pages_per_seq;
       for (int p = p0, it = 0; p < p1; ++p, ++it) {
         const int s = it % kMmaStages;
@@ -692,7 +697,8 @@ extern "C" int q38_attention_decode(const q38_attention_params* p, const q38_bat
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p->out);
   attn_decode_mma_kernel<<<dim3(splits, p->num_kv_heads, batch->num_seqs), kMmaThreads, kMmaSmem, s>>>(
       reinterpret_cast<const __half*>(p->q), gate, p->ld_gate, out, p->num_q_heads, group, p->attn_layer,
-      p->split_scratch, p->max_splits, splits, batch->seq_start, batch->seq_slot, batch->seq_pos0, make_view(*kv));
+      p->split_scratch, p->max_splits, splits, 1, batch->seq_start, batch->seq_slot, batch->seq_pos0, batch->tok_pos,
+      batch->tok_seq, make_view(*kv));
   Q38_LAUNCH_OK("attn_decode_mma_kernel");
   if (splits > 1) {
     attn_merge_kernel<<<dim3(p->num_q_heads, batch->num_seqs), kHd, 0, s>>>(p->split_scratch, p->max_splits, splits, gate,
@@ -708,5 +714,18 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
   const int rc = check_attention(p, batch, kv);
   if (rc != Q38_OK) return rc;
   if (batch->num_tokens == 0) return Q38_OK;
-  return dispatch_group(p->num_q_heads / p->num_kv_heads, *p, *batch, *kv, false, 1, as_stream(stream));
+  const int group = p->num_q_heads / p->num_kv_heads;
+  if (kv->dtype != Q38_KV_INT8) return dispatch_group(group, *p, *batch, *kv, false, 1, as_stream(stream));
+  // int8 KV: the tensor-core kernel, one CTA per (kv head, prompt token); neighbouring tokens walk the same pages, so
+  // all but the first reader of a page are served by L2
+  Q38_REQUIRE(group >= 1 && group <= 8, "attention: GQA group %d is not implemented (1..8)", group);
+  static const cudaError_t attr =
+      cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+  Q38_CUDA_OK(attr);
+  attn_decode_mma_kernel<<<dim3(1, p->num_kv_heads, batch->num_tokens), kMmaThreads, kMmaSmem, as_stream(stream)>>>(
+      reinterpret_cast<const __half*>(p->q), reinterpret_cast<const __nv_bfloat16*>(p->gate), p->ld_gate,
+      reinterpret_cast<__nv_bfloat16*>(p->out), p->num_q_heads, group, p->attn_layer, p->split_scratch, p->max_splits, 1,
+      0, batch->seq_start, batch->seq_slot, batch->seq_pos0, batch->tok_pos, batch->tok_seq, make_view(*kv));
+  Q38_LAUNCH_OK("attn_decode_mma_kernel");
+  return Q38_OK;
 }
