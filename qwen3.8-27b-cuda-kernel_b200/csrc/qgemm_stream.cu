@@ -21,6 +21,8 @@
 //   * A tile segment ends with a fixed-order reduction of the 8 k-warps into a shared C tile; segments
 //     that do not cover all of K go to the workspace and the last-arriving CTA sums them in CTA order
 //     (self-resetting counter): results are bit-reproducible from run to run.
+#include <algorithm>
+
 #include "bq_dequant.cuh"
 #include "common.cuh"
 #include "host_util.h"
@@ -403,14 +405,23 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.units = (long long)a.tiles * a.kg;
   a.dc = decode_consts(BITS);
   const int sms = num_sms();
-  int grid = int(std::min<long long>(sms, std::max<long long>(1, a.units / 8)));
-  const size_t need = (size_t)grid * 2 * C::kMpad * kTileN;
-  a.split = ws && ws->partials && ws->counters && ws->partial_floats >= need && ws->num_counters >= a.tiles;
+  // Cut of the (tile, k-group) list over the CTAs: with fewer tiles than SMs, s = SMs / tiles CTAs per tile and no
+  // CTA spanning two tiles (one fix-up per CTA, s partial tiles per reduction); otherwise an even cut over all SMs.
+  const bool have_ws = ws && ws->partials && ws->counters && ws->num_counters >= a.tiles;
+  int grid;
+  if (a.tiles < sms) {
+    int s = std::max(1, std::min(sms / a.tiles, a.kg / 8));
+    if (!have_ws || ws->partial_floats < (size_t)a.tiles * s * 2 * C::kMpad * kTileN) s = 1;
+    grid = a.tiles * s;
+    a.split = s > 1;
+  } else {
+    grid = sms;
+    a.split = have_ws && ws->partial_floats >= (size_t)grid * 2 * C::kMpad * kTileN;
+    if (!a.split) grid = std::min(sms, a.tiles);
+  }
   if (a.split) {
     a.ws = ws->partials;
     a.counters = ws->counters;
-  } else {
-    grid = std::min(sms, a.tiles);
   }
   qgemm_stream_kernel<BITS, MT><<<grid, kThreads, C::kSmemBytes, stream>>>(xmap, a);
   Q38_LAUNCH_OK("qgemm_stream_kernel");

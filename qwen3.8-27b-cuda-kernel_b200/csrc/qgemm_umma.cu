@@ -618,16 +618,27 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.units = (long long)a.tiles * a.kg;
   a.dc = decode_consts(BITS);
   const int sms = num_sms();
-  int grid = int(std::min<long long>(sms, std::max<long long>(1, a.units / 8)));
-  const size_t need = (size_t)grid * 2 * TOK * kTileN;
-  // stream-K pays a workspace round trip per CTA boundary: only worth it when the tiles alone cannot fill the SMs evenly
-  const bool want_split = a.tiles < 3 * sms || TOK <= 64;
-  a.split = want_split && ws && ws->partials && ws->counters && ws->partial_floats >= need && ws->num_counters >= a.tiles;
+  // How the (tile, k-group) list is cut over the CTAs. Every cut inside a tile costs a partial-tile round trip
+  // through the workspace and a serial sum by the tile's last CTA, so:
+  //   * fewer tiles than SMs: s = SMs / tiles CTAs per tile, every CTA inside one tile (grid = tiles * s makes the
+  //     even cut land on tile boundaries); s is capped where the partial tiles are large;
+  //   * tiles >= SMs: an even cut over all SMs (stream-K) while partial tiles are small, whole tiles otherwise.
+  const bool have_ws = ws && ws->partials && ws->counters && ws->num_counters >= a.tiles;
+  int grid;
+  if (a.tiles < sms) {
+    int s = sms / a.tiles;
+    s = std::min(s, TOK >= 256 ? 3 : 8);
+    s = std::max(1, std::min(s, a.kg / 8));
+    if (!have_ws || ws->partial_floats < (size_t)a.tiles * s * 2 * TOK * kTileN) s = 1;
+    grid = a.tiles * s;
+    a.split = s > 1;
+  } else {
+    grid = sms;
+    a.split = TOK <= 128 && have_ws && ws->partial_floats >= (size_t)grid * 2 * TOK * kTileN;
+  }
   if (a.split) {
     a.ws = ws->partials;
     a.counters = ws->counters;
-  } else {
-    grid = std::min(sms, a.tiles);
   }
   qgemm_umma_kernel<BITS, TOK><<<grid, kThreads, C::kSmemBytes, stream>>>(xmap, a);
   Q38_LAUNCH_OK("qgemm_umma_kernel");
