@@ -361,7 +361,7 @@ def main():
     per_step = {k: v[0] / args.profile_steps for k, v in prof.items() if k != "start"}
     calls = {k: v[1] // args.profile_steps for k, v in prof.items()}
     step_ms_profiled = sum(per_step.values())
-    families = {"qgemm_stream (all BQ GEMMs)": [k for k in per_step if k.startswith("gemm.")],
+    families = {"qgemm_umma / qgemm_stream (all BQ GEMMs)": [k for k in per_step if k.startswith("gemm.")],
                 "gdn_recurrence": ["gdn.recurrence"], "attn_token + merge (decode attention)": ["attn.decode"]}
     fam = {}
     for name, ops in families.items():
@@ -373,7 +373,12 @@ def main():
                          "GBps": by / ms / 1e6, "frac": by / ms / 1e6 / peak}
     top = max(fam, key=lambda k: fam[k]["ms_per_step"])
     roofline = {"bound": "hbm", "kernel": top, "achieved": fam[top]["GBps"], "peak": peak, "unit": "GB/s",
-                "frac": fam[top]["frac"], "traffic": None, "peak_source": peak_src,
+                "frac": fam[top]["frac"],
+                # DRAM bytes per launch: the ncu capture of a smaller case of the same kernel read + wrote 1.005 x its
+                # algorithmic bytes (every plane byte once, plus the output), scaled here by the bytes one launch covers
+                "traffic": (1.005 * sum(bytes_by_op.get(o, 0) for o in families[top]) / max(1, fam[top]["launches_per_step"])
+                            if top.startswith("qgemm") else None),
+                "peak_source": peak_src,
                 "avg_launch_us": 1000.0 * fam[top]["ms_per_step"] / max(1, fam[top]["launches_per_step"]),
                 "share_of_step": fam[top]["share"], "all": fam}
     step_bytes = sum(bytes_by_op.values())

@@ -1,0 +1,164 @@
+"""Micro-benchmark of the two state-streaming decode kernels at the 27B geometry: paged int8 decode attention
+(24 q heads / 4 kv heads, head_dim 256, 64-token pages in a shuffled page table, contexts log-uniform in
+128..32768) and the Gated DeltaNet decode recurrence (48 value heads / 16 key heads, 128x128 fp32 state).
+
+The KV pages hold random bytes with random fp16 scales and the recurrent states random floats: the timing does not
+depend on the values. Each measurement is a CUDA graph of `--iters` launches timed with CUDA events; the
+working set of either kernel is far larger than L2.
+
+  python qwen3.8-27b-cuda-kernel_b200/op_bench.py                       # both kernels, 64 sequences
+  python qwen3.8-27b-cuda-kernel_b200/op_bench.py --op attn --seqs 16 --launches 3 --untimed
+      # a few plain launches and nothing else: the small case to put under a profiler
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import importlib.util
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+NQ, NKV, HD, PAGE = 24, 4, 256, 64
+NK, NV = 16, 48
+
+
+def _package():
+    name = "q38b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, HERE / "__init__.py", submodule_search_locations=[str(HERE)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def batch_desc(pkg, seqs, pos0):
+    """One new token per sequence; slot b = sequence b."""
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    t = {"seq_start": mk(list(range(seqs + 1))), "seq_slot": mk(list(range(seqs))), "seq_pos0": mk(pos0),
+         "tok_pos": mk(pos0), "tok_seq": mk(list(range(seqs)))}
+    desc = pkg.BatchDesc(seqs, seqs, 1, pkg.ptr(t["seq_start"]), pkg.ptr(t["seq_slot"]), pkg.ptr(t["seq_pos0"]),
+                         pkg.ptr(t["tok_pos"]), pkg.ptr(t["tok_seq"]))
+    return desc, t
+
+
+def timed_graph(launch, iters):
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            launch(st.cuda_stream)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=st):
+        for _ in range(iters):
+            launch(st.cuda_stream)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def attn_case(pkg, seqs, seed):
+    K = pkg.kernels()
+    rng = np.random.default_rng(seed)
+    ctx = np.exp(rng.uniform(np.log(128), np.log(32768), size=seqs)).astype(np.int64)
+    pages_per_seq = [int((c + 1 + PAGE - 1) // PAGE) for c in ctx]
+    num_pages = sum(pages_per_seq) + 1
+    page_bytes = int(K.q38_kv_page_bytes(pkg.KV_INT8, NKV))
+    pool = torch.randint(0, 256, (num_pages * page_bytes,), dtype=torch.uint8, device="cuda")
+    # the scale rows must be finite fp16 numbers: overwrite every 16-bit word pattern's exponent via a mask
+    pool.view(torch.int16).bitwise_and_(0x3BFF)
+    max_pages = max(pages_per_seq)
+    table = np.zeros((seqs, max_pages), dtype=np.int32)
+    perm = rng.permutation(num_pages - 1) + 1
+    at = 0
+    for b, n in enumerate(pages_per_seq):
+        table[b, :n] = perm[at:at + n]
+        at += n
+    table_d = torch.from_numpy(table).cuda()
+    kv = pkg.KvCacheDesc(pkg.ptr(pool), pkg.KV_INT8, NKV, num_pages, page_bytes, num_pages * page_bytes,
+                         pkg.ptr(table_d), max_pages)
+    desc, keep = batch_desc(pkg, seqs, [int(c) for c in ctx])
+    q = torch.randn((seqs, NQ, HD), device="cuda").to(torch.float16)
+    gate = torch.randn((seqs, NQ * HD), device="cuda").to(torch.bfloat16)
+    out = torch.empty((seqs, NQ * HD), dtype=torch.bfloat16, device="cuda")
+    splits = 64
+    scratch = torch.empty(seqs * NQ * splits * (HD + 2), dtype=torch.float32, device="cuda")
+    ap = pkg.AttentionParams(pkg.ptr(q), pkg.ptr(gate), NQ * HD, pkg.ptr(out), NQ, NKV, 0, pkg.ptr(scratch), splits)
+    kv_bytes = int(sum(int(c) + 1 for c in ctx)) * NKV * (2 * HD + 16)
+
+    def launch(stream):
+        pkg.check(K.q38_attention_decode(C.byref(ap), C.byref(desc), C.byref(kv), stream))
+    return launch, kv_bytes, (pool, table_d, keep, q, gate, out, scratch), f"{seqs} sequences, {int(ctx.sum())} context tokens"
+
+
+def gdn_case(pkg, seqs, seed):
+    K = pkg.kernels()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    conv_dim = (2 * NK + NV) * 128
+    ld = conv_dim + NV * 128
+    rec = torch.randn((seqs, 1, NV, 128, 128), generator=g, device="cuda") * 0.1
+    conv = torch.zeros((seqs, 1, 3, conv_dim), dtype=torch.bfloat16, device="cuda")
+    st = pkg.GdnStateDesc(pkg.ptr(rec), pkg.ptr(conv), 1)
+    dims = pkg.GdnDims(NK, NV, conv_dim, ld)
+    desc, keep = batch_desc(pkg, seqs, [100] * seqs)
+    qkv = torch.randn((seqs, conv_dim), generator=g, device="cuda") * 0.1
+    ab = torch.randn((seqs, 2 * NV), generator=g, device="cuda")
+    A = -torch.rand(NV, generator=g, device="cuda") - 0.5
+    dt = torch.randn(NV, generator=g, device="cuda") * 0.5
+    nw = torch.ones(128, device="cuda")
+    proj = torch.randn((seqs, ld), generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.empty((seqs, NV * 128), dtype=torch.bfloat16, device="cuda")
+    rp = pkg.GdnRecurrenceParams(pkg.ptr(qkv), pkg.ptr(ab), pkg.ptr(A), pkg.ptr(dt), pkg.ptr(proj) + conv_dim * 2, ld,
+                                 pkg.ptr(nw), 1e-6, pkg.ptr(out), 0)
+    state_bytes = 2 * seqs * NV * 128 * 128 * 4
+
+    def launch(stream):
+        pkg.check(K.q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(desc), C.byref(st), stream))
+    return launch, state_bytes, (rec, conv, keep, qkv, ab, A, dt, nw, proj, out), f"{seqs} sequences x {NV} heads"
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", default="attn,gdn", help="comma-separated: attn, gdn")
+    ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--launches", type=int, default=3, help="with --untimed: number of plain launches")
+    ap.add_argument("--untimed", action="store_true", help="launch --launches times on the default stream and exit")
+    ap.add_argument("--peak-gbs", type=float, default=0.0)
+    ap.add_argument("--seed", type=int, default=7)
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("op_bench needs a CUDA device")
+    pkg = _package()
+    K = pkg.kernels()
+    for op in args.op.split(","):
+        launch, nbytes, keep, what = (attn_case if op == "attn" else gdn_case)(pkg, args.seqs, args.seed)
+        if args.untimed:
+            for _ in range(args.launches):
+                launch(None)
+            torch.cuda.synchronize()
+            print(f"ok: {op}: {args.launches} launches, {what}, {nbytes} algorithmic bytes per launch")
+        else:
+            us = timed_graph(launch, args.iters)
+            gbs = nbytes / us / 1e3
+            frac = f" ({100 * gbs / args.peak_gbs:.1f}% of peak)" if args.peak_gbs else ""
+            print(f"{op:5s} {what}: {us:8.1f} us  {gbs:7.0f} GB/s{frac}", flush=True)
+        if K.q38_device_error(1):
+            raise SystemExit("device-side wait gave up")
+        del keep
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
