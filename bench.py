@@ -344,10 +344,8 @@ def main():
         core_ms = runner.replay_decode_core(B, args.steps)
         torch.cuda.synchronize()
     clock_summary = clocks.summary()
-    times = torch.tensor([e2e_s, core_ms * args.steps / 1000.0], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    e2e_s, core_s = float(times[0]), float(times[1])
+    from q38b200 import sharding
+    e2e_s, core_s = sharding.max_over_ranks([e2e_s, core_ms * args.steps / 1000.0], dist, device="cuda")
     total_tokens = B * world * args.steps
 
     # ---- per-op device times of the same step (eager, CUDA events between kernels) -----------------
@@ -385,7 +383,7 @@ def main():
     launches = sum(calls.get(k, 0) for k in per_step) + calls.get("gdn.conv", 0) + calls.get("attn.decode", 0) + 1
 
     line = {
-        "metric": "decode_tok_per_s", "value": total_tokens / core_s, "unit": "tok/s", "n_gpus": world,
+        "metric": "decode_tok_per_s", "value": sharding.whole_job_rate(B * args.steps, world, core_s), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * core_s / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 x BQ4/5/8 weights, fp32 accumulate", "data": "synthetic", "config": config,
