@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--max-context", type=int, default=8192 + 512 + 1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=3)
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="A/B aid: classic stream order instead of programmatic dependent launch")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: reserve the KV pages but leave them zero-filled (the line is then not a bench value)")
     args = ap.parse_args()
@@ -271,6 +273,9 @@ def main():
         torch.cuda.synchronize()
 
     from q38b200 import engine as eng
+    if args.no_dependent_launch:
+        import q38b200
+        q38b200.kernels().q38_set_dependent_launch(0)
 
     model_path = MODEL_DIR / f"q38_bench_27b_{args.recipe}_L{args.layers}.q38"
     cfg = build_model(model_path, args.layers, args.recipe, rank, world)

@@ -251,6 +251,11 @@ int q38_pack_ragged(const int* seq_count, const int* seq_pos0, int num_seqs, int
 
 /* Diagnostics. */
 const char* q38_last_error(void);           /* message of the last failed launcher call on this thread */
+/* Programmatic dependent launch (on by default): every launcher allows its kernel to be scheduled while the
+ * previous kernel of the stream drains; inside, griddepcontrol.wait precedes the first access to data an earlier
+ * kernel produces, so results do not depend on the setting. Off = classic stream order. Applies to launches (and
+ * graph captures) made after the call. No counterpart in the reference. */
+void q38_set_dependent_launch(int allowed);
 unsigned int q38_device_error(int clear);   /* non-zero if a bounded device-side wait ran out (synchronises) */
 int q38_num_sms(void);                      /* SM count of the current device as cached by the library */
 

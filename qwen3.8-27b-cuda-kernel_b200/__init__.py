@@ -134,6 +134,7 @@ KERNEL_API = {
     "q38_pack_ragged": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_void_p]),
     "q38_last_error": (C.c_char_p, []),
+    "q38_set_dependent_launch": (None, [C.c_int]),
     "q38_device_error": (C.c_uint, [C.c_int]),
     "q38_num_sms": (C.c_int, []),
 }

@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(1024) qk_norm_rope_kernel(const __nv_bfloat16*
                                                             const int* __restrict__ tok_pos,
                                                             const int* __restrict__ tok_seq,
                                                             const int* __restrict__ seq_slot, KvView kv) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp >= nq + 2 * nkv) return;
   const int pos = tok_pos[m];
@@ -178,6 +180,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_token_kernel(
     int nq, int layer, float* __restrict__ scratch, int max_splits, int num_splits, int decode_rows,
     const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, KvView kv) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int m, slot, L;
@@ -359,6 +363,8 @@ __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
     int nq, int group, int layer, float* __restrict__ scratch, int max_splits, int num_splits, int decode_rows,
     const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, KvView kv) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   extern __shared__ __align__(128) uint8_t dsm[];
   uint64_t* full = reinterpret_cast<uint64_t*>(dsm + kMmaStages * kStageBytes);
   uint64_t* empty = full + kMmaStages;
@@ -573,6 +579,8 @@ __global__ void __launch_bounds__(kHd) attn_merge_kernel(const float* __restrict
                                                          int num_splits, const __nv_bfloat16* __restrict__ gate,
                                                          int ld_gate, __nv_bfloat16* __restrict__ out, int nq,
                                                          const int* __restrict__ seq_start) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int qh = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
   const int m = seq_start[row];
   const float* base = scratch + ((size_t)row * nq + qh) * max_splits * (kHd + 2);
@@ -600,16 +608,16 @@ int launch_token_attention(const q38_attention_params& p, const q38_batch_desc& 
   const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p.gate);
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
   if (kv.int8)
-    attn_token_kernel<GROUP, true><<<grid, kAttnWarps * 32, 0, s>>>(
+    (void)launch_kernel(attn_token_kernel<GROUP, true>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 
         q, gate, p.ld_gate, out, p.num_q_heads, p.attn_layer, p.split_scratch, p.max_splits, splits, decode ? 1 : 0,
         b.seq_start, b.seq_slot, b.seq_pos0, b.tok_pos, b.tok_seq, kv);
   else
-    attn_token_kernel<GROUP, false><<<grid, kAttnWarps * 32, 0, s>>>(
+    (void)launch_kernel(attn_token_kernel<GROUP, false>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 
         q, gate, p.ld_gate, out, p.num_q_heads, p.attn_layer, p.split_scratch, p.max_splits, splits, decode ? 1 : 0,
         b.seq_start, b.seq_slot, b.seq_pos0, b.tok_pos, b.tok_seq, kv);
   Q38_LAUNCH_OK("attn_token_kernel");
   if (splits > 1) {
-    attn_merge_kernel<<<dim3(p.num_q_heads, rows), kHd, 0, s>>>(p.split_scratch, p.max_splits, splits, gate, p.ld_gate,
+    (void)launch_kernel(attn_merge_kernel, dim3(p.num_q_heads, rows), dim3(kHd), 0, s, p.split_scratch, p.max_splits, splits, gate, p.ld_gate,
                                                                out, p.num_q_heads, b.seq_start);
     Q38_LAUNCH_OK("attn_merge_kernel");
   }
@@ -659,7 +667,7 @@ extern "C" int q38_qk_norm_rope_append(const q38_qk_norm_rope_params* p, const q
   Q38_REQUIRE(p->ld_proj % 8 == 0, "qk_norm_rope_append: ld_proj must be a multiple of 8");
   RopeTable rope;
   for (int i = 0; i < 32; ++i) rope.inv_freq[i] = 1.0f / std::pow(float(p->rope_theta), float(2 * i) / 64.0f);
-  qk_norm_rope_kernel<<<batch->num_tokens, warps * 32, 0, as_stream(stream)>>>(
+  (void)launch_kernel(qk_norm_rope_kernel, dim3(batch->num_tokens), dim3(warps * 32), 0, as_stream(stream), 
       reinterpret_cast<const __nv_bfloat16*>(p->proj), p->ld_proj, p->q_norm, p->k_norm, p->eps, p->num_q_heads,
       p->num_kv_heads, reinterpret_cast<__half*>(p->q_out), p->attn_layer, rope, batch->tok_pos, batch->tok_seq,
       batch->seq_slot, make_view(*kv));
@@ -695,13 +703,13 @@ extern "C" int q38_attention_decode(const q38_attention_params* p, const q38_bat
   const cudaStream_t s = as_stream(stream);
   const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p->gate);
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p->out);
-  attn_decode_mma_kernel<<<dim3(splits, p->num_kv_heads, batch->num_seqs), kMmaThreads, kMmaSmem, s>>>(
+  (void)launch_kernel(attn_decode_mma_kernel, dim3(splits, p->num_kv_heads, batch->num_seqs), dim3(kMmaThreads), kMmaSmem, s, 
       reinterpret_cast<const __half*>(p->q), gate, p->ld_gate, out, p->num_q_heads, group, p->attn_layer,
       p->split_scratch, p->max_splits, splits, 1, batch->seq_start, batch->seq_slot, batch->seq_pos0, batch->tok_pos,
       batch->tok_seq, make_view(*kv));
   Q38_LAUNCH_OK("attn_decode_mma_kernel");
   if (splits > 1) {
-    attn_merge_kernel<<<dim3(p->num_q_heads, batch->num_seqs), kHd, 0, s>>>(p->split_scratch, p->max_splits, splits, gate,
+    (void)launch_kernel(attn_merge_kernel, dim3(p->num_q_heads, batch->num_seqs), dim3(kHd), 0, s, p->split_scratch, p->max_splits, splits, gate,
                                                                            p->ld_gate, out, p->num_q_heads,
                                                                            batch->seq_start);
     Q38_LAUNCH_OK("attn_merge_kernel");
@@ -722,7 +730,7 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
   static const cudaError_t attr =
       cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
   Q38_CUDA_OK(attr);
-  attn_decode_mma_kernel<<<dim3(1, p->num_kv_heads, batch->num_tokens), kMmaThreads, kMmaSmem, as_stream(stream)>>>(
+  (void)launch_kernel(attn_decode_mma_kernel, dim3(1, p->num_kv_heads, batch->num_tokens), dim3(kMmaThreads), kMmaSmem, as_stream(stream), 
       reinterpret_cast<const __half*>(p->q), reinterpret_cast<const __nv_bfloat16*>(p->gate), p->ld_gate,
       reinterpret_cast<__nv_bfloat16*>(p->out), p->num_q_heads, group, p->attn_layer, p->split_scratch, p->max_splits, 1,
       0, batch->seq_start, batch->seq_slot, batch->seq_pos0, batch->tok_pos, batch->tok_seq, make_view(*kv));

@@ -35,6 +35,11 @@ const DeviceProps& props() {
 }
 }  // namespace
 
+namespace {
+bool g_dependent_launch = true;
+}
+bool dependent_launch_allowed() { return g_dependent_launch; }
+
 int num_sms() { return props().sms > 0 ? props().sms : 1; }
 int max_optin_smem() { return props().smem_optin; }
 
@@ -49,6 +54,8 @@ unsigned int misc_error(bool clear);
 }  // namespace q38
 
 extern "C" const char* q38_last_error(void) { return q38::g_error; }
+
+extern "C" void q38_set_dependent_launch(int allowed) { q38::g_dependent_launch = allowed != 0; }
 
 extern "C" unsigned int q38_device_error(int clear) {
   cudaDeviceSynchronize();

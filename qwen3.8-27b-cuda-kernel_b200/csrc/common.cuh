@@ -32,6 +32,11 @@ static inline unsigned int read_tu_error(bool clear) {
   return v;
 }
 
+// Programmatic dependent launch: let the next kernel of the stream be scheduled / wait until everything the
+// previous kernels of the stream wrote is visible. Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
 // ---- mbarrier -------------------------------------------------------------------------------------

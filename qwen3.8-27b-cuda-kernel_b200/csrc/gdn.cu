@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __rest
                                                      const __nv_bfloat16* __restrict__ w, int rows,
                                                      const float* __restrict__ partials_in, float eps,
                                                      float* __restrict__ ab_out) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   __shared__ float red[8][kAbRows * kAbTokens];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int j0 = blockIdx.x * kAbRows, m0 = blockIdx.y * kAbTokens;
@@ -103,6 +105,8 @@ __global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __re
                                                        const int* __restrict__ seq_start,
                                                        const int* __restrict__ seq_slot,
                                                        const int* __restrict__ tok_seq) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int c = blockIdx.x * 128 + threadIdx.x, m = blockIdx.y;
   const int b = tok_seq[m];
   const int i = m - seq_start[b];  // index of the token inside its sequence's chunk
@@ -138,6 +142,8 @@ __global__ void __launch_bounds__(128) gdn_conv_state_kernel(const __nv_bfloat16
                                                              __nv_bfloat16* __restrict__ conv_state,
                                                              const int* __restrict__ seq_start,
                                                              const int* __restrict__ seq_slot) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int c = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
   const int s = seq_start[b], n = seq_start[b + 1] - s;
   if (n <= 0) return;
@@ -171,6 +177,8 @@ __global__ void __launch_bounds__(kRecWarps * 32, 1) gdn_recurrence_kernel(
     const float* __restrict__ dt_bias, const __nv_bfloat16* __restrict__ z, int ld_z,
     const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
     int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int vh = blockIdx.x, b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s0 = seq_start[b], s1 = seq_start[b + 1];
@@ -294,6 +302,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
     // ------------------------------ producer ------------------------------
     const uint64_t pol = policy_evict_first();
     uint32_t it = 0;
+    bool waited = false;
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
       const int b = item / nv, vh = item - b * nv;
       const int m = seq_start[b];
@@ -314,7 +323,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
       if (lane < 4)
         bulk_g2s(dst + lane * (kDecStateBytes / 4), reinterpret_cast<const uint8_t*>(S) + lane * (kDecStateBytes / 4),
                  kDecStateBytes / 4, &full[slot], pol);
-      else if (lane == 4)
+      if (!waited) {  // the state and the batch metadata are older than the previous kernel; the token rows may not be
+        pdl_wait();
+        waited = true;
+      }
+      if (lane == 4)
         bulk_g2s(dst + kDecQOff, row + (size_t)kh * kDk, 512, &full[slot], pol);
       else if (lane == 5)
         bulk_g2s(dst + kDecKOff, row + (size_t)nk * kDk + (size_t)kh * kDk, 512, &full[slot], pol);
@@ -329,6 +342,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
   }
 
   // ------------------------------ compute warps ------------------------------
+  pdl_wait();
+  pdl_launch_dependents();
   const int row0 = warp * kRowsPerWarp;
   const int tid = threadIdx.x;
   uint32_t it = 0;
@@ -468,6 +483,8 @@ constexpr int kPrepSmemBytes = (2 * kCh * kLd + kCh * kLdP + 3 * kCh) * 4;
 __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_prep_kernel(
     const float* __restrict__ qkv, int conv_dim, const float* __restrict__ ab, const float* __restrict__ A,
     const float* __restrict__ dt_bias, int nk, int nv, const int* __restrict__ seq_start, float* __restrict__ scratch) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   extern __shared__ float prep_sm[];
   float* Ks = prep_sm;
   float* Qs = Ks + kCh * kLd;
@@ -558,16 +575,16 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_prep_kernel(
     }
 #pragma unroll
     for (int i = 1; i < kCh; ++i) {
-      float acc = 0.0f;
+      float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;  // four chains: the row's sum is not one serial dependency
 #pragma unroll
       for (int j0 = 0; j0 < i; j0 += 4) {
         const float4 a4 = *reinterpret_cast<const float4*>(As + i * kLdP + j0);  // entries at j >= i are zero
-        acc += a4.x * x[j0];
-        if (j0 + 1 < i) acc += a4.y * x[j0 + 1];
-        if (j0 + 2 < i) acc += a4.z * x[j0 + 2];
-        if (j0 + 3 < i) acc += a4.w * x[j0 + 3];
+        c0 += a4.x * x[j0];
+        if (j0 + 1 < i) c1 += a4.y * x[j0 + 1];
+        if (j0 + 2 < i) c2 += a4.z * x[j0 + 2];
+        if (j0 + 3 < i) c3 += a4.w * x[j0 + 3];
       }
-      x[i] -= acc;
+      x[i] -= (c0 + c1) + (c2 + c3);
     }
     float* dst = tid < 128 ? U0g + tid : Wg + (tid - 128);
 #pragma unroll
@@ -582,6 +599,8 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
     int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
     const float* __restrict__ scratch) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   extern __shared__ float scan_sm[];
   float* Ss = scan_sm;               // [128 v][kLd]
   float* Ws = Ss + 128 * kLd;        // [64][kLd]
@@ -625,90 +644,101 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
           *reinterpret_cast<const float4*>(in + 2 * kCh * 128 + (size_t)i * 4);
     __syncthreads();
 
-    // thread tile of the [64 tokens][128 v] products: tokens 4 warp + i, v = lane + 32 jj
-    const int t0 = 4 * warp;
-    float acc[4][4];
-    // ---- (a) U = U0 - W S0^T ----
+    // [64 tokens][128 v] products: threads 0-255 compute X = W S0^T, threads 256-511 Y = Q S0^T at the same time.
+    // Thread tile 8 tokens (8 gw + i) x 4 v (lane + 32 jj): 12 shared-memory reads feed 128 FMAs, which keeps the
+    // products FMA-bound instead of shared-memory-bound.
+    const int grp = warp >> 3, gw = warp & 7;  // grp 0: X / upper half of P U, grp 1: Y / lower half + output
+    const int t0 = 8 * gw;
+    float acc[8][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+    {
+      const float* Am = grp == 0 ? Ws : Qs;
 #pragma unroll 2
-    for (int kk = 0; kk < 128; kk += 4) {
-      float4 av[4], bv[4];
+      for (int kk = 0; kk < 128; kk += 4) {
+        float4 bv[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(Ws + (t0 + i) * kLd + kk);
+        for (int jj = 0; jj < 4; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
+        for (int i = 0; i < 8; ++i) {
+          const float4 av = *reinterpret_cast<const float4*>(Am + (t0 + i) * kLd + kk);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          acc[i][jj] += av[i].x * bv[jj].x + av[i].y * bv[jj].y + av[i].z * bv[jj].z + av[i].w * bv[jj].w;
+          for (int jj = 0; jj < 4; ++jj)
+            acc[i][jj] += av.x * bv[jj].x + av.y * bv[jj].y + av.z * bv[jj].z + av.w * bv[jj].w;
+        }
+      }
     }
+    if (grp == 0) {  // (a) U = U0 - X
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) Us[(t0 + i) * kLd + lane + 32 * jj] -= acc[i][jj];
-    __syncthreads();
+        for (int jj = 0; jj < 4; ++jj) Us[(t0 + i) * kLd + lane + 32 * jj] -= acc[i][jj];
+    } else {         // (b) Y scaled by e^{lg_t}
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) acc[i][jj] *= eg_s[t0 + i];
+    }
+    __syncthreads();  // U complete; nobody reads W any more
 
-    // ---- (b) Y = diag(e^lg) Q S0^T, (c) O = Y + P U ----
+    // ---- (c) O = Y + P U. P is lower triangular: tokens 8 gw .. 8 gw + 7 need j < 8 gw + 8; the two thread groups
+    // split that range (group 1 continues on top of Y, group 0 starts from zero and hands its part over through
+    // the W buffer).
+    {
+      const int j_end = 8 * gw + 8;
+      const int j_mid = (j_end / 2) & ~3;
+      const int ja = grp == 0 ? j_mid : 0, jb = grp == 0 ? j_end : j_mid;
+      if (grp == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
-#pragma unroll 2
-    for (int kk = 0; kk < 128; kk += 4) {
-      float4 av[4], bv[4];
+          for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+      }
+      for (int j = ja; j < jb; j += 4) {
+        float uv[4][4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(Qs + (t0 + i) * kLd + kk);
+        for (int q = 0; q < 4; ++q)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
+          for (int jj = 0; jj < 4; ++jj) uv[q][jj] = Us[(j + q) * kLd + lane + 32 * jj];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 8; ++i) {
+          const float4 pv = *reinterpret_cast<const float4*>(Ps + (t0 + i) * kLdP + j);
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          acc[i][jj] += av[i].x * bv[jj].x + av[i].y * bv[jj].y + av[i].z * bv[jj].z + av[i].w * bv[jj].w;
+          for (int jj = 0; jj < 4; ++jj)
+            acc[i][jj] += pv.x * uv[0][jj] + pv.y * uv[1][jj] + pv.z * uv[2][jj] + pv.w * uv[3][jj];
+        }
+      }
+      if (grp == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) Ws[(t0 + i) * kLd + lane + 32 * jj] = acc[i][jj];
+      }
     }
+    __syncthreads();  // group 0's part of P U is in the W buffer; every read of S0 is done
+    if (grp == 1) {
+      // gated RMSNorm over the 128 outputs of each token (a warp holds whole tokens)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 8; ++i) {
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) acc[i][jj] *= eg_s[t0 + i];
-#pragma unroll 2
-    for (int j = 0; j < kCh; j += 4) {
-      float4 pv[4];
+        for (int jj = 0; jj < 4; ++jj) acc[i][jj] += Ws[(t0 + i) * kLd + lane + 32 * jj];
+        const float ss =
+            warp_sum(acc[i][0] * acc[i][0] + acc[i][1] * acc[i][1] + acc[i][2] * acc[i][2] + acc[i][3] * acc[i][3]);
+        const int t = t0 + i;
+        if (t < nc) {
+          const float r = 1.0f / sqrtf(ss / float(kDv) + eps);
+          const size_t m = (size_t)(m0 + t);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (t0 + i) * kLdP + j);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float uv[4];
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) uv[jj] = Us[(j + q) * kLd + lane + 32 * jj];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float pij = q == 0 ? pv[i].x : q == 1 ? pv[i].y : q == 2 ? pv[i].z : pv[i].w;
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) acc[i][jj] += pij * uv[jj];
+          for (int jj = 0; jj < 4; ++jj) {
+            const int d = lane + 32 * jj;
+            const float zz = __bfloat162float(z[m * ld_z + (size_t)vh * kDv + d]);
+            out[m * nv * kDv + (size_t)vh * kDv + d] = __float2bfloat16_rn(acc[i][jj] * r * nw[jj] * silu_f(zz));
+          }
         }
       }
     }
-    // gated RMSNorm over the 128 outputs of each token (a warp holds whole tokens)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float ss = warp_sum(acc[i][0] * acc[i][0] + acc[i][1] * acc[i][1] + acc[i][2] * acc[i][2] + acc[i][3] * acc[i][3]);
-      const int t = t0 + i;
-      if (t < nc) {
-        const float r = 1.0f / sqrtf(ss / float(kDv) + eps);
-        const size_t m = (size_t)(m0 + t);
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int d = lane + 32 * jj;
-          const float zz = __bfloat162float(z[m * ld_z + (size_t)vh * kDv + d]);
-          out[m * nv * kDv + (size_t)vh * kDv + d] = __float2bfloat16_rn(acc[i][jj] * r * nw[jj] * silu_f(zz));
-        }
-      }
-    }
-    __syncthreads();  // every read of S0 is done
 
     // ---- (d) S = e^{lg_C} S0 + U^T Kd: thread tile v = 4 vq + i, k = 4 ko + {0..3} and 64 + 4 ko + {0..3} ----
     {
@@ -767,7 +797,7 @@ extern "C" int q38_gdn_ab(const q38_bf16* xbf, int m, int hidden, const q38_bf16
   Q38_REQUIRE(xbf && w_ab && ab_out, "gdn_ab: null argument");
   Q38_REQUIRE(m > 0 && hidden > 0 && hidden % 128 == 0 && rows > 0, "gdn_ab: m %d hidden %d rows %d", m, hidden, rows);
   const dim3 grid((rows + kAbRows - 1) / kAbRows, (m + kAbTokens - 1) / kAbTokens);
-  gdn_ab_kernel<<<grid, 256, 0, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(xbf), m, hidden,
+  (void)launch_kernel(gdn_ab_kernel, dim3(grid), dim3(256), 0, as_stream(stream), reinterpret_cast<const __nv_bfloat16*>(xbf), m, hidden,
                                                      reinterpret_cast<const __nv_bfloat16*>(w_ab), rows, partials_in, eps,
                                                      ab_out);
   Q38_LAUNCH_OK("gdn_ab_kernel");
@@ -783,11 +813,11 @@ extern "C" int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d,
   const cudaStream_t s = as_stream(stream);
   const __nv_bfloat16* proj = reinterpret_cast<const __nv_bfloat16*>(p->proj);
   __nv_bfloat16* cs = reinterpret_cast<__nv_bfloat16*>(st->conv);
-  gdn_conv_kernel<<<dim3(d->conv_dim / 128, batch->num_tokens), 128, 0, s>>>(
+  (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, batch->num_tokens), dim3(128), 0, s, 
       proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128, p->gdn_layer, st->num_gdn_layers, cs,
       batch->seq_start, batch->seq_slot, batch->tok_seq);
   Q38_LAUNCH_OK("gdn_conv_kernel");
-  gdn_conv_state_kernel<<<dim3(d->conv_dim / 128, batch->num_seqs), 128, 0, s>>>(
+  (void)launch_kernel(gdn_conv_state_kernel, dim3(d->conv_dim / 128, batch->num_seqs), dim3(128), 0, s, 
       proj, d->ld_proj, d->conv_dim, p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot);
   Q38_LAUNCH_OK("gdn_conv_state_kernel");
   return Q38_OK;
@@ -808,14 +838,14 @@ extern "C" int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_
                     reinterpret_cast<uintptr_t>(p->z) % 16 == 0 && reinterpret_cast<uintptr_t>(st->recurrent) % 16 == 0,
                 "gdn_recurrence: rows of qkv, z and the state must be 16-byte aligned");
     const int items = batch->num_seqs * d->num_v_heads;
-    gdn_recurrence_decode_kernel<<<std::min(num_sms(), items), kDecThreads, kDecSmemBytes, as_stream(stream)>>>(
+    (void)launch_kernel(gdn_recurrence_decode_kernel, dim3(std::min(num_sms(), items)), dim3(kDecThreads), kDecSmemBytes, as_stream(stream), 
         p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w,
         p->eps, reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads,
         d->num_v_heads, st->recurrent, batch->seq_start, batch->seq_slot, batch->num_seqs);
     Q38_LAUNCH_OK("gdn_recurrence_decode_kernel");
     return Q38_OK;
   }
-  gdn_recurrence_kernel<<<dim3(d->num_v_heads, batch->num_seqs), kRecWarps * 32, 0, as_stream(stream)>>>(
+  (void)launch_kernel(gdn_recurrence_kernel, dim3(d->num_v_heads, batch->num_seqs), dim3(kRecWarps * 32), 0, as_stream(stream), 
       p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w,
       p->eps, reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads,
       d->num_v_heads, st->recurrent, batch->seq_start, batch->seq_slot);
@@ -849,10 +879,10 @@ extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, co
   Q38_CUDA_OK(attr2);
   const cudaStream_t s = as_stream(stream);
   const int max_chunks = (batch->max_tokens_per_seq + kCh - 1) / kCh;
-  gdn_chunk_prep_kernel<<<dim3(max_chunks, d->num_v_heads, batch->num_seqs), kChunkThreads, kPrepSmemBytes, s>>>(
+  (void)launch_kernel(gdn_chunk_prep_kernel, dim3(max_chunks, d->num_v_heads, batch->num_seqs), dim3(kChunkThreads), kPrepSmemBytes, s, 
       p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, d->num_k_heads, d->num_v_heads, batch->seq_start, scratch);
   Q38_LAUNCH_OK("gdn_chunk_prep_kernel");
-  gdn_chunk_scan_kernel<<<dim3(d->num_v_heads, batch->num_seqs), kChunkThreads, kScanSmemBytes, s>>>(
+  (void)launch_kernel(gdn_chunk_scan_kernel, dim3(d->num_v_heads, batch->num_seqs), dim3(kChunkThreads), kScanSmemBytes, s, 
       p->qkv, d->conv_dim, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w, p->eps,
       reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads, d->num_v_heads,
       st->recurrent, batch->seq_start, batch->seq_slot, scratch);

@@ -45,4 +45,26 @@ int max_optin_smem();
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
+// Every kernel of the library is launched through this helper. With programmatic dependent launch allowed (the
+// default, q38_set_dependent_launch) a kernel may be scheduled while its predecessor in the stream is still
+// draining: its prologue (barrier set-up, TMEM allocation, prefetch of weights, which no kernel writes) overlaps
+// the predecessor's tail, and griddepcontrol.wait inside the kernel holds back everything that touches data the
+// predecessor produces. The attribute is recorded as a programmatic edge when the stream is being captured.
+bool dependent_launch_allowed();  // defined in c_abi.cu
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent_launch_allowed() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace q38

@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(256) embed_kernel(const __nv_bfloat16* __restr
                                                     const int32_t* __restrict__ tokens, int hidden,
                                                     float* __restrict__ residual, __nv_bfloat16* __restrict__ xbf,
                                                     float* __restrict__ partials) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const __nv_bfloat16* row = table + (size_t)tokens[m] * hidden;
   const int blocks = hidden / 128;
@@ -39,6 +41,8 @@ __global__ void __launch_bounds__(1024) pack_ragged_kernel(const int* __restrict
                                                            const int* __restrict__ seq_pos0, int num_seqs,
                                                            int num_tokens, int* __restrict__ seq_start,
                                                            int* __restrict__ tok_pos, int* __restrict__ tok_seq) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   __shared__ int scan[1024];
   __shared__ int carry;
   const int tid = threadIdx.x;
@@ -157,6 +161,8 @@ __device__ uint32_t radix_threshold(const float* logits, int V, uint32_t floor_k
 }
 
 __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(q38_sampling_args a) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   extern __shared__ __align__(16) uint8_t sample_smem[];
   SampleShared& sm = *reinterpret_cast<SampleShared*>(sample_smem);
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -303,6 +309,8 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(q38_sampling_
 __global__ void __launch_bounds__(256) target_logprob_kernel(const float* __restrict__ logits, int ld, int vocab,
                                                              const int32_t* __restrict__ targets,
                                                              float* __restrict__ out) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   __shared__ float red_f[8];
   __shared__ double red_d[8];
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -340,7 +348,7 @@ extern "C" int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, in
   if (m == 0) return Q38_OK;
   Q38_REQUIRE(table && tokens && residual && xbf && partials, "embed: null argument");
   Q38_REQUIRE(m > 0 && hidden > 0 && hidden % 128 == 0, "embed: m %d hidden %d", m, hidden);
-  embed_kernel<<<m, 256, 0, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(table), tokens, hidden,
+  (void)launch_kernel(embed_kernel, dim3(m), dim3(256), 0, as_stream(stream), reinterpret_cast<const __nv_bfloat16*>(table), tokens, hidden,
                                                  residual, reinterpret_cast<__nv_bfloat16*>(xbf), partials);
   Q38_LAUNCH_OK("embed_kernel");
   return Q38_OK;
@@ -351,7 +359,7 @@ extern "C" int q38_pack_ragged(const int* seq_count, const int* seq_pos0, int nu
   if (num_seqs == 0) return Q38_OK;
   Q38_REQUIRE(seq_count && seq_pos0 && seq_start && tok_pos && tok_seq, "pack_ragged: null argument");
   Q38_REQUIRE(num_seqs > 0 && num_tokens >= 0, "pack_ragged: sizes");
-  pack_ragged_kernel<<<1, 1024, 0, as_stream(stream)>>>(seq_count, seq_pos0, num_seqs, num_tokens, seq_start,
+  (void)launch_kernel(pack_ragged_kernel, dim3(1), dim3(1024), 0, as_stream(stream), seq_count, seq_pos0, num_seqs, num_tokens, seq_start,
                                                         tok_pos, tok_seq);
   Q38_LAUNCH_OK("pack_ragged_kernel");
   return Q38_OK;
@@ -365,7 +373,7 @@ extern "C" int q38_sample(const q38_sampling_args* a, int batch, void* stream) {
   static const cudaError_t attr =
       cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(SampleShared)));
   Q38_CUDA_OK(attr);
-  sample_kernel<<<batch, kSampleThreads, sizeof(SampleShared), as_stream(stream)>>>(*a);
+  (void)launch_kernel(sample_kernel, dim3(batch), dim3(kSampleThreads), sizeof(SampleShared), as_stream(stream), *a);
   Q38_LAUNCH_OK("sample_kernel");
   return Q38_OK;
 }
@@ -374,7 +382,7 @@ extern "C" int q38_target_logprobs(const float* logits, int ld, int vocab, const
                                    float* out, void* stream) {
   if (rows == 0) return Q38_OK;
   Q38_REQUIRE(logits && targets && out && vocab > 0, "target_logprobs: arguments");
-  target_logprob_kernel<<<rows, 256, 0, as_stream(stream)>>>(logits, ld, vocab, targets, out);
+  (void)launch_kernel(target_logprob_kernel, dim3(rows), dim3(256), 0, as_stream(stream), logits, ld, vocab, targets, out);
   Q38_LAUNCH_OK("target_logprob_kernel");
   return Q38_OK;
 }

@@ -43,6 +43,8 @@ int auto_config(int m, const q38_bq_weight& w, const q38_gemm_workspace* ws) {
 template <int BITS>
 __global__ void bq_dequant_kernel(const uint8_t* __restrict__ lo, const uint8_t* __restrict__ hi,
                                   const uint8_t* __restrict__ sc, int n, int k, __nv_bfloat16* __restrict__ out) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   using G = BqGeom<BITS>;
   const int lane = threadIdx.x & 31;
   const long long slab = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -132,10 +134,10 @@ extern "C" int q38_bq_dequant(const q38_bq_weight* w, q38_bf16* out, void* strea
   __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
   const cudaStream_t s = as_stream(stream);
   switch (w->bits) {
-    case 4: bq_dequant_kernel<4><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
-    case 5: bq_dequant_kernel<5><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
-    case 6: bq_dequant_kernel<6><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
-    case 8: bq_dequant_kernel<8><<<grid, warps * 32, 0, s>>>(w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 4: (void)launch_kernel(bq_dequant_kernel<4>, dim3(grid), dim3(warps * 32), 0, s, w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 5: (void)launch_kernel(bq_dequant_kernel<5>, dim3(grid), dim3(warps * 32), 0, s, w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 6: (void)launch_kernel(bq_dequant_kernel<6>, dim3(grid), dim3(warps * 32), 0, s, w->lo, w->hi, sc, w->n, w->k, o); break;
+    case 8: (void)launch_kernel(bq_dequant_kernel<8>, dim3(grid), dim3(warps * 32), 0, s, w->lo, w->hi, sc, w->n, w->k, o); break;
     default: Q38_REQUIRE(false, "bq_dequant: unsupported bit width %d", w->bits);
   }
   Q38_LAUNCH_OK("bq_dequant_kernel");

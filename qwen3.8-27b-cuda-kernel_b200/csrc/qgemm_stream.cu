@@ -99,6 +99,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 template <int BITS, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   using C = Cfg<BITS, MT>;
   using G = BqGeom<BITS>;
   extern __shared__ uint8_t smem_raw[];
@@ -423,7 +425,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
     a.ws = ws->partials;
     a.counters = ws->counters;
   }
-  qgemm_stream_kernel<BITS, MT><<<grid, kThreads, C::kSmemBytes, stream>>>(xmap, a);
+  (void)launch_kernel(qgemm_stream_kernel<BITS, MT>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, xmap, a);
   Q38_LAUNCH_OK("qgemm_stream_kernel");
   return Q38_OK;
 }

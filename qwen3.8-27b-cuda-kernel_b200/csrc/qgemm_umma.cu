@@ -252,7 +252,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     }
   } else if (warp == 2) {
     // ------------------------------ activation producer ------------------------------
+    // The first thread of the CTA that touches data of earlier kernels: until here the CTA only set itself up and
+    // prefetched / decoded weights, which overlaps the previous kernel's tail under programmatic dependent launch.
     if (lane == 0) {
+      pdl_wait();
+      pdl_launch_dependents();
       uint32_t uc = 0;
       bool alive = true;
       for (long long u = u0; u < u1 && alive;) {
@@ -324,13 +328,14 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     const int dnb = (dw >> 2) & 1;     // 64-column block of the tile
     const int ks = dw & 3;             // its k16 slab of the group
     const int gl = lane >> 2, tl = lane & 3;
-    const DecodeConsts dc = a.dc;
+    DecodeConsts dc;  // in registers: a logic instruction takes only one operand from the constant bank
+    asm volatile("mov.b32 %0, %1;" : "=r"(dc.nib) : "r"(a.dc.nib));
+    asm volatile("mov.b32 %0, %1;" : "=r"(dc.magic) : "r"(a.dc.magic));
+    asm volatile("mov.b32 %0, %1;" : "=r"(dc.himask) : "r"(a.dc.himask));
     const int quarter = dw & 3;        // TMEM lanes this warp may read (warp index modulo 4)
     const int cchunk = dw >> 2;        // which chunk of the token columns it handles in the epilogue
     const bool epi_active = cchunk < C::kEpiChunks;
     const int et = tid - kFirstDecodeWarp * 32;  // 0..511 among the decode threads
-    row_scales_to_smem(a.partials_in, a.m, TOK, a.hidden, a.eps, rs_sm, et, kDecodeThreads);
-    named_bar_sync(1, kDecodeThreads);
     // destination of pair (j, h) of slab ks: row 64 dnb + 8 j + gl, 16-byte chunk (2 ks + h) ^ gl
     const uint32_t row_off = uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
     const uint32_t c0_off = row_off + (uint32_t((2 * ks) ^ gl) << 4);
@@ -373,14 +378,26 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         *reinterpret_cast<uint32_t*>(base + c1_off + j * 1024) = w[2 * j + 1];
       }
     };
-    uint32_t it = 0, unit_ctr = 0, seg = 0;
+    // ring positions are carried along (slot + phase bit) instead of being derived from counters by division
+    uint32_t seg = 0;
+    int s = 0;                   // raw stage and the parity of its current use
+    uint32_t s_par = 0;
+    int u_slot = 0;              // operand slot of the first unit of the current stage, parity of its current use
+    uint32_t u_par = 0;
+    auto unit_at = [&](int delta, int& slot, uint32_t& par) {  // ring position `delta` units after (u_slot, u_par)
+      slot = u_slot + delta;
+      par = u_par;
+      while (slot >= C::kUnits) {
+        slot -= C::kUnits;
+        par ^= 1u;
+      }
+    };
     for (long long u = u0; u < u1; ++seg) {
       const int tile = int(u / a.kg), kg_a = int(u % a.kg);
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
-      for (int g = kg_a; g < kg_b; g += kGroupsPerStage, ++it) {
-        const int s = it % C::kStages;
+      for (int g = kg_a; g < kg_b; g += kGroupsPerStage) {
         const int ng = min(kGroupsPerStage, kg_b - g);
-        const bool ok = wait_flag(&raw_full[s], (it / C::kStages) & 1, flags, 0x305);
+        const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
         const int g0 = C::kSpu == 2 ? 2 * half : half;  // first of this warp's two k-groups of the stage
         constexpr int kGStep = C::kSpu == 2 ? 1 : 2;      // distance to its second one
@@ -396,9 +413,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           expand_scales(sv0, s2);
           decode_slab<BITS>(lo0, hi0, s2, w, dc);
           if constexpr (C::kSpu == 2) {
-            const uint32_t uc = unit_ctr + uint32_t(half);
-            const int slot = uc % C::kUnits;
-            const bool free_slot = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x306);
+            int slot;
+            uint32_t par;
+            unit_at(half, slot, par);
+            const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
             uint8_t* base = units + (size_t)slot * C::kUnitBytes;
             if (ok && free_slot) store_slice(base, w);
             if (two) {
@@ -417,9 +435,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                   expand_scales(sv1, s2);
                   decode_slab<BITS>(lo1, hi1, s2, w, dc);
                 }
-                const uint32_t uc = unit_ctr + uint32_t(g0 + kGStep * e);
-                const int slot = uc % C::kUnits;
-                const bool free_slot = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x306);
+                int slot;
+                uint32_t par;
+                unit_at(g0 + kGStep * e, slot, par);
+                const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
                 if (ok && free_slot) store_slice(units + (size_t)slot * C::kUnitBytes, w);
                 fence_async_smem();
                 __syncwarp();
@@ -430,12 +449,21 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[s]);
-        unit_ctr += uint32_t((ng + C::kSpu - 1) / C::kSpu);
+        if (++s == C::kStages) {
+          s = 0;
+          s_par ^= 1u;
+        }
+        unit_at((ng + C::kSpu - 1) / C::kSpu, u_slot, u_par);
       }
 
       // ---- epilogue of this tile segment ----
       const bool got = __all_sync(0xffffffffu, wait_flag(acc_full, seg & 1, flags, 0x307));
       tc_fence_after();
+      if (seg == 0) {  // first use of activations-side data by these warps: the row scales of the folded RMSNorm
+        pdl_wait();
+        row_scales_to_smem(a.partials_in, a.m, TOK, a.hidden, a.eps, rs_sm, et, kDecodeThreads);
+        named_bar_sync(1, kDecodeThreads);
+      }
       const bool whole = kg_a == 0 && kg_b == a.kg;
       const int n_row = 32 * quarter + lane;  // row of the tile this thread reads from TMEM
       const int n_glob = tile * kTileN + n_row;
@@ -640,7 +668,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
     a.ws = ws->partials;
     a.counters = ws->counters;
   }
-  qgemm_umma_kernel<BITS, TOK><<<grid, kThreads, C::kSmemBytes, stream>>>(xmap, a);
+  (void)launch_kernel(qgemm_umma_kernel<BITS, TOK>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, xmap, a);
   Q38_LAUNCH_OK("qgemm_umma_kernel");
   return Q38_OK;
 }

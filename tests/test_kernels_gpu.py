@@ -166,6 +166,20 @@ def test_qgemm_27b_shapes(n, k, bits):
     sync_ok()
 
 
+@pytest.mark.parametrize("bits", [4, 5, 6, 8])
+def test_quantiser_on_gpu_equals_cpu(bits):
+    """The MSE-search quantiser (reference tools/bqpack.py:40-102) is plain tensor arithmetic: run on the GPU it must
+    give the codes and scales of the CPU run (which the golden fixtures pin to the reference's bytes)."""
+    g = torch.Generator().manual_seed(100 + bits)
+    w = torch.randn((384, 1024), generator=g) * 0.02
+    w[5, 64:128] = 0.0          # a dead group
+    w[7, 0] = 3.0               # an outlier
+    c_cpu, s_cpu = bq.quantize_matrix(w, bits)
+    c_gpu, s_gpu = bq.quantize_matrix(w.cuda(), bits)
+    assert torch.equal(s_gpu.cpu(), s_cpu)
+    assert torch.equal(c_gpu.cpu(), c_cpu)
+
+
 # ---------------------------------------------------------------------------------------------------
 # embed, ragged packing
 # ---------------------------------------------------------------------------------------------------
