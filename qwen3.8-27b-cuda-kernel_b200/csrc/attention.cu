@@ -378,6 +378,14 @@ __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
   const int pages = (L + kPage - 1) / kPage;
   const int pages_per_split = (pages + num_splits - 1) / num_splits;
   const int p0 = min(pages, split * pages_per_split), p1 = min(pages, (split + 1) * pages_per_split);
+  if (p0 >= p1 && num_splits > 1) {  // a split beyond this sequence's pages: an empty state for the merge, nothing else
+    if (tid < group) {
+      float* dst = scratch + (((size_t)row * nq + (size_t)kvh * group + tid) * max_splits + split) * (kHd + 2);
+      dst[kHd] = -INFINITY;
+      dst[kHd + 1] = 0.0f;
+    }
+    return;
+  }
   if (tid == 0) {
     for (int s = 0; s < kMmaStages; ++s) {
       mbar_init(&full[s], 1);
@@ -590,7 +598,8 @@ __global__ void __launch_bounds__(kHd) attn_merge_kernel(const float* __restrict
   for (int s = 0; s < num_splits; ++s) {
     const float* p = base + (size_t)s * (kHd + 2);
     const float ms = p[kHd];
-    const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+    if (ms == -INFINITY) continue;  // an empty split: its accumulator row was never written
+    const float c = exp2f(ms - mm);
     ll += p[kHd + 1] * c;
     a += p[d] * c;
   }
@@ -675,11 +684,14 @@ extern "C" int q38_qk_norm_rope_append(const q38_qk_norm_rope_params* p, const q
   return Q38_OK;
 }
 
-// Split count of the decode launcher: enough CTAs for two waves over the SMs, at most max_splits.
+// Split count of the decode launcher. Context lengths of a ragged batch differ by orders of magnitude and the count is
+// fixed per captured graph, so it is chosen for balance, not for occupancy: about sixteen work items per SM, so
+// that the longest sequence's share per CTA is small against the whole step; splits beyond a short sequence's
+// pages cost one early-exiting CTA each.
 extern "C" int q38_attention_decode_splits(int batch_seqs, int kv_heads, int num_sms, int max_splits) {
   const int ctas = batch_seqs * kv_heads;
   if (ctas <= 0) return 1;
-  int s = (2 * num_sms + ctas - 1) / ctas;
+  int s = (16 * num_sms + ctas - 1) / ctas;
   if (s < 1) s = 1;
   if (s > max_splits) s = max_splits;
   if (s > 64) s = 64;

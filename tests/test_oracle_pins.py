@@ -185,4 +185,8 @@ def test_c_abi_library_exports_every_declared_symbol():
         assert hasattr(lib, name), name
     assert lib.q38_qgemm_num_configs() >= 4
     assert lib.q38_kv_page_bytes(0, 4) == 135168
-    assert lib.q38_attention_decode_splits(64, 4, 148, 64) == 2
+    # about sixteen (sequence, kv head, split) work items per SM, within [1, max_splits]
+    assert lib.q38_attention_decode_splits(64, 4, 148, 64) == 10
+    assert lib.q38_attention_decode_splits(1, 4, 148, 64) == 64
+    assert lib.q38_attention_decode_splits(4096, 4, 148, 64) == 1
+    assert lib.q38_attention_decode_splits(64, 4, 148, 4) == 4
