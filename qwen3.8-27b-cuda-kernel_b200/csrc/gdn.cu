@@ -101,23 +101,29 @@ __global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __rest
 __global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
                                                        const float* __restrict__ conv_w, float* __restrict__ qkv,
                                                        int conv_dim, int key_dim, int layer, int num_layers,
-                                                       const __nv_bfloat16* __restrict__ conv_state,
+                                                       __nv_bfloat16* __restrict__ conv_state,
                                                        const int* __restrict__ seq_start,
                                                        const int* __restrict__ seq_slot,
-                                                       const int* __restrict__ tok_seq) {
+                                                       const int* __restrict__ tok_seq, int roll_state) {
   pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
   pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int c = blockIdx.x * 128 + threadIdx.x, m = blockIdx.y;
   const int b = tok_seq[m];
   const int i = m - seq_start[b];  // index of the token inside its sequence's chunk
-  const __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
+  __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
   const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)c * 4);
   float x[4];
+  __nv_bfloat16 xb[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {  // x[j] = input 3 - j steps back
     const int back = 3 - j;
-    x[j] = back <= i ? __bfloat162float(proj[(size_t)(m - back) * ld_proj + c])
-                     : __bfloat162float(st[(size_t)(3 + i - back) * conv_dim + c]);
+    xb[j] = back <= i ? proj[(size_t)(m - back) * ld_proj + c] : st[(size_t)(3 + i - back) * conv_dim + c];
+    x[j] = __bfloat162float(xb[j]);
+  }
+  if (roll_state) {  // one token per sequence: this thread is the only reader of its channel's taps, so it also rolls them
+    st[c] = xb[1];
+    st[(size_t)conv_dim + c] = xb[2];
+    st[(size_t)2 * conv_dim + c] = xb[3];
   }
   float acc = 0.0f;
   acc += w.x * x[0];
@@ -813,10 +819,14 @@ extern "C" int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d,
   const cudaStream_t s = as_stream(stream);
   const __nv_bfloat16* proj = reinterpret_cast<const __nv_bfloat16*>(p->proj);
   __nv_bfloat16* cs = reinterpret_cast<__nv_bfloat16*>(st->conv);
+  // decode batches (one token per sequence) roll the conv state inside the conv kernel; longer runs need the second
+  // kernel, because the first three tokens of a run all read the old taps
+  const int roll = batch->max_tokens_per_seq == 1 ? 1 : 0;
   (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, batch->num_tokens), dim3(128), 0, s, 
       proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128, p->gdn_layer, st->num_gdn_layers, cs,
-      batch->seq_start, batch->seq_slot, batch->tok_seq);
+      batch->seq_start, batch->seq_slot, batch->tok_seq, roll);
   Q38_LAUNCH_OK("gdn_conv_kernel");
+  if (roll) return Q38_OK;
   (void)launch_kernel(gdn_conv_state_kernel, dim3(d->conv_dim / 128, batch->num_seqs), dim3(128), 0, s, 
       proj, d->ld_proj, d->conv_dim, p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot);
   Q38_LAUNCH_OK("gdn_conv_state_kernel");

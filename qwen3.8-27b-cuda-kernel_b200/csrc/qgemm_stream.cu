@@ -408,7 +408,8 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.dc = decode_consts(BITS);
   const int sms = num_sms();
   // Cut of the (tile, k-group) list over the CTAs: with fewer tiles than SMs, s = SMs / tiles CTAs per tile and no
-  // CTA spanning two tiles (one fix-up per CTA, s partial tiles per reduction); otherwise an even cut over all SMs.
+  // CTA spanning two tiles (one fix-up per CTA, s partial tiles per reduction); with up to four tiles per SM whole
+  // tiles; otherwise an even cut over all SMs (stream-K).
   const bool have_ws = ws && ws->partials && ws->counters && ws->num_counters >= a.tiles;
   int grid;
   if (a.tiles < sms) {
@@ -419,6 +420,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   } else {
     grid = sms;
     a.split = have_ws && ws->partial_floats >= (size_t)grid * 2 * C::kMpad * kTileN;
+    if (a.tiles < 4 * sms) a.split = 0;  // a few tiles per CTA: two fix-ups per CTA cost more than the uneven last wave
     if (!a.split) grid = std::min(sms, a.tiles);
   }
   if (a.split) {

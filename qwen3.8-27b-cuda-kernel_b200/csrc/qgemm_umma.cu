@@ -650,7 +650,8 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   // through the workspace and a serial sum by the tile's last CTA, so:
   //   * fewer tiles than SMs: s = SMs / tiles CTAs per tile, every CTA inside one tile (grid = tiles * s makes the
   //     even cut land on tile boundaries); s is capped where the partial tiles are large;
-  //   * tiles >= SMs: an even cut over all SMs (stream-K) while partial tiles are small, whole tiles otherwise.
+  //   * tiles >= SMs: whole tiles while a CTA gets fewer than four of them or the partial tiles are large (>= 256
+  //     tokens), an even cut over all SMs (stream-K) otherwise.
   const bool have_ws = ws && ws->partials && ws->counters && ws->num_counters >= a.tiles;
   int grid;
   if (a.tiles < sms) {
@@ -663,6 +664,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   } else {
     grid = sms;
     a.split = TOK <= 128 && have_ws && ws->partial_floats >= (size_t)grid * 2 * TOK * kTileN;
+    if (a.tiles < 4 * sms) a.split = 0;  // a few tiles per CTA: two fix-ups per CTA cost more than the uneven last wave
   }
   if (a.split) {
     a.ws = ws->partials;
