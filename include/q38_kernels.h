@@ -127,6 +127,12 @@ int q38_bq_dequant(const q38_bq_weight* w, q38_bf16* out, void* stream);
 int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, int hidden, float* residual, q38_bf16* xbf,
               float* partials, void* stream);
 
+/* The Residual GEMM epilogue as an op of its own: residual += delta, xbf = bf16(residual), partials[m][col / 128] =
+ * sum of squares. For tensor-parallel runs, where the row-parallel projections store fp32 partial products
+ * (Q38_EPI_STORE_F32) that are summed over the ranks first. No counterpart in the reference (single GPU). */
+int q38_residual_update(const float* delta, int m, int hidden, float* residual, q38_bf16* xbf, float* partials,
+                        void* stream);
+
 /* kernels::QkNormRopeParams + qk_norm_rope_append, kernels.h:140-155 */
 typedef struct q38_qk_norm_rope_params {
   const q38_bf16* proj; /* [M][ld_proj]: [q | gate | k | v] */

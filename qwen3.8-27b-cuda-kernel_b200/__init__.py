@@ -113,6 +113,7 @@ KERNEL_API = {
     "q38_set_qgemm_tuning": (None, [C.c_void_p]),
     "q38_bq_dequant": (C.c_int, [C.POINTER(BQWeight), C.c_void_p, C.c_void_p]),
     "q38_embed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "q38_residual_update": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "q38_qk_norm_rope_append": (C.c_int, [C.POINTER(QkNormRopeParams), C.POINTER(BatchDesc), C.POINTER(KvCacheDesc),
                                           C.c_void_p]),
     "q38_attention_decode_splits": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),

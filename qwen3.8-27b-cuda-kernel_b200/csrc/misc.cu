@@ -34,6 +34,39 @@ __global__ void __launch_bounds__(256) embed_kernel(const __nv_bfloat16* __restr
 }
 
 // ---------------------------------------------------------------------------------------------------
+// residual_update: the Residual GEMM epilogue as an op of its own, for tensor-parallel runs in which the
+// row-parallel projection's partial products are summed over the ranks before they may enter the residual:
+// residual += delta; xbf = bf16(residual); partials[m][col / 128] = sum of residual^2 over the 128 columns.
+// One warp per (token, 128-column block), as embed_kernel.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) residual_update_kernel(const float* __restrict__ delta, int hidden,
+                                                              float* __restrict__ residual,
+                                                              __nv_bfloat16* __restrict__ xbf,
+                                                              float* __restrict__ partials) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blocks = hidden / 128;
+  for (int b = warp; b < blocks; b += blockDim.x >> 5) {
+    const size_t at = (size_t)m * hidden + b * 128 + 4 * lane;
+    const float4 d = *reinterpret_cast<const float4*>(delta + at);
+    float4 r = *reinterpret_cast<const float4*>(residual + at);
+    r.x += d.x;
+    r.y += d.y;
+    r.z += d.z;
+    r.w += d.w;
+    *reinterpret_cast<float4*>(residual + at) = r;
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(r.x, r.y), p1 = __floats2bfloat162_rn(r.z, r.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&p0);
+    packed.y = *reinterpret_cast<const uint32_t*>(&p1);
+    *reinterpret_cast<uint2*>(xbf + at) = packed;
+    const float ss = warp_sum(r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w);
+    if (lane == 0) partials[(size_t)m * blocks + b] = ss;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
 // pack_ragged: per-sequence (count, pos0) -> seq_start (exclusive scan), tok_pos, tok_seq.
 // One CTA; the scan is a shared-memory Hillis-Steele over up to 1024 sequences per pass.
 // ---------------------------------------------------------------------------------------------------
@@ -351,6 +384,17 @@ extern "C" int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, in
   (void)launch_kernel(embed_kernel, dim3(m), dim3(256), 0, as_stream(stream), reinterpret_cast<const __nv_bfloat16*>(table), tokens, hidden,
                                                  residual, reinterpret_cast<__nv_bfloat16*>(xbf), partials);
   Q38_LAUNCH_OK("embed_kernel");
+  return Q38_OK;
+}
+
+extern "C" int q38_residual_update(const float* delta, int m, int hidden, float* residual, q38_bf16* xbf,
+                                   float* partials, void* stream) {
+  if (m == 0) return Q38_OK;
+  Q38_REQUIRE(delta && residual && xbf && partials, "residual_update: null argument");
+  Q38_REQUIRE(m > 0 && hidden > 0 && hidden % 128 == 0, "residual_update: m %d hidden %d", m, hidden);
+  (void)launch_kernel(residual_update_kernel, dim3(m), dim3(256), 0, as_stream(stream), delta, hidden, residual,
+                      reinterpret_cast<__nv_bfloat16*>(xbf), partials);
+  Q38_LAUNCH_OK("residual_update_kernel");
   return Q38_OK;
 }
 

@@ -1,0 +1,121 @@
+"""Tensor-parallel runner against the reference model's logits: the same tiny model as the engine tests, run through
+TPRunner on one rank (sharding code path without all-reduce) and on two ranks over NCCL."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+GOLD = ROOT / "tests" / "golden"
+pytestmark = pytest.mark.gpu
+
+
+def _check_against_golden(runner, tag, seq, graph_from=16, log=None):
+    gold = np.load(GOLD / "tiny_cfg1_golden.npz")
+    prompt, gen = gold[f"prompt{seq}"], gold[f"gen{tag}{seq}"]
+    ref = gold[f"logits{tag}{seq}"].astype(np.float32)
+    rel = lambda got, want: float(np.abs(got - want).max() / np.abs(want).max())
+    say = log or (lambda *a: None)
+    runner.forward(prompt, 0)
+    worst = rel(runner.logits(), ref[len(prompt) - 1])
+    say(f"prefill rel {worst:.3e}")
+    agree = 0
+    for step in range(len(gen)):
+        pos = len(prompt) + step
+        if step < graph_from:
+            runner.forward([int(gen[step])], pos)      # eager launches
+        else:
+            runner.decode_replay(int(gen[step]), pos)  # captured step (kernels + all-reduces)
+        got = runner.logits()
+        say(f"step {step} rel {rel(got, ref[pos]):.3e}")
+        worst = max(worst, rel(got, ref[pos]))
+        agree += int(got.argmax() == ref[pos].argmax())
+    assert runner.device_error() == 0
+    assert worst <= 2e-2, worst
+    assert agree >= 0.9 * len(gen), agree
+    return worst, agree
+
+
+def test_single_rank_tp_runner_matches_reference():
+    import __graft_entry__ as entry
+    entry.load_package()
+    import q38b200
+    from q38b200 import tp
+    for tag in ("", "_unit"):
+        runner = tp.TPRunner(q38b200, GOLD / f"tiny_cfg1{tag}.q38", max_tokens=256, max_context=512)
+        worst, agree = _check_against_golden(runner, tag, 3)
+        print(f"tp x1{tag}: rel_max {worst:.3e}, top-1 {agree}/32")
+        assert worst <= 2e-2
+
+
+def _worker(rank, world, port, out_dir, graph_from):
+    logf = open(Path(out_dir) / f"rank{rank}.log", "w")
+
+    def log(*a):
+        print(*a, file=logf, flush=True)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import __graft_entry__ as entry
+    entry.load_package()
+    import q38b200
+    from q38b200 import tp
+    log("process group up")
+    runner = tp.TPRunner(q38b200, GOLD / "tiny_cfg1_unit.q38", rank, world, dist, max_tokens=256, max_context=512)
+    log("runner built")
+    worst, agree = _check_against_golden(runner, "_unit", 3, graph_from=graph_from, log=log)
+    log("checked", worst, agree)
+    assert runner.reduce_calls > 0
+    runner.close()
+    del runner
+    log("closed")
+    dist.barrier()
+    log("barrier passed")
+    dist.destroy_process_group()
+    (Path(out_dir) / f"ok{rank}").write_text(f"{worst:.3e} {agree}")
+
+
+def _log_dir(tmp_path, name):
+    out = ROOT / "gpurun_out"
+    d = out / name if out.is_dir() else tmp_path
+    d.mkdir(exist_ok=True)
+    return d
+
+
+@pytest.mark.timeout(150)
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("graph_from", [99, 8], ids=["eager", "graph"])
+def test_two_rank_tp_runner_matches_reference(tmp_path, graph_from):
+    """Two NCCL ranks; "graph" replays the decode step (kernels and all-reduces) as a CUDA graph from step 8 on."""
+    import torch.multiprocessing as mp
+    world, port = 2, 29100 + (os.getpid() + graph_from) % 2000
+    d = _log_dir(tmp_path, f"tp2_{graph_from}")
+    mp.spawn(_worker, args=(world, port, str(d), graph_from), nprocs=world, join=True)
+    print([(d / f"ok{r}").read_text() for r in range(world)])
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("rank", [0, 1])
+def test_rank_shard_shapes_run_without_a_process_group(rank):
+    """The kernels on one rank's shard shapes of a two-way split (k ranges of 128..512, two-tile projections), without
+    the all-reduce: values are partial sums, so only completion, finiteness and the device error word are checked."""
+    import __graft_entry__ as entry
+    entry.load_package()
+    import q38b200
+    from q38b200 import tp
+    gold = np.load(GOLD / "tiny_cfg1_golden.npz")
+    runner = tp.TPRunner(q38b200, GOLD / "tiny_cfg1_unit.q38", rank, 2, None, max_tokens=256, max_context=512)
+    runner.forward(gold["prompt3"], 0)
+    assert np.isfinite(runner.logits()).all()
+    for step in range(4):
+        runner.forward([int(gold["gen_unit3"][step])], 130 + step)
+    for step in range(4, 8):
+        runner.decode_replay(int(gold["gen_unit3"][step]), 130 + step)
+    assert np.isfinite(runner.logits()).all()
+    assert runner.device_error() == 0
