@@ -694,7 +694,7 @@ extern "C" int q38_attention_decode_splits(int batch_seqs, int kv_heads, int num
   int s = (16 * num_sms + ctas - 1) / ctas;
   if (s < 1) s = 1;
   if (s > max_splits) s = max_splits;
-  if (s > 64) s = 64;
+  if (s > 256) s = 256;
   return s;
 }
 

@@ -1,0 +1,155 @@
+"""Benchmark of the tensor-parallel path: one request with a very long context (default 262,144 tokens, lean recipe,
+27B geometry) over all ranks of the job.
+
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29533 \\
+      qwen3.8-27b-cuda-kernel_b200/tp_bench.py --context 262144
+
+Weights are random BQ planes of the real geometry (written once to shared memory by rank 0); every rank uploads only
+its shard. The first `--real-prefill` tokens of the context are really prefilled (512-token steps, timed); the rest of
+the KV cache is filled with random int8 rows and finite scales, because a real prefill of the whole context through
+the per-token attention kernel would take minutes. Then `--steps` decode steps (one CUDA graph per step: kernels and
+NCCL all-reduces) are timed with CUDA events, max over ranks; one 512-token prefill step at the end of the context
+is timed as well. Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def _package():
+    name = "q38b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, HERE / "__init__.py", submodule_search_locations=[str(HERE)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--context", type=int, default=262144)
+    ap.add_argument("--real-prefill", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--recipe", default="lean")
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = _package()
+    from q38b200 import synth, tp
+
+    shm = Path("/dev/shm") if Path("/dev/shm").is_dir() else Path("/tmp")
+    path = shm / f"q38_tp_27b_{args.recipe}_L{args.layers}.q38"
+    if rank == 0 and not path.exists():
+        types = None
+        if args.layers != 64:
+            types = ["full_attention" if (i + 1) % 4 == 0 else "linear_attention" for i in range(args.layers)]
+        cfg = synth.model_config(**{**synth.CONFIG_27B, "layers": args.layers, "layer_types": types})
+        t0 = time.time()
+        synth.write_random_planes_q38(path, cfg, recipe=args.recipe, seed=11)
+        print(f"tp_bench: model planes written in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    if dist is not None:
+        dist.barrier()
+    t0 = time.time()
+    runner = tp.TPRunner(pkg, path, rank, world, dist, max_tokens=512, max_context=args.context + 64)
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"tp_bench: shards uploaded in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+
+    rng = np.random.default_rng(3)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        e0, e1 = ev(), ev()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms[0])
+
+    # ---- real prefill of the head of the context ----
+    real = min(args.real_prefill, args.context - 1024) // 512 * 512
+    pre_ms = 0.0
+    for p0 in range(0, real, 512):
+        toks = rng.integers(1000, 150000, size=512)
+        pre_ms += timed(lambda: runner.forward(toks, p0))
+    # ---- the rest of the KV cache: random int8 rows, finite fp16 scales ----
+    kvp = runner.kv_pool
+    first_fake_page = real // 64
+    per_layer = runner.pages * runner.page_bytes
+    g = torch.Generator(device="cuda").manual_seed(5 + rank)
+    for layer in range(max(1, sum(1 for L in runner.layers if L["attention"]))):
+        a = layer * per_layer + first_fake_page * runner.page_bytes
+        b = (layer + 1) * per_layer
+        view = kvp[a:b]
+        view.copy_(torch.randint(0, 256, (b - a,), dtype=torch.uint8, device="cuda", generator=g))
+        view.view(torch.int16).bitwise_and_(0x2BFF)  # as fp16: positive, below 0.06 (int8 rows are unaffected in kind)
+    torch.cuda.synchronize()
+
+    # ---- one prefill step at the far end of the context ----
+    far0 = args.context - 1024
+    toks = rng.integers(1000, 150000, size=512)
+    far_ms = timed(lambda: runner.forward(toks, far0))
+
+    # ---- decode ----
+    pos = args.context - 512
+    tok = 12345
+    for _ in range(max(args.warmup, 2)):
+        runner.decode_replay(tok, pos)
+        pos += 1
+    state = {"pos": pos}
+
+    def steps():
+        for _ in range(args.steps):
+            runner.decode_replay(tok, state["pos"])
+            state["pos"] += 1
+    dec_ms = timed(steps) / args.steps
+    logits = runner.logits()
+    err = runner.device_error()
+    line = {
+        "metric": "tp_decode_tok_per_s", "value": 1000.0 / dec_ms, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "ms_per_step": dec_ms, "context_tokens": args.context, "recipe": args.recipe, "layers": args.layers,
+        "all_reduces_per_step": 2 * args.layers,
+        "prefill_tok_per_s_short_context": (real / pre_ms * 1000.0) if pre_ms > 0 else None,
+        "prefill_512_at_context_end_ms": far_ms,
+        "kv": f"first {real} tokens really prefilled, the rest random int8 rows",
+        "logits_finite": bool(np.isfinite(logits).all()), "device_error": err, "data": "synthetic",
+    }
+    runner.close()
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
