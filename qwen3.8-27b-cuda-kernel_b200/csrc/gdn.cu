@@ -484,6 +484,24 @@ __device__ __forceinline__ void load_rows_128(float* dst, const float* __restric
   }
 }
 
+// The same copy as asynchronous 16-byte copies (cp.async): no register staging, so all of a tile's requests are in
+// flight at once and the copy overlaps whatever the threads do until they wait for its group.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the destination is zero-filled, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void rows_async_128(float* dst, const float* __restrict__ src, size_t ld, int nc, int tid) {
+  for (int i = tid; i < kCh * 32; i += kChunkThreads) {
+    const int r = i >> 5, c4 = i & 31;
+    cp_async16(dst + r * kLd + 4 * c4, src + (size_t)(r < nc ? r : 0) * ld + 4 * c4, r < nc);
+  }
+}
+
 constexpr int kPrepSmemBytes = (2 * kCh * kLd + kCh * kLdP + 3 * kCh) * 4;
 
 __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_prep_kernel(
@@ -611,7 +629,7 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
   float* Ss = scan_sm;               // [128 v][kLd]
   float* Ws = Ss + 128 * kLd;        // [64][kLd]
   float* Qs = Ws + kCh * kLd;
-  float* Kd = Qs + kCh * kLd;        // K rows scaled by e^{lg_C - lg_j}
+  float* Kd = Qs + kCh * kLd;        // K rows
   float* Us = Kd + kCh * kLd;        // U0, then U
   float* Ps = Us + kCh * kLd;        // [64][kLdP]
   float* lg_s = Ps + kCh * kLdP;
@@ -641,13 +659,16 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     }
     __syncthreads();
     const float* rows = qkv + (size_t)m0 * conv_dim;
-    load_rows_128(Us, in, 128, kCh, nullptr, tid);
-    load_rows_128(Ws, in + kCh * 128, 128, kCh, nullptr, tid);
-    load_rows_128(Qs, rows + (size_t)kh * kDk, conv_dim, nc, nullptr, tid);
-    load_rows_128(Kd, rows + (size_t)nk * kDk + (size_t)kh * kDk, conv_dim, nc, kd_s, tid);
+    // group 1: what the two state products need (W, Q, U0); group 2: P and K, which land while those run
+    rows_async_128(Ws, in + kCh * 128, 128, kCh, tid);
+    rows_async_128(Qs, rows + (size_t)kh * kDk, conv_dim, nc, tid);
+    rows_async_128(Us, in, 128, kCh, tid);
+    cp_async_commit();
+    rows_async_128(Kd, rows + (size_t)nk * kDk + (size_t)kh * kDk, conv_dim, nc, tid);
     for (int i = tid; i < kCh * 16; i += kChunkThreads)
-      *reinterpret_cast<float4*>(Ps + (i >> 4) * kLdP + 4 * (i & 15)) =
-          *reinterpret_cast<const float4*>(in + 2 * kCh * 128 + (size_t)i * 4);
+      cp_async16(Ps + (i >> 4) * kLdP + 4 * (i & 15), in + 2 * kCh * 128 + (size_t)i * 4, true);
+    cp_async_commit();
+    cp_async_wait<1>();
     __syncthreads();
 
     // [64 tokens][128 v] products: threads 0-255 compute X = W S0^T, threads 256-511 Y = Q S0^T at the same time.
@@ -687,7 +708,8 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) acc[i][jj] *= eg_s[t0 + i];
     }
-    __syncthreads();  // U complete; nobody reads W any more
+    cp_async_wait<0>();
+    __syncthreads();  // U complete; nobody reads W any more; P and K have landed
 
     // ---- (c) O = Y + P U. P is lower triangular: tokens 8 gw .. 8 gw + 7 need j < 8 gw + 8; the two thread groups
     // split that range (group 1 continues on top of Y, group 0 starts from zero and hands its part over through
@@ -759,7 +781,8 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
         const float4 u4 = *reinterpret_cast<const float4*>(Us + j * kLd + 4 * vq);
         const float4 k0 = *reinterpret_cast<const float4*>(Kd + j * kLd + 4 * ko);
         const float4 k1 = *reinterpret_cast<const float4*>(Kd + j * kLd + 64 + 4 * ko);
-        const float uu[4] = {u4.x, u4.y, u4.z, u4.w};
+        const float kdj = kd_s[j];  // e^{lg_C - lg_j}: the decay from token j to the end of the chunk
+        const float uu[4] = {u4.x * kdj, u4.y * kdj, u4.z * kdj, u4.w * kdj};
         const float kk8[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i)
