@@ -618,34 +618,42 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_prep_kernel(
 
 constexpr int kScanSmemBytes = (128 * kLd + 4 * kCh * kLd + kCh * kLdP + 3 * kCh) * 4;
 
+// VSPLIT = 1: one CTA per (v head, sequence) updates all 128 state rows and finishes the output (gated RMSNorm)
+// itself. VSPLIT = 2: two CTAs per head, 64 state rows each (the rows are independent given k, q, beta, decay); the
+// un-normalised outputs go to scratch and gdn_norm_gate_kernel finishes them, because the norm runs over all 128
+// outputs of a token. The split doubles the CTAs of the sequential part when a step has few (head, sequence) pairs.
+template <int VSPLIT>
 __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     const float* __restrict__ qkv, int conv_dim, const __nv_bfloat16* __restrict__ z, int ld_z,
     const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
     int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
-    const float* __restrict__ scratch) {
+    const float* __restrict__ scratch, float* __restrict__ o_scratch) {
   pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
   pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
+  constexpr int NV = kDv / VSPLIT;  // state rows (v) of this CTA
+  constexpr int TV = 4 / VSPLIT;    // v per thread in the [tokens][v] products: v = lane + 32 jj
   extern __shared__ float scan_sm[];
-  float* Ss = scan_sm;               // [128 v][kLd]
-  float* Ws = Ss + 128 * kLd;        // [64][kLd]
+  float* Ss = scan_sm;               // [NV v][kLd]
+  float* Ws = Ss + NV * kLd;         // [64][kLd]
   float* Qs = Ws + kCh * kLd;
   float* Kd = Qs + kCh * kLd;        // K rows
-  float* Us = Kd + kCh * kLd;        // U0, then U
+  float* Us = Kd + kCh * kLd;        // U0, then U: [64][kLd], NV columns used
   float* Ps = Us + kCh * kLd;        // [64][kLdP]
   float* lg_s = Ps + kCh * kLdP;
   float* eg_s = lg_s + kCh;          // e^{lg_t}
   float* kd_s = eg_s + kCh;          // e^{lg_C - lg_j}
-  const int vh = blockIdx.x, b = blockIdx.y;
+  const int vh = blockIdx.x / VSPLIT, vbase = (blockIdx.x % VSPLIT) * NV, b = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int s0 = seq_start[b], n = seq_start[b + 1] - s0;
   if (n <= 0) return;
   const int kh = vh / (nv / nk);
-  float* S = recurrent + (((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv * kDk;
-  for (int i = tid; i < 128 * 32; i += kChunkThreads)
+  float* S = recurrent + ((((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv + vbase) * kDk;
+  for (int i = tid; i < NV * 32; i += kChunkThreads)
     *reinterpret_cast<float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31)) = *reinterpret_cast<const float4*>(S + (size_t)i * 4);
   const int chunks = (n + kCh - 1) / kCh;
-  const float nw0 = norm_w[lane], nw1 = norm_w[lane + 32], nw2 = norm_w[lane + 64], nw3 = norm_w[lane + 96];
-  const float nw[4] = {nw0, nw1, nw2, nw3};
+  float nw[TV];
+#pragma unroll
+  for (int jj = 0; jj < TV; ++jj) nw[jj] = norm_w[vbase + lane + 32 * jj];
 
   for (int c = 0; c < chunks; ++c) {
     const int nc = min(kCh, n - c * kCh), m0 = s0 + c * kCh;
@@ -662,7 +670,10 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     // group 1: what the two state products need (W, Q, U0); group 2: P and K, which land while those run
     rows_async_128(Ws, in + kCh * 128, 128, kCh, tid);
     rows_async_128(Qs, rows + (size_t)kh * kDk, conv_dim, nc, tid);
-    rows_async_128(Us, in, 128, kCh, tid);
+    for (int i = tid; i < kCh * (NV / 4); i += kChunkThreads) {
+      const int r = i / (NV / 4), c4 = i % (NV / 4);
+      cp_async16(Us + r * kLd + 4 * c4, in + (size_t)r * 128 + vbase + 4 * c4, true);
+    }
     cp_async_commit();
     rows_async_128(Kd, rows + (size_t)nk * kDk + (size_t)kh * kDk, conv_dim, nc, tid);
     for (int i = tid; i < kCh * 16; i += kChunkThreads)
@@ -671,28 +682,28 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     cp_async_wait<1>();
     __syncthreads();
 
-    // [64 tokens][128 v] products: threads 0-255 compute X = W S0^T, threads 256-511 Y = Q S0^T at the same time.
-    // Thread tile 8 tokens (8 gw + i) x 4 v (lane + 32 jj): 12 shared-memory reads feed 128 FMAs, which keeps the
-    // products FMA-bound instead of shared-memory-bound.
+    // [64 tokens][NV v] products: threads 0-255 compute X = W S0^T, threads 256-511 Y = Q S0^T at the same time.
+    // Thread tile 8 tokens (8 gw + i) x TV v (lane + 32 jj): with TV = 4, 12 shared-memory reads feed 128 FMAs, which
+    // keeps the products FMA-bound instead of shared-memory-bound.
     const int grp = warp >> 3, gw = warp & 7;  // grp 0: X / upper half of P U, grp 1: Y / lower half + output
     const int t0 = 8 * gw;
-    float acc[8][4];
+    float acc[8][TV];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+      for (int jj = 0; jj < TV; ++jj) acc[i][jj] = 0.0f;
     {
       const float* Am = grp == 0 ? Ws : Qs;
 #pragma unroll 2
       for (int kk = 0; kk < 128; kk += 4) {
-        float4 bv[4];
+        float4 bv[TV];
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
+        for (int jj = 0; jj < TV; ++jj) bv[jj] = *reinterpret_cast<const float4*>(Ss + (lane + 32 * jj) * kLd + kk);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 av = *reinterpret_cast<const float4*>(Am + (t0 + i) * kLd + kk);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
+          for (int jj = 0; jj < TV; ++jj)
             acc[i][jj] += av.x * bv[jj].x + av.y * bv[jj].y + av.z * bv[jj].z + av.w * bv[jj].w;
         }
       }
@@ -701,12 +712,12 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) Us[(t0 + i) * kLd + lane + 32 * jj] -= acc[i][jj];
+        for (int jj = 0; jj < TV; ++jj) Us[(t0 + i) * kLd + lane + 32 * jj] -= acc[i][jj];
     } else {         // (b) Y scaled by e^{lg_t}
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) acc[i][jj] *= eg_s[t0 + i];
+        for (int jj = 0; jj < TV; ++jj) acc[i][jj] *= eg_s[t0 + i];
     }
     cp_async_wait<0>();
     __syncthreads();  // U complete; nobody reads W any more; P and K have landed
@@ -722,19 +733,19 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.0f;
+          for (int jj = 0; jj < TV; ++jj) acc[i][jj] = 0.0f;
       }
       for (int j = ja; j < jb; j += 4) {
-        float uv[4][4];
+        float uv[4][TV];
 #pragma unroll
         for (int q = 0; q < 4; ++q)
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) uv[q][jj] = Us[(j + q) * kLd + lane + 32 * jj];
+          for (int jj = 0; jj < TV; ++jj) uv[q][jj] = Us[(j + q) * kLd + lane + 32 * jj];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 pv = *reinterpret_cast<const float4*>(Ps + (t0 + i) * kLdP + j);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
+          for (int jj = 0; jj < TV; ++jj)
             acc[i][jj] += pv.x * uv[0][jj] + pv.y * uv[1][jj] + pv.z * uv[2][jj] + pv.w * uv[3][jj];
         }
       }
@@ -742,57 +753,66 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) Ws[(t0 + i) * kLd + lane + 32 * jj] = acc[i][jj];
+          for (int jj = 0; jj < TV; ++jj) Ws[(t0 + i) * kLd + lane + 32 * jj] = acc[i][jj];
       }
     }
     __syncthreads();  // group 0's part of P U is in the W buffer; every read of S0 is done
     if (grp == 1) {
-      // gated RMSNorm over the 128 outputs of each token (a warp holds whole tokens)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) acc[i][jj] += Ws[(t0 + i) * kLd + lane + 32 * jj];
-        const float ss =
-            warp_sum(acc[i][0] * acc[i][0] + acc[i][1] * acc[i][1] + acc[i][2] * acc[i][2] + acc[i][3] * acc[i][3]);
+        for (int jj = 0; jj < TV; ++jj) acc[i][jj] += Ws[(t0 + i) * kLd + lane + 32 * jj];
         const int t = t0 + i;
-        if (t < nc) {
-          const float r = 1.0f / sqrtf(ss / float(kDv) + eps);
-          const size_t m = (size_t)(m0 + t);
+        const size_t m = (size_t)(m0 + t);
+        if constexpr (VSPLIT == 1) {
+          // gated RMSNorm over the 128 outputs of each token (a warp holds whole tokens)
+          float sq = 0.0f;
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const int d = lane + 32 * jj;
-            const float zz = __bfloat162float(z[m * ld_z + (size_t)vh * kDv + d]);
-            out[m * nv * kDv + (size_t)vh * kDv + d] = __float2bfloat16_rn(acc[i][jj] * r * nw[jj] * silu_f(zz));
+          for (int jj = 0; jj < TV; ++jj) sq += acc[i][jj] * acc[i][jj];
+          const float ss = warp_sum(sq);
+          if (t < nc) {
+            const float r = 1.0f / sqrtf(ss / float(kDv) + eps);
+#pragma unroll
+            for (int jj = 0; jj < TV; ++jj) {
+              const int d = lane + 32 * jj;
+              const float zz = __bfloat162float(z[m * ld_z + (size_t)vh * kDv + d]);
+              out[m * nv * kDv + (size_t)vh * kDv + d] = __float2bfloat16_rn(acc[i][jj] * r * nw[jj] * silu_f(zz));
+            }
           }
+        } else if (t < nc) {
+#pragma unroll
+          for (int jj = 0; jj < TV; ++jj)
+            o_scratch[m * nv * kDv + (size_t)vh * kDv + vbase + lane + 32 * jj] = acc[i][jj];
         }
       }
     }
 
-    // ---- (d) S = e^{lg_C} S0 + U^T Kd: thread tile v = 4 vq + i, k = 4 ko + {0..3} and 64 + 4 ko + {0..3} ----
+    // ---- (d) S = e^{lg_C} S0 + U^T diag(e^{lg_C - lg}) K: thread tile v = TV vq + i, k = 4 ko + {0..3} and 64 + 4 ko + {0..3}
     {
       const int vq = tid >> 4, ko = tid & 15;
-      float sacc[4][8];
+      float sacc[TV][8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < TV; ++i)
 #pragma unroll
         for (int e = 0; e < 8; ++e) sacc[i][e] = 0.0f;
 #pragma unroll 4
       for (int j = 0; j < kCh; ++j) {
-        const float4 u4 = *reinterpret_cast<const float4*>(Us + j * kLd + 4 * vq);
+        const float kdj = kd_s[j];  // e^{lg_C - lg_j}: the decay from token j to the end of the chunk
+        float uu[TV];
+#pragma unroll
+        for (int i = 0; i < TV; ++i) uu[i] = Us[j * kLd + TV * vq + i] * kdj;
         const float4 k0 = *reinterpret_cast<const float4*>(Kd + j * kLd + 4 * ko);
         const float4 k1 = *reinterpret_cast<const float4*>(Kd + j * kLd + 64 + 4 * ko);
-        const float kdj = kd_s[j];  // e^{lg_C - lg_j}: the decay from token j to the end of the chunk
-        const float uu[4] = {u4.x * kdj, u4.y * kdj, u4.z * kdj, u4.w * kdj};
         const float kk8[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < TV; ++i)
 #pragma unroll
           for (int e = 0; e < 8; ++e) sacc[i][e] += uu[i] * kk8[e];
       }
       const float gC = eg_s[kCh - 1];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float* r0 = Ss + (4 * vq + i) * kLd + 4 * ko;
+      for (int i = 0; i < TV; ++i) {
+        float* r0 = Ss + (TV * vq + i) * kLd + 4 * ko;
         float4 a = *reinterpret_cast<float4*>(r0), bq = *reinterpret_cast<float4*>(r0 + 64);
         a.x = gC * a.x + sacc[i][0];
         a.y = gC * a.y + sacc[i][1];
@@ -808,8 +828,25 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     }
   }
   __syncthreads();
-  for (int i = tid; i < 128 * 32; i += kChunkThreads)
+  for (int i = tid; i < NV * 32; i += kChunkThreads)
     *reinterpret_cast<float4*>(S + (size_t)i * 4) = *reinterpret_cast<const float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31));
+}
+
+// Gated RMSNorm of the split scan's outputs: one CTA per (token, v head), 128 threads.
+__global__ void __launch_bounds__(kDv) gdn_norm_gate_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ z,
+                                                            int ld_z, const float* __restrict__ norm_w, float eps,
+                                                            __nv_bfloat16* __restrict__ out, int nv) {
+  pdl_wait();
+  pdl_launch_dependents();
+  __shared__ float red[4];
+  const int m = blockIdx.x, vh = blockIdx.y, d = threadIdx.x;
+  const float v = o[((size_t)m * nv + vh) * kDv + d];
+  const float ss = warp_sum(v * v);
+  if ((d & 31) == 0) red[d >> 5] = ss;
+  __syncthreads();
+  const float r = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / float(kDv) + eps);
+  const float zz = __bfloat162float(z[(size_t)m * ld_z + (size_t)vh * kDv + d]);
+  out[((size_t)m * nv + vh) * kDv + d] = __float2bfloat16_rn(v * r * norm_w[d] * silu_f(zz));
 }
 
 }  // namespace
@@ -887,7 +924,9 @@ extern "C" int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_
 }
 
 extern "C" size_t q38_gdn_chunk_scratch_floats(int max_tokens, int max_seqs, int num_v_heads) {
-  return (size_t)(max_tokens / kCh + max_seqs) * (size_t)num_v_heads * kChunkFloats;
+  // per-chunk U0 / W / P / lg for every chunk slot, then one [tokens][v heads * 128] fp32 row block for the split scan
+  return (size_t)(max_tokens / kCh + max_seqs) * (size_t)num_v_heads * kChunkFloats +
+         (size_t)max_tokens * (size_t)num_v_heads * kDv;
 }
 
 extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d,
@@ -907,18 +946,37 @@ extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, co
   static const cudaError_t attr1 =
       cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmemBytes);
   static const cudaError_t attr2 =
-      cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+      cudaFuncSetAttribute(gdn_chunk_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  static const cudaError_t attr3 =
+      cudaFuncSetAttribute(gdn_chunk_scan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
   Q38_CUDA_OK(attr1);
   Q38_CUDA_OK(attr2);
+  Q38_CUDA_OK(attr3);
   const cudaStream_t s = as_stream(stream);
   const int max_chunks = (batch->max_tokens_per_seq + kCh - 1) / kCh;
   (void)launch_kernel(gdn_chunk_prep_kernel, dim3(max_chunks, d->num_v_heads, batch->num_seqs), dim3(kChunkThreads), kPrepSmemBytes, s, 
       p->qkv, d->conv_dim, p->ab, p->A, p->dt_bias, d->num_k_heads, d->num_v_heads, batch->seq_start, scratch);
   Q38_LAUNCH_OK("gdn_chunk_prep_kernel");
-  (void)launch_kernel(gdn_chunk_scan_kernel, dim3(d->num_v_heads, batch->num_seqs), dim3(kChunkThreads), kScanSmemBytes, s, 
-      p->qkv, d->conv_dim, reinterpret_cast<const __nv_bfloat16*>(p->z), p->ld_z, p->norm_w, p->eps,
-      reinterpret_cast<__nv_bfloat16*>(p->out), p->gdn_layer, st->num_gdn_layers, d->num_k_heads, d->num_v_heads,
-      st->recurrent, batch->seq_start, batch->seq_slot, scratch);
-  Q38_LAUNCH_OK("gdn_chunk_scan_kernel");
+  const __nv_bfloat16* zp = reinterpret_cast<const __nv_bfloat16*>(p->z);
+  __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p->out);
+  float* o_scratch = scratch + (size_t)(batch->num_tokens / kCh + batch->num_seqs) * (size_t)d->num_v_heads * kChunkFloats;
+  // the sequential part has one CTA per (v head, sequence); with few of them, two CTAs share a head's state rows
+  const bool split = 2 * d->num_v_heads * batch->num_seqs <= num_sms();
+  if (split) {
+    (void)launch_kernel(gdn_chunk_scan_kernel<2>, dim3(2 * d->num_v_heads, batch->num_seqs), dim3(kChunkThreads),
+                        kScanSmemBytes, s, p->qkv, d->conv_dim, zp, p->ld_z, p->norm_w, p->eps, outp, p->gdn_layer,
+                        st->num_gdn_layers, d->num_k_heads, d->num_v_heads, st->recurrent, batch->seq_start,
+                        batch->seq_slot, scratch, o_scratch);
+    Q38_LAUNCH_OK("gdn_chunk_scan_kernel");
+    (void)launch_kernel(gdn_norm_gate_kernel, dim3(batch->num_tokens, d->num_v_heads), dim3(kDv), 0, s, o_scratch, zp,
+                        p->ld_z, p->norm_w, p->eps, outp, d->num_v_heads);
+    Q38_LAUNCH_OK("gdn_norm_gate_kernel");
+  } else {
+    (void)launch_kernel(gdn_chunk_scan_kernel<1>, dim3(d->num_v_heads, batch->num_seqs), dim3(kChunkThreads),
+                        kScanSmemBytes, s, p->qkv, d->conv_dim, zp, p->ld_z, p->norm_w, p->eps, outp, p->gdn_layer,
+                        st->num_gdn_layers, d->num_k_heads, d->num_v_heads, st->recurrent, batch->seq_start,
+                        batch->seq_slot, scratch, o_scratch);
+    Q38_LAUNCH_OK("gdn_chunk_scan_kernel");
+  }
   return Q38_OK;
 }

@@ -416,6 +416,52 @@ def test_gdn_matches_oracle(nk, nv, chunked):
     assert float(rec[0].abs().sum()) == 0 and float(rec[:, 0].abs().sum()) == 0, "other slots / layers untouched"
 
 
+@pytest.mark.parametrize("seqs", [2, 30])
+def test_gdn_chunked_matches_sequential_kernel(seqs):
+    """The chunked form against the token-sequential kernel on the same inputs: few (head, sequence) pairs take the
+    two-CTAs-per-head scan with the separate norm kernel, many take the one-CTA scan."""
+    rng = np.random.default_rng(31)
+    nk, nv, layers, layer = 2, 6, 1, 0
+    conv_dim = 2 * nk * 128 + nv * 128
+    ld = conv_dim + nv * 128
+    lens = [int(x) for x in rng.integers(1, 150, size=seqs)]
+    n = sum(lens)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    A_d = dev((-rng.uniform(0.5, 8, nv)).astype(np.float32))
+    dt_d = dev((0.5 * rng.standard_normal(nv)).astype(np.float32))
+    nw_d = dev((1 + 0.2 * rng.standard_normal(128)).astype(np.float32))
+    qkv_np = rng.standard_normal((n, conv_dim)).astype(np.float32)
+    for h in range(2 * nk):  # q and k heads normalised as the conv kernel leaves them
+        blk = qkv_np[:, h * 128:(h + 1) * 128]
+        blk /= np.sqrt((blk * blk).sum(axis=1, keepdims=True) + 1e-6)
+    qkv = dev(qkv_np)
+    ab = dev(rng.standard_normal((n, 2 * nv)).astype(np.float32))
+    proj_d = tl.to_dev_bf16(tl.bf16_round(rng.standard_normal((n, ld))))
+    rec0 = dev((0.1 * rng.standard_normal((seqs, layers, nv, 128, 128))).astype(np.float32))
+    batch = tl.Batch([(b, 0, lens[b]) for b in range(seqs)])
+    dims = pkg.GdnDims(nk, nv, conv_dim, ld)
+    res = []
+    for chunked in (False, True):
+        rec = rec0.clone()
+        conv = torch.zeros((seqs, layers, 3, conv_dim), dtype=torch.bfloat16, device="cuda")
+        st = pkg.GdnStateDesc(pkg.ptr(rec), pkg.ptr(conv), layers)
+        out = torch.zeros((n, nv * 128), dtype=torch.bfloat16, device="cuda")
+        rp = pkg.GdnRecurrenceParams(pkg.ptr(qkv), pkg.ptr(ab), pkg.ptr(A_d), pkg.ptr(dt_d), pkg.ptr(proj_d) + conv_dim * 2,
+                                     ld, pkg.ptr(nw_d), 1e-6, pkg.ptr(out), layer)
+        if chunked:
+            need = K().q38_gdn_chunk_scratch_floats(n, seqs, nv)
+            scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+            pkg.check(K().q38_gdn_recurrence_chunked(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st),
+                                                     pkg.ptr(scratch), need, None))
+        else:
+            pkg.check(K().q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
+        sync_ok()
+        res.append((out.float().cpu().numpy(), rec.cpu().numpy()))
+    (o_seq, s_seq), (o_chk, s_chk) = res
+    assert np.all(np.abs(o_chk - o_seq) <= 2e-2 * (np.abs(o_seq) + 0.05))
+    assert np.all(np.abs(s_chk - s_seq) <= 1e-4 + 1e-3 * np.abs(s_seq))
+
+
 def test_gdn_decode_kernel_equals_general_kernel():
     """Batches in which every sequence advances by one token take the persistent state-streaming kernel; it must
     reproduce the general kernel bit for bit (outputs and states), also with an empty sequence in the batch and
