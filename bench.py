@@ -383,7 +383,10 @@ def main():
                             if top.startswith("qgemm") else None),
                 "peak_source": peak_src,
                 "avg_launch_us": 1000.0 * fam[top]["ms_per_step"] / max(1, fam[top]["launches_per_step"]),
-                "share_of_step": fam[top]["share"], "all": fam}
+                "share_of_step": fam[top]["share"], "all": fam,
+                # the per-op times come from an eager replica of the step with events between the kernels; scaled to
+                # the graph-timed step they give the rate inside the timed region
+                "achieved_in_graph_estimate": fam[top]["GBps"] * step_ms_profiled / (1000.0 * core_s / args.steps)}
     step_bytes = sum(bytes_by_op.values())
     launches = sum(calls.get(k, 0) for k in per_step) + calls.get("gdn.conv", 0) + calls.get("attn.decode", 0) + 1
 
