@@ -211,6 +211,46 @@ def weight_macs():
     return {"pair": gdn + attn, "all_layers": 48 * gdn + 16 * attn, "lm_head": V * H}
 
 
+def run_trace(args, eng, model, rank, world, dist, config, barrier):
+    """The whole trace through the Engine (scheduler, ragged chunked prefill, CUDA-graph decode): requests are dealt
+    round-robin over the ranks, every rank offers its share at t = 0 and serves it with 64 slots."""
+    import torch
+    from q38b200 import sharding
+    reqs = sharding.shard_requests(sharding.trace_requests(args.trace, seed=11), rank, world)
+    rng = np.random.default_rng(SEED + rank)
+    B = args.batch
+    kv_tokens = B * (8192 + 1024 + 128)
+    e = eng.Engine(model, eng.default_runner_options(max_batch=B, prefill_chunk=512, kv_tokens=kv_tokens,
+                                                     max_context=args.max_context, verbose=int(rank == 0)),
+                   ragged_prefill=True)
+    g = eng.greedy()
+    for _, (plen, olen) in reqs:
+        e.submit(rng.integers(1000, 150000, size=plen).astype(np.int32), g, max_new_tokens=olen, ignore_eos=True)
+    barrier()
+    t0 = time.perf_counter()
+    e.run()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    done = e.take_finished()
+    st = e.stats()
+    prompt_tokens = sum(p for _, (p, _) in reqs)
+    out_tokens = sum(len(f.tokens) for f in done)
+    wall_max, = sharding.max_over_ranks([wall], dist, device="cuda")
+    tot = torch.tensor([prompt_tokens, out_tokens, len(done)], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(tot)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "trace_tok_per_s", "value": float(tot[0] + tot[1]) / wall_max, "unit": "tok/s (prompt + generated)",
+            "n_gpus": world, "requests": int(tot[2]), "wall_s": wall_max, "prompt_tokens": int(tot[0]),
+            "generated_tokens": int(tot[1]), "generated_tok_per_s": float(tot[1]) / wall_max,
+            "rank0_engine_stats": {"prefill_tokens": int(st.prefill_tokens), "prefill_s": st.prefill_s,
+                                   "decode_tokens": int(st.decode_tokens), "decode_s": st.decode_s,
+                                   "decode_steps": int(st.decode_steps)},
+            "scaling": "weak" if world == 1 else "strong", "data": "synthetic", "config": config}))
+    e.close()
+
+
 # ----------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -226,6 +266,9 @@ def main():
     ap.add_argument("--profile-steps", type=int, default=3)
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="A/B aid: classic stream order instead of programmatic dependent launch")
+    ap.add_argument("--trace", type=int, default=0, metavar="N",
+                    help="run the continuous-batching trace instead (N requests, prompts log-uniform 64..8192, outputs "
+                         "uniform 64..1024, all offered at t = 0, 64 slots per GPU) through the Engine and report it")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: reserve the KV pages but leave them zero-filled (the line is then not a bench value)")
     args = ap.parse_args()
@@ -282,6 +325,12 @@ def main():
     barrier()
     model = eng.Model(model_path)
     B = args.batch
+    if args.trace:
+        run_trace(args, eng, model, rank, world, dist, config, barrier)
+        model.close()
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     ctx = trace_contexts(B, rank)
     kv_tokens = int(sum((c + args.steps + args.warmup + 64 + 63) // 64 * 64 for c in ctx)) + 64 * 8
     runner = eng.Runner(model, eng.default_runner_options(max_batch=B, prefill_chunk=512, kv_tokens=kv_tokens,
