@@ -88,6 +88,10 @@ struct ModelRunner::Impl {
   std::unique_ptr<KvCache> kv;
   std::unique_ptr<GdnStatePool> state;
   Stream stream;
+  // side branch of the step: the a/b gate projection of a GDN layer needs only the layer's input, so it runs beside
+  // the layer's (much larger) in-projection GEMM; fork / join events make it a parallel branch of the captured graph
+  Stream side;
+  Event fork_ev, join_ev;
   DeviceArena ws;
   int max_tokens = 0, max_rows = 0, dummy_slot = 0, proj_ld = 0;
 
@@ -338,6 +342,13 @@ void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool dec
     in.partials_in = partials;
     in.hidden = H;
     in.eps = eps;
+    const bool side_ab = !W.attention && !profiling;  // the per-op profile keeps everything on one stream
+    if (side_ab) {
+      fork_ev.record(s);
+      QWEN38_CUDA(cudaStreamWaitEvent(side.get(), fork_ev.get(), 0));
+      kernels::gdn_ab(xbf, m, H, W.ab, W.ab_rows, partials, eps, ab, side.get());
+      join_ev.record(side.get());
+    }
     kernels::qgemm(xbf, m, W.in_proj, in, gemm_ws, s);
     mark(W.attention ? "gemm.attn_qkvg" : "gemm.gdn_qkvz");
     if (W.attention) {
@@ -369,7 +380,8 @@ void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool dec
       mark(decode ? "attn.decode" : "attn.prefill");
       ++attn_i;
     } else {
-      kernels::gdn_ab(xbf, m, H, W.ab, W.ab_rows, partials, eps, ab, s);
+      if (side_ab) QWEN38_CUDA(cudaStreamWaitEvent(s, join_ev.get(), 0));
+      else kernels::gdn_ab(xbf, m, H, W.ab, W.ab_rows, partials, eps, ab, s);
       mark("gdn.ab");
       kernels::GdnConvParams cp;
       cp.proj = proj;
