@@ -12,13 +12,14 @@ namespace {
 
 struct ConfigInfo {
   const char* name;
-  int tile_m;
+  int tile_m;   // tokens per launch
   bool umma;
+  int mblocks;  // tcgen05 kernel: token blocks of tile_m / mblocks rows inside one launch
 };
 constexpr ConfigInfo kConfigs[] = {
-    {"stream_m8", 8, false}, {"stream_m16", 16, false}, {"umma_t32", 32, true},
-    {"umma_t64", 64, true},  {"umma_t128", 128, true},  {"umma_t256", 256, true},
-    {"umma_t512", 512, true},
+    {"stream_m8", 8, false, 1}, {"stream_m16", 16, false, 1}, {"umma_t32", 32, true, 1},
+    {"umma_t64", 64, true, 1},  {"umma_t128", 128, true, 1},  {"umma_t256", 256, true, 1},
+    {"umma_t512", 512, true, 1}, {"umma_t256x2", 512, true, 2},
 };
 constexpr int kNumConfigs = int(sizeof(kConfigs) / sizeof(kConfigs[0]));
 
@@ -34,7 +35,11 @@ int auto_config(int m, const q38_bq_weight& w, const q38_gemm_workspace* ws) {
   if (m <= 32) return 2;
   if (m <= 64) return 3;
   if (m <= 128) return 4;
-  if (m <= 256 || w.bits == 8) return 5;
+  if (m <= 256) return 5;
+  // few weight tiles and a short k: two 256-token blocks side by side give twice the whole-tile work items and need
+  // no cut in k (with a long k the three-way cut of the 512-token pass wins: 118 against 139 us on 5120 x 17408)
+  if (2 * (w.n / 128) <= num_sms() && w.k <= 8192) return 7;
+  if (w.bits == 8) return 5;
   const bool roomy = ws && ws->partials && ws->partial_floats >= size_t(2) * size_t(num_sms()) * 128 * 512;
   return roomy || w.n / 128 >= 3 * num_sms() ? 6 : 5;
 }
@@ -117,7 +122,8 @@ extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const
       e.out = static_cast<q38_bf16*>(e.out) + (size_t)r0 * e.ldo;
     }
     if (e.partials_in) e.partials_in += (size_t)r0 * (e.hidden / 128);
-    const int rc = kConfigs[config].umma ? qgemm_umma_launch(tm, ap + (size_t)r0 * w->k, rows, *w, e, ws, s)
+    const int mb = kConfigs[config].mblocks;
+    const int rc = kConfigs[config].umma ? qgemm_umma_launch(tm / mb, mb, ap + (size_t)r0 * w->k, rows, *w, e, ws, s)
                                          : qgemm_stream_launch(tm / 8, ap + (size_t)r0 * w->k, rows, *w, e, ws, s);
     if (rc != Q38_OK) return rc;
   }

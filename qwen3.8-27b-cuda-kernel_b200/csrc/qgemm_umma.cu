@@ -86,15 +86,17 @@ struct UmmaArgs {
   float eps;
   float* ws;
   int* counters;
-  int tiles, kg;
-  long long units;
+  int tiles, kg;   // 128-column weight tiles, 64-wide k-groups
+  int mblocks;     // token blocks of TOK rows handled in one launch (work item = (token block, weight tile))
+  int items;       // tiles * mblocks
+  long long units; // items * kg
   int split;
   DecodeConsts dc;
 };
 
 __device__ __forceinline__ long long u_begin(const UmmaArgs& a, int cta, int grid) {
   if (a.split) return (long long)cta * a.units / grid;
-  return ((long long)cta * a.tiles / grid) * a.kg;
+  return ((long long)cta * a.items / grid) * a.kg;
 }
 
 // Bounded wait that also gives up once another thread of the CTA has given up (the flag is polled only on the slow
@@ -215,7 +217,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     uint32_t it = 0;
     bool alive = true;
     for (long long u = u0; u < u1 && alive;) {
-      const int tile = int(u / a.kg), kg_a = int(u % a.kg);
+      const int tile = int(u / a.kg) % a.tiles, kg_a = int(u % a.kg);
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
       for (int g = kg_a; g < kg_b && alive; g += kGroupsPerStage, ++it) {
         const int s = it % C::kStages;
@@ -262,6 +264,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       for (long long u = u0; u < u1 && alive;) {
         const int kg_a = int(u % a.kg);
         const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+        const int row0 = (int(u / a.kg) / a.tiles) * TOK;  // first token of this item's token block
         for (int g = kg_a; g < kg_b; g += C::kSpu, ++uc) {
           const int slot = uc % C::kUnits;
           const int nu = min(C::kSpu, kg_b - g);
@@ -272,7 +275,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           for (int gi = 0; gi < nu; ++gi)
 #pragma unroll
             for (int nh = 0; nh < TOK / C::kMmaN; ++nh)
-              tma_load_2d(xs + gi * C::kXBytes + nh * C::kMmaN * 128, &xmap, (g + gi) * 64, nh * C::kMmaN, &op_full[slot]);
+              tma_load_2d(xs + gi * C::kXBytes + nh * C::kMmaN * 128, &xmap, (g + gi) * 64, row0 + nh * C::kMmaN,
+                          &op_full[slot]);
         }
         u += kg_b - kg_a;
       }
@@ -393,7 +397,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       }
     };
     for (long long u = u0; u < u1; ++seg) {
-      const int tile = int(u / a.kg), kg_a = int(u % a.kg);
+      const int item = int(u / a.kg), kg_a = int(u % a.kg);
+      const int tile = item % a.tiles;          // weight tile
+      const int row0 = (item / a.tiles) * TOK;  // first token of the token block
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
       for (int g = kg_a; g < kg_b; g += kGroupsPerStage) {
         const int ng = min(kGroupsPerStage, kg_b - g);
@@ -459,11 +465,13 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       // ---- epilogue of this tile segment ----
       const bool got = __all_sync(0xffffffffu, wait_flag(acc_full, seg & 1, flags, 0x307));
       tc_fence_after();
-      if (seg == 0) {  // first use of activations-side data by these warps: the row scales of the folded RMSNorm
-        pdl_wait();
-        row_scales_to_smem(a.partials_in, a.m, TOK, a.hidden, a.eps, rs_sm, et, kDecodeThreads);
+      if (seg == 0 || a.mblocks > 1) {  // the row scales of the folded RMSNorm for this token block
+        if (seg == 0) pdl_wait();       // first use of activations-side data by these warps
+        row_scales_to_smem(a.partials_in ? a.partials_in + (size_t)row0 * (a.hidden / 128) : nullptr, a.m - row0, TOK,
+                           a.hidden, a.eps, rs_sm, et, kDecodeThreads);
         named_bar_sync(1, kDecodeThreads);
       }
+      const int m_here = a.m - row0;  // valid tokens of this block (may exceed TOK)
       const bool whole = kg_a == 0 && kg_b == a.kg;
       const int n_row = 32 * quarter + lane;  // row of the tile this thread reads from TMEM
       const int n_glob = tile * kTileN + n_row;
@@ -478,11 +486,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           for (int j = 0; j < 16; ++j) {
             const int col = col0 + j;
             float r = 0.0f;
-            if (col < a.m) {
-              float* rp = a.residual + (size_t)col * a.n + n_glob;
+            if (col < m_here) {
+              float* rp = a.residual + (size_t)(row0 + col) * a.n + n_glob;
               r = *rp + v[j];
               *rp = r;
-              a.xbf[(size_t)col * a.n + n_glob] = __float2bfloat16_rn(r);
+              a.xbf[(size_t)(row0 + col) * a.n + n_glob] = __float2bfloat16_rn(r);
             }
             const float ss = warp_sum(r * r);
             if (lane == 0) part_sm[col * 4 + quarter] = ss;
@@ -495,13 +503,14 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           const float x = v[j] * rs_sm[col];
           if (a.kind == Q38_EPI_SWIGLU) {
             const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-            if ((lane & 1) == 0 && col < a.m && n_glob < n_lim)
-              static_cast<__nv_bfloat16*>(a.out)[(size_t)col * a.ldo + n_glob / 2] = __float2bfloat16_rn(silu_f(x) * other);
-          } else if (col < a.m && n_glob < n_lim) {
+            if ((lane & 1) == 0 && col < m_here && n_glob < n_lim)
+              static_cast<__nv_bfloat16*>(a.out)[(size_t)(row0 + col) * a.ldo + n_glob / 2] =
+                  __float2bfloat16_rn(silu_f(x) * other);
+          } else if (col < m_here && n_glob < n_lim) {
             if (a.kind == Q38_EPI_STORE_BF16)
-              static_cast<__nv_bfloat16*>(a.out)[(size_t)col * a.ldo + n_glob] = __float2bfloat16_rn(x);
+              static_cast<__nv_bfloat16*>(a.out)[(size_t)(row0 + col) * a.ldo + n_glob] = __float2bfloat16_rn(x);
             else
-              static_cast<float*>(a.out)[(size_t)col * a.ldo + n_glob] = x;
+              static_cast<float*>(a.out)[(size_t)(row0 + col) * a.ldo + n_glob] = x;
           }
         }
       };
@@ -572,9 +581,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       }
       if (a.kind == Q38_EPI_RESIDUAL) {
         named_bar_sync(2, kDecodeThreads);
-        if (run_epilogue && et < a.m && et < TOK) {
+        if (run_epilogue && et < m_here && et < TOK) {
           const float* p = part_sm + et * 4;
-          a.partials_out[(size_t)et * (a.n / 128) + tile] = (p[0] + p[1]) + (p[2] + p[3]);
+          a.partials_out[(size_t)(row0 + et) * (a.n / 128) + tile] = (p[0] + p[1]) + (p[2] + p[3]);
         }
       }
       named_bar_sync(2, kDecodeThreads);
@@ -606,7 +615,7 @@ EncodeFn encode_fn() {
 }
 
 template <int BITS, int TOK>
-int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
+int launch_one(const __nv_bfloat16* a_ptr, int m, int mblocks, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
                const q38_gemm_workspace* ws, cudaStream_t stream) {
   using C = UCfg<BITS, TOK>;
   static const cudaError_t attr =
@@ -643,7 +652,9 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.eps = ep.eps;
   a.tiles = w.n / kTileN;
   a.kg = w.k / 64;
-  a.units = (long long)a.tiles * a.kg;
+  a.mblocks = mblocks;
+  a.items = a.tiles * mblocks;
+  a.units = (long long)a.items * a.kg;
   a.dc = decode_consts(BITS);
   const int sms = num_sms();
   // How the (tile, k-group) list is cut over the CTAs. Every cut inside a tile costs a partial-tile round trip
@@ -654,7 +665,10 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   //     tokens), an even cut over all SMs (stream-K) otherwise.
   const bool have_ws = ws && ws->partials && ws->counters && ws->num_counters >= a.tiles;
   int grid;
-  if (a.tiles < sms) {
+  if (mblocks > 1) {  // several token blocks per launch: enough whole items to spread, no cut inside a tile
+    grid = std::min(sms, a.items);
+    a.split = 0;
+  } else if (a.tiles < sms) {
     int s = sms / a.tiles;
     s = std::min(s, TOK >= 256 ? 3 : 8);
     s = std::max(1, std::min(s, a.kg / 8));
@@ -676,33 +690,34 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
 }
 
 template <int BITS>
-int launch_bits(int tok, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
-                const q38_gemm_workspace* ws, cudaStream_t s) {
+int launch_bits(int tok, int mblocks, const __nv_bfloat16* a, int m, const q38_bq_weight& w,
+                const q38_gemm_epilogue& ep, const q38_gemm_workspace* ws, cudaStream_t s) {
   switch (tok) {
-    case 32: return launch_one<BITS, 32>(a, m, w, ep, ws, s);
-    case 64: return launch_one<BITS, 64>(a, m, w, ep, ws, s);
-    case 128: return launch_one<BITS, 128>(a, m, w, ep, ws, s);
-    case 256: return launch_one<BITS, 256>(a, m, w, ep, ws, s);
+    case 32: return launch_one<BITS, 32>(a, m, mblocks, w, ep, ws, s);
+    case 64: return launch_one<BITS, 64>(a, m, mblocks, w, ep, ws, s);
+    case 128: return launch_one<BITS, 128>(a, m, mblocks, w, ep, ws, s);
+    case 256: return launch_one<BITS, 256>(a, m, mblocks, w, ep, ws, s);
     default:
       if constexpr (BITS == 8) {
         set_error("qgemm: the 512-token configuration is not built for 8-bit weights");
         return Q38_ERR_INVALID;
       } else {
-        return launch_one<BITS, 512>(a, m, w, ep, ws, s);
+        return launch_one<BITS, 512>(a, m, 1, w, ep, ws, s);
       }
   }
 }
 
 }  // namespace
 
-// m <= tok, tok in {32, 64, 128, 256, 512}. Called by the dispatcher in qgemm.cu.
-int qgemm_umma_launch(int tok, const __nv_bfloat16* a, int m, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
-                      const q38_gemm_workspace* ws, cudaStream_t s) {
+// m <= tok * mblocks, tok in {32, 64, 128, 256, 512} (mblocks > 1: that many token blocks of `tok` rows in one
+// launch, whole tiles per CTA; not with tok = 512). Called by the dispatcher in qgemm.cu.
+int qgemm_umma_launch(int tok, int mblocks, const __nv_bfloat16* a, int m, const q38_bq_weight& w,
+                      const q38_gemm_epilogue& ep, const q38_gemm_workspace* ws, cudaStream_t s) {
   switch (w.bits) {
-    case 4: return launch_bits<4>(tok, a, m, w, ep, ws, s);
-    case 5: return launch_bits<5>(tok, a, m, w, ep, ws, s);
-    case 6: return launch_bits<6>(tok, a, m, w, ep, ws, s);
-    default: return launch_bits<8>(tok, a, m, w, ep, ws, s);
+    case 4: return launch_bits<4>(tok, mblocks, a, m, w, ep, ws, s);
+    case 5: return launch_bits<5>(tok, mblocks, a, m, w, ep, ws, s);
+    case 6: return launch_bits<6>(tok, mblocks, a, m, w, ep, ws, s);
+    default: return launch_bits<8>(tok, mblocks, a, m, w, ep, ws, s);
   }
 }
 

@@ -112,7 +112,7 @@ def time_gemm(pkg, copies, ws, m, config, iters=20):
 def configs_for(pkg, bits):
     """Every tile configuration built for this bit width (the 512-token pass does not exist for 8-bit weights)."""
     K = pkg.kernels()
-    return [c for c in range(K.q38_qgemm_num_configs()) if not (bits == 8 and K.q38_qgemm_config_tile_m(c) == 512)]
+    return [c for c in range(K.q38_qgemm_num_configs()) if not (bits == 8 and K.q38_qgemm_config_name(c) == b"umma_t512")]
 
 
 def main(argv=None):
