@@ -91,7 +91,7 @@ def weight_bytes_by_role(cfg, recipe):
 
 
 def op_bytes(cfg, recipe, batch, ctx_sum):
-    """Algorithmic bytes per decode step of every op class (the per-unit figures of DESIGN.md)."""
+    """Algorithmic bytes per decode step of every op class (weights once, KV of every context token, GDN state twice)."""
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     lk, lv = cfg["linear_num_key_heads"], cfg["linear_num_value_heads"]

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) gdn_ab_kernel(const __nv_bfloat16* __rest
 // ---------------------------------------------------------------------------------------------------
 // gdn_conv: depthwise causal conv (width 4) + SiLU over the [q | k | v] channels; q/k heads are
 // L2-normalised (x * rsqrt(sum x^2 + 1e-6)), q additionally scaled by 1/sqrt(128).
-// Token-parallel: one CTA per (128-channel head block, token). The three previous inputs of a channel
+// Token-parallel: one CTA per (128-channel head block, 1 or 8 consecutive tokens). The three previous inputs of a channel
 // come from the same chunk's earlier rows of `proj`, or from the conv state for the first tokens of a
 // sequence's chunk. A second small kernel then rolls the conv state forward by the chunk.
 // ---------------------------------------------------------------------------------------------------
@@ -104,43 +104,48 @@ __global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __re
                                                        __nv_bfloat16* __restrict__ conv_state,
                                                        const int* __restrict__ seq_start,
                                                        const int* __restrict__ seq_slot,
-                                                       const int* __restrict__ tok_seq, int roll_state) {
+                                                       const int* __restrict__ tok_seq, int roll_state, int num_tokens,
+                                                       int tokens_per_cta) {
   pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
   pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
-  const int c = blockIdx.x * 128 + threadIdx.x, m = blockIdx.y;
-  const int b = tok_seq[m];
-  const int i = m - seq_start[b];  // index of the token inside its sequence's chunk
-  __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
+  __shared__ float red[4];
+  const int c = blockIdx.x * 128 + threadIdx.x;
   const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)c * 4);
-  float x[4];
-  __nv_bfloat16 xb[4];
+  const int m_end = min(num_tokens, (int(blockIdx.y) + 1) * tokens_per_cta);
+  for (int m = blockIdx.y * tokens_per_cta; m < m_end; ++m) {
+    const int b = tok_seq[m];
+    const int i = m - seq_start[b];  // index of the token inside its sequence's chunk
+    __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
+    float x[4];
+    __nv_bfloat16 xb[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {  // x[j] = input 3 - j steps back
-    const int back = 3 - j;
-    xb[j] = back <= i ? proj[(size_t)(m - back) * ld_proj + c] : st[(size_t)(3 + i - back) * conv_dim + c];
-    x[j] = __bfloat162float(xb[j]);
+    for (int j = 0; j < 4; ++j) {  // x[j] = input 3 - j steps back
+      const int back = 3 - j;
+      xb[j] = back <= i ? proj[(size_t)(m - back) * ld_proj + c] : st[(size_t)(3 + i - back) * conv_dim + c];
+      x[j] = __bfloat162float(xb[j]);
+    }
+    if (roll_state) {  // one token per sequence: this thread is the only reader of its channel's taps, so it also rolls them
+      st[c] = xb[1];
+      st[(size_t)conv_dim + c] = xb[2];
+      st[(size_t)2 * conv_dim + c] = xb[3];
+    }
+    float acc = 0.0f;
+    acc += w.x * x[0];
+    acc += w.y * x[1];
+    acc += w.z * x[2];
+    acc += w.w * x[3];
+    float y = silu_f(acc);
+    if (c < 2 * key_dim) {  // block-uniform: the 128 channels of a CTA are one q or k head
+      const float ss = warp_sum(y * y);
+      __syncthreads();  // the previous token's readers of red[] are done
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      const float total = red[0] + red[1] + red[2] + red[3];
+      y *= 1.0f / sqrtf(total + 1e-6f);
+      if (c < key_dim) y *= 0.08838834764831845f;  // 1 / sqrt(128)
+    }
+    qkv[(size_t)m * conv_dim + c] = y;
   }
-  if (roll_state) {  // one token per sequence: this thread is the only reader of its channel's taps, so it also rolls them
-    st[c] = xb[1];
-    st[(size_t)conv_dim + c] = xb[2];
-    st[(size_t)2 * conv_dim + c] = xb[3];
-  }
-  float acc = 0.0f;
-  acc += w.x * x[0];
-  acc += w.y * x[1];
-  acc += w.z * x[2];
-  acc += w.w * x[3];
-  float y = silu_f(acc);
-  if (c < 2 * key_dim) {  // block-uniform: the 128 channels of a CTA are one q or k head
-    __shared__ float red[4];
-    const float ss = warp_sum(y * y);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    const float total = red[0] + red[1] + red[2] + red[3];
-    y *= 1.0f / sqrtf(total + 1e-6f);
-    if (c < key_dim) y *= 0.08838834764831845f;  // 1 / sqrt(128)
-  }
-  qkv[(size_t)m * conv_dim + c] = y;
 }
 
 __global__ void __launch_bounds__(128) gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
@@ -882,9 +887,12 @@ extern "C" int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d,
   // decode batches (one token per sequence) roll the conv state inside the conv kernel; longer runs need the second
   // kernel, because the first three tokens of a run all read the old taps
   const int roll = batch->max_tokens_per_seq == 1 ? 1 : 0;
-  (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, batch->num_tokens), dim3(128), 0, s, 
-      proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128, p->gdn_layer, st->num_gdn_layers, cs,
-      batch->seq_start, batch->seq_slot, batch->tok_seq, roll);
+  // decode-sized steps: one token per CTA (latency); prefill-sized steps: eight, to keep the CTA count in the thousands
+  const int per_cta = batch->num_tokens >= 256 ? 8 : 1;
+  (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, (batch->num_tokens + per_cta - 1) / per_cta),
+                      dim3(128), 0, s, proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128,
+                      p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot, batch->tok_seq, roll,
+                      batch->num_tokens, per_cta);
   Q38_LAUNCH_OK("gdn_conv_kernel");
   if (roll) return Q38_OK;
   (void)launch_kernel(gdn_conv_state_kernel, dim3(d->conv_dim / 128, batch->num_seqs), dim3(128), 0, s, 

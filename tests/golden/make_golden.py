@@ -1,9 +1,9 @@
 """Generates the golden fixtures of tests/golden/ from the REFERENCE's own code.
 
-Run once on a machine that has the reference checkout (default /root/reference) and oracle/_ref built
+Run once on a machine that has the reference checkout (--reference PATH) and oracle/_ref built
 (`make -C oracle ref`). The GPU box has neither; it only reads the committed fixtures.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference PATH
 
 Fixtures written:
   bq_golden.npz        per bit width: a weight matrix, the reference quantiser's codes / scales

@@ -82,9 +82,10 @@ def _worker(rank, world, port, out_dir, graph_from):
 
 
 def _log_dir(tmp_path, name):
-    out = ROOT / "gpurun_out"
-    d = out / name if out.is_dir() else tmp_path
-    d.mkdir(exist_ok=True)
+    """Where the ranks write their progress logs: Q38_TEST_LOG_DIR if set (to keep them after the run), else tmp."""
+    base = os.environ.get("Q38_TEST_LOG_DIR")
+    d = Path(base) / name if base else tmp_path
+    d.mkdir(parents=True, exist_ok=True)
     return d
 
 
