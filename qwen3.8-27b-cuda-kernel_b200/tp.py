@@ -262,14 +262,8 @@ class TPRunner:
             torch.cuda.synchronize()
             self._set_inputs([token], pos)
             g = torch.cuda.CUDAGraph()
-            # kernels next to captured collectives (which sit on the process group's own stream) get plain edges
-            if self.dist is not None:
-                self.K.q38_set_dependent_launch(0)
-            try:
-                with torch.cuda.graph(g):
-                    self._run(1)
-            finally:
-                self.K.q38_set_dependent_launch(1)
+            with torch.cuda.graph(g):
+                self._run(1)
             self._graph = g
             # the capture did not execute: the state still holds the warm-up step's effect, which equals this step's
             return
