@@ -8,10 +8,11 @@
 //
 // Design (B200):
 //   * BQ planes are n-block-major: for one 64-column block all of K is one contiguous byte run in each
-//     plane. A tile is 128 columns (2 blocks); the stream-K work list is (tile, 64-wide k-group) in
-//     memory order, cut evenly over one persistent CTA per SM, so each CTA streams two contiguous runs
-//     per plane with large 1-D bulk (TMA) copies into a multi-stage shared-memory ring (mbarrier
-//     full/empty pairs, one producer warp). Weights carry an L2 evict-first policy: they are read once.
+//     plane. A tile is 128 columns (2 blocks); the work list is (tile, 64-wide k-group) in memory order,
+//     cut over one persistent CTA per SM (whole tiles, s CTAs inside each tile, or an even cut: the
+//     launcher decides), so each CTA streams two contiguous runs per plane with large 1-D bulk (TMA)
+//     copies into a multi-stage shared-memory ring (mbarrier full/empty pairs, one producer warp).
+//     Weights carry an L2 evict-first policy: they are read once.
 //   * The activation chunk of a stage arrives through a 2-D tensor map with the 128-byte swizzle, rows
 //     beyond M zero-filled by the TMA unit.
 //   * 16 consumer warps = 2 column blocks x 8 k-groups of a stage (the decode chain is latency-bound per warp,

@@ -1,26 +1,31 @@
-// BQ GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for 17 <= M <= 256 tokens
-// per pass: large decode batches and prefill chunks. Same contract and epilogues as the streaming kernel
+// BQ GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for 17 <= M <= 512 tokens
+// per launch: large decode batches and prefill chunks. Same contract and epilogues as the streaming kernel
 // (qgemm_stream.cu); replaces kernels::qgemm of the reference (src/kernels/kernels.h:119-121) for these M.
 //
 // Orientation: the weights are the MMA's A operand (M_mma = 128 output columns = two 64-column BQ blocks),
-// the tokens are its N operand (N_mma = 32..256), so any token count fills the 128 TMEM lanes.
-// One persistent CTA per SM walks a stream-K work list of (tile, 64-wide k-group). Three independent rings:
-//   raw ring     the BQ planes of 4 k-groups per stage (contiguous per 64-column block: 1-D bulk copies, L2
-//                evict-first). It is as deep as shared memory allows (about 100 KB in flight per SM), because the
-//                achieved HBM rate of this kernel is set by the bytes in flight;
-//   x ring       one activation k-slice [TOK][64] bf16 per slot (2-D tensor map, 128-byte swizzle, rows >= M
-//                zero-filled), L2-resident, so a few slots suffice;
-//   slice ring   decoded bf16 operand slices [128 n][64 k] in the K-major 128-byte-swizzled layout a UMMA
-//                descriptor reads.
+// the tokens are its N operand (N_mma = 32..256; 512 tokens = two MMAs over all 512 TMEM columns), so any token
+// count fills the 128 TMEM lanes. One persistent CTA per SM walks a list of (work item, 64-wide k-group), a work
+// item being a weight tile (or a (token block, weight tile) pair when a launch covers two token blocks); how the
+// list is cut over the CTAs - whole tiles, s CTAs inside each tile, or an even cut - is chosen by the launcher.
+// Two rings:
+//   raw ring      the BQ planes of 4 k-groups per stage (contiguous per 64-column block: 1-D bulk copies, L2
+//                 evict-first), as deep as shared memory allows next to the operand ring;
+//   operand ring  units of one or two decoded bf16 slices [128 n][64 k] in the K-major 128-byte-swizzled layout a
+//                 UMMA descriptor reads, each with its activation slices [TOK][64] bf16 (2-D tensor map, same
+//                 swizzle, rows >= M zero-filled). One mbarrier per unit collects the decode warps' arrivals and
+//                 the activation copies' bytes; one tcgen05.commit hands the unit back.
 // Warp roles:
 //   warp 0       raw producer (six copies per stage, one lane each);
-//   warp 1       one elected thread issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32) per 16-wide k step and
-//                tcgen05.commit to hand slices / x slots / the accumulator back;
-//   warp 2       activation producer;  warp 3 idle (keeps the decode warps aligned to the TMEM lane quarters);
+//   warp 1       stays converged; one elected lane issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32) per 16-wide
+//                k step with descriptors precomputed by addition, and tcgen05.commit per unit / per accumulator;
+//   warp 2       activation producer - the first thread that touches data of earlier kernels (griddepcontrol.wait);
+//                everything before it (set-up, TMEM allocation, weight prefetch and decode) overlaps the previous
+//                kernel's tail;
+//   warp 3       idle (keeps the decode warps aligned to the TMEM lane quarters);
 //   warps 4-19   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> 4-byte
-//                bank-conflict-free stores into a slice; 8 warps fill one slice, two slices per pass. The same
-//                warps run the epilogue out of TMEM (tcgen05.ld).
-// Partial tiles (stream-K) go through the caller's workspace; the last-arriving CTA sums them in CTA order, so
+//                bank-conflict-free stores into a slice, two slabs per barrier round trip. The same warps run
+//                the epilogue out of TMEM (tcgen05.ld).
+// Partial tiles go through the caller's workspace; the tile's last-arriving CTA sums them in CTA order, so
 // results are bit-reproducible. Every wait is bounded; TMEM is always released before the kernel ends.
 #include <algorithm>
 
