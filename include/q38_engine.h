@@ -68,6 +68,14 @@ typedef struct q38e_prefill_row {
   int step;
 } q38e_prefill_row;
 
+/* GEMM tile-configuration table (qwen38::load_tuning / install_tuning / lookup_tuning, include/qwen38/tuning.h,
+ * src/tuning.cpp:24-70): a JSON file {"device": ..., "entries": [{bits, n, k, m_max, config, us}]}, as written by the
+ * GEMM sweep (gemm_bench.py --sweep --save). Loading installs the table into the kernel library's dispatcher for this
+ * process; an empty path clears it. q38e_tuning_lookup returns the configuration id the table gives for a call, or
+ * -1 (the dispatcher's own choice). */
+int q38e_tuning_load(const char* path);
+int q38e_tuning_lookup(int bits, int n, int k, int m);
+
 /* ModelFile */
 int q38e_model_open(const char* path, q38e_model** out);
 void q38e_model_close(q38e_model* m);

@@ -79,6 +79,16 @@ def default_runner_options(**kw) -> RunnerOptions:
     return o
 
 
+def load_tuning(path) -> None:
+    """Installs a GEMM tile-configuration table (JSON written by gemm_bench.py --sweep --save); "" clears it."""
+    _ok(lib().q38e_tuning_load(str(path).encode()))
+
+
+def tuning_lookup(bits: int, n: int, k: int, m: int) -> int:
+    """Configuration id the installed table gives for a call, -1 = the dispatcher's own choice."""
+    return int(lib().q38e_tuning_lookup(bits, n, k, m))
+
+
 class Model:
     def __init__(self, path):
         self.h = C.c_void_p()

@@ -84,6 +84,14 @@ void q38e_default_runner_options(q38e_runner_options* o) {
   o->verbose = d.verbose;
 }
 
+int q38e_tuning_load(const char* path) {
+  return guard([&] {
+    if (path == nullptr || path[0] == '\0') install_tuning({});
+    else load_tuning(path);
+  });
+}
+int q38e_tuning_lookup(int bits, int n, int k, int m) { return lookup_tuning(bits, n, k, m); }
+
 int q38e_model_open(const char* path, q38e_model** out) {
   return guard([&] {
     auto m = std::make_unique<q38e_model>();

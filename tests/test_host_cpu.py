@@ -51,3 +51,27 @@ def test_engine_library_exports_declared_symbols():
     lib = eng.lib()
     for name in declared:
         assert hasattr(lib, name), name
+
+
+def test_tuning_table_round_trip(tmp_path):
+    """A table in the layout the GEMM sweep writes is installed into the dispatcher's lookup: the smallest matching
+    m_max wins, unknown shapes fall back to the dispatcher's own choice (-1), an empty path clears the table."""
+    import json
+    table = {"device": "test", "entries": [
+        {"bits": 5, "n": 5120, "k": 6144, "m_max": 64, "config": 3, "us": 21.8},
+        {"bits": 5, "n": 5120, "k": 6144, "m_max": 8, "config": 0, "us": 16.7},
+        {"bits": 4, "n": 34816, "k": 5120, "m_max": 512, "config": 6, "us": 148.0}]}
+    path = tmp_path / "tuning.json"
+    path.write_text(json.dumps(table))
+    eng.load_tuning(path)
+    assert eng.tuning_lookup(5, 5120, 6144, 1) == 0
+    assert eng.tuning_lookup(5, 5120, 6144, 8) == 0
+    assert eng.tuning_lookup(5, 5120, 6144, 9) == 3
+    assert eng.tuning_lookup(5, 5120, 6144, 65) == -1
+    assert eng.tuning_lookup(4, 34816, 5120, 300) == 6
+    assert eng.tuning_lookup(8, 248320, 5120, 1) == -1
+    eng.load_tuning("")
+    assert eng.tuning_lookup(5, 5120, 6144, 1) == -1
+    (tmp_path / "bad.json").write_text("{not json")
+    with pytest.raises(eng.EngineError, match="malformed tuning table"):
+        eng.load_tuning(tmp_path / "bad.json")
