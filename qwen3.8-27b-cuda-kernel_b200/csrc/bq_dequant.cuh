@@ -104,6 +104,21 @@ __device__ __forceinline__ void decode_slab(const uint32_t (&lo)[4], const uint3
   decode_all<BITS>(lo, hi, s2, w, dc, std::make_integer_sequence<int, 16>{});
 }
 
+// Half a slab = the lane's pairs of four adjacent columns j = 4 f + j', j' = 0..3, given as lo[0..1] = its lo words
+// 2 f, 2 f + 1; hi[] = the matching hi words moved to the front (5 bit: the word shifted right by 8 f; 6 bit: word
+// f; 8 bit: words 2 f, 2 f + 1); s2[0..3] = the four columns' scales. decode_fragment<F> decodes the pairs of
+// columns j' = 2 F, 2 F + 1 in the register order of an mma.m16n8k16 A fragment:
+// a0 = (row g, k 2t..) a1 = (row g + 8, k 2t..) a2 = (row g, k 2t + 8..) a3 = (row g + 8, k 2t + 8..).
+template <int BITS, int F>
+__device__ __forceinline__ void decode_fragment(const uint32_t (&lo)[4], const uint32_t (&hi)[4], const uint32_t (&s2)[8],
+                                                const DecodeConsts& dc, uint32_t& a0, uint32_t& a1, uint32_t& a2,
+                                                uint32_t& a3) {
+  a0 = decode_pair<BITS, 4 * F + 0>(lo, hi, s2[2 * F], dc);
+  a2 = decode_pair<BITS, 4 * F + 1>(lo, hi, s2[2 * F], dc);
+  a1 = decode_pair<BITS, 4 * F + 2>(lo, hi, s2[2 * F + 1], dc);
+  a3 = decode_pair<BITS, 4 * F + 3>(lo, hi, s2[2 * F + 1], dc);
+}
+
 // Expands the lane's eight scales (one 16-byte read: columns 8 j + g, j = 0..7) into duplicated pairs.
 __device__ __forceinline__ void expand_scales(const uint4& sv, uint32_t (&s2)[8]) {
   const uint32_t words[4] = {sv.x, sv.y, sv.z, sv.w};

@@ -15,33 +15,33 @@ struct ConfigInfo {
   int tile_m;   // tokens per launch
   bool umma;
   int mblocks;  // tcgen05 kernel: token blocks of tile_m / mblocks rows inside one launch
+  bool a_in_tmem;  // tcgen05 kernel: decoded weights reach the MMA through tensor memory
 };
 constexpr ConfigInfo kConfigs[] = {
-    {"stream_m8", 8, false, 1}, {"stream_m16", 16, false, 1}, {"umma_t32", 32, true, 1},
-    {"umma_t64", 64, true, 1},  {"umma_t128", 128, true, 1},  {"umma_t256", 256, true, 1},
-    {"umma_t512", 512, true, 1}, {"umma_t256x2", 512, true, 2},
+    {"stream_m8", 8, false, 1, false},  {"stream_m16", 16, false, 1, false}, {"umma_t32", 32, true, 1, false},
+    {"umma_t64", 64, true, 1, false},   {"umma_t128", 128, true, 1, false},  {"umma_t256", 256, true, 1, false},
+    {"umma_t512", 512, true, 1, false}, {"umma_t256x2", 512, true, 2, false}, {"tmem_t32", 32, true, 1, true},
+    {"tmem_t64", 64, true, 1, true},    {"tmem_t128", 128, true, 1, true},   {"tmem_t256", 256, true, 1, true},
+    {"tmem_t256x2", 512, true, 2, true},
 };
 constexpr int kNumConfigs = int(sizeof(kConfigs) / sizeof(kConfigs[0]));
 
 q38_gemm_tuning_lookup g_tuning = nullptr;
 
 // Small batches stream the weights through mma.sync (tokens are the 8-wide operand); from 17 tokens on the
-// tcgen05 kernel keeps the accumulators in TMEM.
-// Above 256 tokens one pass over 512 of them halves the decode work per token; it needs the larger stream-K
-// workspace (2 * SMs * 128 * 512 floats) and is not built for 8-bit weights.
+// tcgen05 kernel keeps the accumulators in TMEM and, in the tmem_* configurations, also hands the decoded weights
+// to the MMA through TMEM (no shared-memory round trip of the bf16 tile: faster at every token count measured, so
+// the umma_* configurations are only reachable by explicit choice or through a tuning table).
+// Above 256 tokens two 256-token blocks share one launch (whole weight tiles per CTA).
 int auto_config(int m, const q38_bq_weight& w, const q38_gemm_workspace* ws) {
+  (void)ws;
   if (m <= 8) return 0;
-  if (m <= 16) return 1;
-  if (m <= 32) return 2;
-  if (m <= 64) return 3;
-  if (m <= 128) return 4;
-  if (m <= 256) return 5;
-  // few weight tiles and a short k: two 256-token blocks side by side give twice the whole-tile work items and need
-  // no cut in k (with a long k the three-way cut of the 512-token pass wins: 118 against 139 us on 5120 x 17408)
-  if (2 * (w.n / 128) <= num_sms() && w.k <= 8192) return 7;
-  if (w.bits == 8) return 5;
-  const bool roomy = ws && ws->partials && ws->partial_floats >= size_t(2) * size_t(num_sms()) * 128 * 512;
-  return roomy || w.n / 128 >= 3 * num_sms() ? 6 : 5;
+  if (m <= 16) return (w.n / 128 <= num_sms() && w.k <= 8192) ? 8 : 1;  // few short tiles: the tcgen05 kernel's finer cut wins
+  if (m <= 32) return 8;
+  if (m <= 64) return 9;
+  if (m <= 128) return 10;
+  if (m <= 256) return 11;
+  return 12;
 }
 
 // One lane decodes one slab exactly as the GEMM does and writes the 32 weights to W[n][k] (bf16).
@@ -123,7 +123,7 @@ extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const
     }
     if (e.partials_in) e.partials_in += (size_t)r0 * (e.hidden / 128);
     const int mb = kConfigs[config].mblocks;
-    const int rc = kConfigs[config].umma ? qgemm_umma_launch(tm / mb, mb, ap + (size_t)r0 * w->k, rows, *w, e, ws, s)
+    const int rc = kConfigs[config].umma ? qgemm_umma_launch(tm / mb, mb, kConfigs[config].a_in_tmem, ap + (size_t)r0 * w->k, rows, *w, e, ws, s)
                                          : qgemm_stream_launch(tm / 8, ap + (size_t)r0 * w->k, rows, *w, e, ws, s);
     if (rc != Q38_OK) return rc;
   }

@@ -47,14 +47,25 @@ constexpr int kWarpsPerSlice = 8;
 constexpr int kSliceBytes = kTileN * 128;  // one [128 n][64 k] bf16 operand slice
 constexpr int kSmemBudget = 226 * 1024;
 
-template <int BITS, int TOK>
+// ATM: the decoded weights go to tensor memory (tcgen05.st) and the MMA reads its A operand from there; shared memory
+// then holds only the raw planes and the activation slices.
+template <int BITS, int TOK, bool ATM>
 struct UCfg {
   using G = BqGeom<BITS>;
+  static_assert(!ATM || TOK <= 256, "accumulator and weight ring share the 512 TMEM columns");
   // operand unit: what one barrier round trip hands to the MMA thread = kSpu decoded slices + their activations
   static constexpr int kSpu = TOK <= 128 ? 2 : 1;
-  static constexpr int kUnits = TOK <= 64 ? 3 : TOK <= 128 ? 2 : TOK <= 256 ? 3 : 2;
+  static constexpr int kUnits = ATM ? (TOK <= 64 ? 6 : 4)
+                                    : (TOK <= 64 ? 3 : TOK <= 128 ? 2 : TOK <= 256 ? 3 : 2);
   static constexpr int kXBytes = TOK * 128;  // activation k-slice [TOK][64] bf16
-  static constexpr int kUnitBytes = kSpu * (kSliceBytes + kXBytes);
+  static constexpr int kWBytes = ATM ? 0 : kSliceBytes;  // decoded slice held in shared memory
+  static constexpr int kUnitBytes = kSpu * (kWBytes + kXBytes);
+  static constexpr int kDecodeWarpsPerUnit = ATM ? 4 * kSpu : kWarpsPerSlice;
+  // tensor memory: accumulator [128 lanes][TOK columns] at column 0, then (ATM) the ring of decoded units, one
+  // 64-wide k-group = 128 lanes x 32 columns of packed bf16 pairs
+  static constexpr int kACol0 = TOK < 32 ? 32 : TOK;
+  static constexpr int kUnitCols = kSpu * 32;
+  static_assert(!ATM || kACol0 + kUnits * kUnitCols <= 512, "tensor memory columns");
   static constexpr int kLoOff = 0;
   static constexpr int kHiOff = kLoOff + 2 * kGroupsPerStage * G::kLoGroupBytes;
   static constexpr int kScOff = kHiOff + 2 * kGroupsPerStage * G::kHiGroupBytes;
@@ -65,7 +76,7 @@ struct UCfg {
   static constexpr int kUnitOff = kStages * kStageBytes;
   static constexpr int kTailOff = kUnitOff + kUnits * kUnitBytes;
   static constexpr int kSmemBytes = 1024 + kTailOff + kTail;
-  static constexpr int kTmemCols = TOK < 32 ? 32 : TOK;
+  static constexpr int kTmemCols = ATM ? 512 : (TOK < 32 ? 32 : TOK);
   static constexpr int kMmaN = TOK < 256 ? TOK : 256;  // tokens per MMA instruction and per activation box
   static constexpr int kEpiChunks = TOK >= 64 ? 4 : 2;  // decode warps per TMEM lane quarter that run the epilogue
   static constexpr int kColsPerWarp = TOK / kEpiChunks;
@@ -142,6 +153,38 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// With the A operand in tensor memory an MMA reads [128 lanes][8 columns], column c of lane r = A[r][2c], A[r][2c+1].
+// The four MMAs of one 64-wide k-group in one block, so that the election and the operand arithmetic are paid once:
+// A = tensor memory columns a_tmem + 8 ks, B = shared-memory descriptor {b_lo + 2 ks, b_hi} (32 bytes per k16 step;
+// the 14-bit address field cannot carry), ks = 0..3. The first MMA overwrites the accumulator unless `accumulate`.
+__device__ __forceinline__ void umma_group_ta(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, leader;\n\t.reg .b32 a1, a2, a3, l1, l2, l3;\n\t.reg .b64 b0, b1, b2, b3;\n\t"
+      "elect.sync _|leader, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 t, %5, %5;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+      "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
+      "@leader tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b0, %4, p;\n\t"
+      "@leader tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, t;\n\t"
+      "@leader tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, t;\n\t"
+      "@leader tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Registers -> tensor memory, 16 lanes x 32 columns: lane (g = lane >> 2, t = lane & 3) of the warp gives
+// r[2 i] to TMEM lane g, column 4 i + t and r[2 i + 1] to TMEM lane g + 8, column 4 i + t - with two bf16 per
+// column that is the A fragment of mma.m16n8k16 (rows g / g + 8, k = 2 t + 8 h) for four 16-wide k slabs.
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile(
       "{\n\t.reg .pred leader;\n\t"
@@ -169,10 +212,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   return d;
 }
 
-template <int BITS, int TOK>
+template <int BITS, int TOK, bool ATM>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
-  using C = UCfg<BITS, TOK>;
+  using C = UCfg<BITS, TOK, ATM>;
   using G = BqGeom<BITS>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
@@ -200,7 +243,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       mbar_init(&raw_empty[s], kDecodeWarps);
     }
     for (int s = 0; s < C::kUnits; ++s) {
-      mbar_init(&op_full[s], kWarpsPerSlice + 1);  // eight decode warps + the activation copies' expect_tx
+      mbar_init(&op_full[s], C::kDecodeWarpsPerUnit + 1);  // the unit's decode warps + the activation copies' expect_tx
       mbar_init(&op_empty[s], 1);
     }
     mbar_init(acc_full, 1);
@@ -275,7 +318,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           const int nu = min(C::kSpu, kg_b - g);
           alive = wait_flag(&op_empty[slot], ((uc / C::kUnits) & 1) ^ 1, flags, 0x308);
           if (!alive) break;
-          uint8_t* xs = units + (size_t)slot * C::kUnitBytes + C::kSpu * kSliceBytes;
+          uint8_t* xs = units + (size_t)slot * C::kUnitBytes + C::kSpu * C::kWBytes;
           mbar_expect_tx(&op_full[slot], uint32_t(nu) * C::kXBytes);
           for (int gi = 0; gi < nu; ++gi)
 #pragma unroll
@@ -310,17 +353,31 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           if (!alive) break;
           tc_fence_after();
           const uint64_t da = desc0 + uint64_t((uint32_t(slot) * C::kUnitBytes) >> 4);
-          const uint64_t dx = da + uint64_t((C::kSpu * kSliceBytes) >> 4);
+          const uint64_t dx = da + uint64_t((C::kSpu * C::kWBytes) >> 4);
+          if constexpr (ATM) {
+            static_assert(!ATM || TOK == C::kMmaN, "one MMA covers all tokens");
+            const uint32_t ta = tmem_base + uint32_t(C::kACol0 + slot * C::kUnitCols);
+            const uint32_t b_lo = uint32_t(dx), b_hi = uint32_t(dx >> 32);
 #pragma unroll
-          for (int gi = 0; gi < C::kSpu; ++gi) {
-            if (gi < nu) {
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-                for (int nh = 0; nh < TOK / C::kMmaN; ++nh)
-                  umma_bf16(tmem_base + uint32_t(nh * C::kMmaN), da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
-                            dx + uint64_t((gi * C::kXBytes + nh * C::kMmaN * 128 + ks * 32) >> 4), idesc, accumulate);
+            for (int gi = 0; gi < C::kSpu; ++gi) {
+              if (gi < nu) {
+                umma_group_ta(tmem_base, ta + uint32_t(gi * 32), b_lo + uint32_t((gi * C::kXBytes) >> 4), b_hi, idesc,
+                              accumulate);
                 accumulate = 1;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int gi = 0; gi < C::kSpu; ++gi) {
+              if (gi < nu) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                  for (int nh = 0; nh < TOK / C::kMmaN; ++nh)
+                    umma_bf16(tmem_base + uint32_t(nh * C::kMmaN), da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
+                              dx + uint64_t((gi * C::kXBytes + nh * C::kMmaN * 128 + ks * 32) >> 4), idesc, accumulate);
+                  accumulate = 1;
+                }
               }
             }
           }
@@ -410,50 +467,124 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         const int ng = min(kGroupsPerStage, kg_b - g);
         const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
-        const int g0 = C::kSpu == 2 ? 2 * half : half;  // first of this warp's two k-groups of the stage
-        constexpr int kGStep = C::kSpu == 2 ? 1 : 2;      // distance to its second one
-        if (g0 < ng) {
-          const bool two = g0 + kGStep < ng;
-          uint32_t lo0[4] = {0, 0, 0, 0}, hi0[4] = {0, 0, 0, 0}, lo1[4] = {0, 0, 0, 0}, hi1[4] = {0, 0, 0, 0};
-          uint4 sv0 = make_uint4(0, 0, 0, 0), sv1 = sv0;
-          if (ok) {
-            load_raw(st, g0, lo0, hi0, sv0);
-            if (two) load_raw(st, g0 + kGStep, lo1, hi1, sv1);
-          }
-          uint32_t s2[8], w[16];
-          expand_scales(sv0, s2);
-          decode_slab<BITS>(lo0, hi0, s2, w, dc);
-          if constexpr (C::kSpu == 2) {
+        if constexpr (ATM) {
+          // One warp = one k-group of the stage x one TMEM lane quarter: 32 of the tile's 128 columns, i.e. half of
+          // a 64-column block (pairs j = 4 fh .. 4 fh + 3 of every slab: lo words 2 fh, 2 fh + 1), all four k16 slabs.
+          const int gi = dw >> 2;
+          const int ui = gi / C::kSpu;  // its unit among the stage's
+          if (ui * C::kSpu < ng) {
+            const bool have = ok && gi < ng;  // a unit at the end of a segment may lack its second k-group
+            const int anb = quarter >> 1, fh = quarter & 1;
+            // raw words of the four k16 slabs: the lane's two lo words of this half, the matching hi words, the scales
+            uint2 lv[4];
+            uint32_t h0[4], h1[4];
+            uint32_t s2[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s2[i] = 0;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              lv[k4] = make_uint2(0, 0);
+              h0[k4] = h1[k4] = 0;
+            }
+            if (have) {
+              const int rslot = anb * kGroupsPerStage + gi;
+              const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes + lane * 16 + fh * 8;
+              const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
+              const uint2 sv = *reinterpret_cast<const uint2*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl + 8 * fh);
+              s2[0] = __byte_perm(sv.x, 0, 0x1010);
+              s2[1] = __byte_perm(sv.x, 0, 0x3232);
+              s2[2] = __byte_perm(sv.y, 0, 0x1010);
+              s2[3] = __byte_perm(sv.y, 0, 0x3232);
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) {
+                lv[k4] = *reinterpret_cast<const uint2*>(lo_g + k4 * 512);
+                if constexpr (BITS == 5) {
+                  h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 128 + lane * 4) >> (8 * fh);
+                } else if constexpr (BITS == 6) {
+                  h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 256 + lane * 8 + fh * 4);
+                } else if constexpr (BITS == 8) {
+                  const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + k4 * 512 + lane * 16 + fh * 8);
+                  h0[k4] = hv.x;
+                  h1[k4] = hv.y;
+                }
+              }
+            }
             int slot;
             uint32_t par;
-            unit_at(half, slot, par);
+            unit_at(ui, slot, par);
             const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
-            uint8_t* base = units + (size_t)slot * C::kUnitBytes;
-            if (ok && free_slot) store_slice(base, w);
-            if (two) {
-              expand_scales(sv1, s2);
-              decode_slab<BITS>(lo1, hi1, s2, w, dc);
-              if (ok && free_slot) store_slice(base + kSliceBytes, w);
+            tc_fence_after();
+            const uint32_t ta = tmem_base + (uint32_t(32 * quarter) << 16) +
+                                uint32_t(C::kACol0 + slot * C::kUnitCols + (gi % C::kSpu) * 32);
+            // rows 0-15 of the quarter (pairs j' = 0, 1), then rows 16-31 (j' = 2, 3): each an mma A fragment per slab
+            {
+              uint32_t f[16];
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) {
+                const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
+                const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
+                decode_fragment<BITS, 0>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
+              }
+              if (have && free_slot) tmem_st_16x128b_x8(ta, f);
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) {
+                const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
+                const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
+                decode_fragment<BITS, 1>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
+              }
+              if (have && free_slot) tmem_st_16x128b_x8(ta + (16u << 16), f);
             }
-            fence_async_smem();
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&op_full[slot]);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              if (e == 0 || two) {
-                if (e == 1) {
-                  expand_scales(sv1, s2);
-                  decode_slab<BITS>(lo1, hi1, s2, w, dc);
+          }
+        } else {
+          const int g0 = C::kSpu == 2 ? 2 * half : half;  // first of this warp's two k-groups of the stage
+          constexpr int kGStep = C::kSpu == 2 ? 1 : 2;      // distance to its second one
+          if (g0 < ng) {
+            const bool two = g0 + kGStep < ng;
+            uint32_t lo0[4] = {0, 0, 0, 0}, hi0[4] = {0, 0, 0, 0}, lo1[4] = {0, 0, 0, 0}, hi1[4] = {0, 0, 0, 0};
+            uint4 sv0 = make_uint4(0, 0, 0, 0), sv1 = sv0;
+            if (ok) {
+              load_raw(st, g0, lo0, hi0, sv0);
+              if (two) load_raw(st, g0 + kGStep, lo1, hi1, sv1);
+            }
+            uint32_t s2[8], w[16];
+            expand_scales(sv0, s2);
+            decode_slab<BITS>(lo0, hi0, s2, w, dc);
+            if constexpr (C::kSpu == 2) {
+              int slot;
+              uint32_t par;
+              unit_at(half, slot, par);
+              const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+              uint8_t* base = units + (size_t)slot * C::kUnitBytes;
+              if (ok && free_slot) store_slice(base, w);
+              if (two) {
+                expand_scales(sv1, s2);
+                decode_slab<BITS>(lo1, hi1, s2, w, dc);
+                if (ok && free_slot) store_slice(base + kSliceBytes, w);
+              }
+              fence_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&op_full[slot]);
+            } else {
+  #pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                if (e == 0 || two) {
+                  if (e == 1) {
+                    expand_scales(sv1, s2);
+                    decode_slab<BITS>(lo1, hi1, s2, w, dc);
+                  }
+                  int slot;
+                  uint32_t par;
+                  unit_at(g0 + kGStep * e, slot, par);
+                  const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+                  if (ok && free_slot) store_slice(units + (size_t)slot * C::kUnitBytes, w);
+                  fence_async_smem();
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(&op_full[slot]);
                 }
-                int slot;
-                uint32_t par;
-                unit_at(g0 + kGStep * e, slot, par);
-                const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
-                if (ok && free_slot) store_slice(units + (size_t)slot * C::kUnitBytes, w);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&op_full[slot]);
               }
             }
           }
@@ -619,12 +750,12 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <int BITS, int TOK>
+template <int BITS, int TOK, bool ATM>
 int launch_one(const __nv_bfloat16* a_ptr, int m, int mblocks, const q38_bq_weight& w, const q38_gemm_epilogue& ep,
                const q38_gemm_workspace* ws, cudaStream_t stream) {
-  using C = UCfg<BITS, TOK>;
-  static const cudaError_t attr =
-      cudaFuncSetAttribute(qgemm_umma_kernel<BITS, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  using C = UCfg<BITS, TOK, ATM>;
+  static const cudaError_t attr = cudaFuncSetAttribute(qgemm_umma_kernel<BITS, TOK, ATM>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   Q38_CUDA_OK(attr);
   EncodeFn enc = encode_fn();
   Q38_REQUIRE(enc != nullptr, "qgemm: cuTensorMapEncodeTiled is not available from this driver");
@@ -689,25 +820,34 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, int mblocks, const q38_bq_weig
     a.ws = ws->partials;
     a.counters = ws->counters;
   }
-  (void)launch_kernel(qgemm_umma_kernel<BITS, TOK>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, xmap, a);
+  (void)launch_kernel(qgemm_umma_kernel<BITS, TOK, ATM>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, xmap, a);
   Q38_LAUNCH_OK("qgemm_umma_kernel");
   return Q38_OK;
 }
 
 template <int BITS>
-int launch_bits(int tok, int mblocks, const __nv_bfloat16* a, int m, const q38_bq_weight& w,
+int launch_bits(int tok, int mblocks, bool a_in_tmem, const __nv_bfloat16* a, int m, const q38_bq_weight& w,
                 const q38_gemm_epilogue& ep, const q38_gemm_workspace* ws, cudaStream_t s) {
+  if (a_in_tmem) {
+    switch (tok) {
+      case 32: return launch_one<BITS, 32, true>(a, m, mblocks, w, ep, ws, s);
+      case 64: return launch_one<BITS, 64, true>(a, m, mblocks, w, ep, ws, s);
+      case 128: return launch_one<BITS, 128, true>(a, m, mblocks, w, ep, ws, s);
+      case 256: return launch_one<BITS, 256, true>(a, m, mblocks, w, ep, ws, s);
+      default: set_error("qgemm: the weights-in-TMEM kernel serves up to 256 tokens per pass"); return Q38_ERR_INVALID;
+    }
+  }
   switch (tok) {
-    case 32: return launch_one<BITS, 32>(a, m, mblocks, w, ep, ws, s);
-    case 64: return launch_one<BITS, 64>(a, m, mblocks, w, ep, ws, s);
-    case 128: return launch_one<BITS, 128>(a, m, mblocks, w, ep, ws, s);
-    case 256: return launch_one<BITS, 256>(a, m, mblocks, w, ep, ws, s);
+    case 32: return launch_one<BITS, 32, false>(a, m, mblocks, w, ep, ws, s);
+    case 64: return launch_one<BITS, 64, false>(a, m, mblocks, w, ep, ws, s);
+    case 128: return launch_one<BITS, 128, false>(a, m, mblocks, w, ep, ws, s);
+    case 256: return launch_one<BITS, 256, false>(a, m, mblocks, w, ep, ws, s);
     default:
       if constexpr (BITS == 8) {
         set_error("qgemm: the 512-token configuration is not built for 8-bit weights");
         return Q38_ERR_INVALID;
       } else {
-        return launch_one<BITS, 512>(a, m, 1, w, ep, ws, s);
+        return launch_one<BITS, 512, false>(a, m, 1, w, ep, ws, s);
       }
   }
 }
@@ -716,13 +856,13 @@ int launch_bits(int tok, int mblocks, const __nv_bfloat16* a, int m, const q38_b
 
 // m <= tok * mblocks, tok in {32, 64, 128, 256, 512} (mblocks > 1: that many token blocks of `tok` rows in one
 // launch, whole tiles per CTA; not with tok = 512). Called by the dispatcher in qgemm.cu.
-int qgemm_umma_launch(int tok, int mblocks, const __nv_bfloat16* a, int m, const q38_bq_weight& w,
+int qgemm_umma_launch(int tok, int mblocks, bool a_in_tmem, const __nv_bfloat16* a, int m, const q38_bq_weight& w,
                       const q38_gemm_epilogue& ep, const q38_gemm_workspace* ws, cudaStream_t s) {
   switch (w.bits) {
-    case 4: return launch_bits<4>(tok, mblocks, a, m, w, ep, ws, s);
-    case 5: return launch_bits<5>(tok, mblocks, a, m, w, ep, ws, s);
-    case 6: return launch_bits<6>(tok, mblocks, a, m, w, ep, ws, s);
-    default: return launch_bits<8>(tok, mblocks, a, m, w, ep, ws, s);
+    case 4: return launch_bits<4>(tok, mblocks, a_in_tmem, a, m, w, ep, ws, s);
+    case 5: return launch_bits<5>(tok, mblocks, a_in_tmem, a, m, w, ep, ws, s);
+    case 6: return launch_bits<6>(tok, mblocks, a_in_tmem, a, m, w, ep, ws, s);
+    default: return launch_bits<8>(tok, mblocks, a_in_tmem, a, m, w, ep, ws, s);
   }
 }
 
