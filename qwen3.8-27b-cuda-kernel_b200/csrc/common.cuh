@@ -50,6 +50,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+#ifndef Q38_WAIT_HINT_NS
+#define Q38_WAIT_HINT_NS 1000
+#endif
+constexpr uint32_t kWaitHintNs = Q38_WAIT_HINT_NS;  // upper bound of one parked poll, nanoseconds
+
 // One poll of the barrier phase. The hint lets the hardware park the thread for up to about a microsecond while the
 // phase is incomplete (it resumes as soon as the phase completes), so that waiting warps do not take issue slots from
 // the warps that compute.
@@ -60,7 +65,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }

@@ -55,12 +55,16 @@ struct UCfg {
   static_assert(!ATM || TOK <= 256, "accumulator and weight ring share the 512 TMEM columns");
   // operand unit: what one barrier round trip hands to the MMA thread = kSpu decoded slices + their activations
   static constexpr int kSpu = TOK <= 128 ? 2 : 1;
-  static constexpr int kUnits = ATM ? (TOK <= 64 ? 6 : 4)
+#ifndef Q38_TMEM_UNITS_SMALL
+#define Q38_TMEM_UNITS_SMALL 6
+#endif
+  static constexpr int kUnits = ATM ? (TOK <= 64 ? Q38_TMEM_UNITS_SMALL : 4)
                                     : (TOK <= 64 ? 3 : TOK <= 128 ? 2 : TOK <= 256 ? 3 : 2);
   static constexpr int kXBytes = TOK * 128;  // activation k-slice [TOK][64] bf16
   static constexpr int kWBytes = ATM ? 0 : kSliceBytes;  // decoded slice held in shared memory
   static constexpr int kUnitBytes = kSpu * (kWBytes + kXBytes);
-  static constexpr int kDecodeWarpsPerUnit = ATM ? 4 * kSpu : kWarpsPerSlice;
+  static constexpr int kDecodeWarpsPerUnit = ATM ? 4 : kWarpsPerSlice;
+  static constexpr int kRawConsumers = ATM && kSpu == 2 ? kDecodeWarps / 2 : kDecodeWarps;  // warps that release a raw stage
   // tensor memory: accumulator [128 lanes][TOK columns] at column 0, then (ATM) the ring of decoded units, one
   // 64-wide k-group = 128 lanes x 32 columns of packed bf16 pairs
   static constexpr int kACol0 = TOK < 32 ? 32 : TOK;
@@ -72,7 +76,9 @@ struct UCfg {
   static constexpr int kStageBytes = kScOff + 2 * kGroupsPerStage * G::kScGroupBytes;  // a multiple of 1024
   static constexpr int kTail = TOK * 4 + TOK * 4 * 4 + 1024;  // row scales, per-quarter partial sums, barriers
   static constexpr int kFit = (kSmemBudget - 1024 - kTail - kUnits * kUnitBytes) / kStageBytes;
-  static constexpr int kStages = kFit > 8 ? 8 : kFit;
+  // (two-group TMEM units: a decode warp visits every other stage, so an even ring length keeps it on consecutive
+  // uses of the same slots - a parity wait cannot tell uses two apart)
+  static constexpr int kStages = kFit > 8 ? 8 : (ATM && kSpu == 2 ? kFit / 2 * 2 : kFit);
   static constexpr int kUnitOff = kStages * kStageBytes;
   static constexpr int kTailOff = kUnitOff + kUnits * kUnitBytes;
   static constexpr int kSmemBytes = 1024 + kTailOff + kTail;
@@ -240,7 +246,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   if (tid == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], kDecodeWarps);
+      mbar_init(&raw_empty[s], C::kRawConsumers);
     }
     for (int s = 0; s < C::kUnits; ++s) {
       mbar_init(&op_full[s], C::kDecodeWarpsPerUnit + 1);  // the unit's decode warps + the activation copies' expect_tx
@@ -446,6 +452,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     };
     // ring positions are carried along (slot + phase bit) instead of being derived from counters by division
     uint32_t seg = 0;
+    uint32_t stage_no = 0;       // raw stages consumed so far (all segments)
     int s = 0;                   // raw stage and the parity of its current use
     uint32_t s_par = 0;
     int u_slot = 0;              // operand slot of the first unit of the current stage, parity of its current use
@@ -465,81 +472,98 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
       for (int g = kg_a; g < kg_b; g += kGroupsPerStage) {
         const int ng = min(kGroupsPerStage, kg_b - g);
-        const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
         if constexpr (ATM) {
-          // One warp = one k-group of the stage x one TMEM lane quarter: 32 of the tile's 128 columns, i.e. half of
-          // a 64-column block (pairs j = 4 fh .. 4 fh + 3 of every slab: lo words 2 fh, 2 fh + 1), all four k16 slabs.
-          const int gi = dw >> 2;
-          const int ui = gi / C::kSpu;  // its unit among the stage's
-          if (ui * C::kSpu < ng) {
-            const bool have = ok && gi < ng;  // a unit at the end of a segment may lack its second k-group
-            const int anb = quarter >> 1, fh = quarter & 1;
-            // raw words of the four k16 slabs: the lane's two lo words of this half, the matching hi words, the scales
-            uint2 lv[4];
-            uint32_t h0[4], h1[4];
-            uint32_t s2[8];
+          // A warp owns one TMEM lane quarter: 32 of the tile's 128 columns, i.e. half of a 64-column block (pairs
+          // j = 4 fh .. 4 fh + 3 of every slab: lo words 2 fh, 2 fh + 1), and decodes whole 64-wide k-groups of it.
+          // Two-group units: the stage's two units x four quarters occupy eight warps; warps 0-7 take the even
+          // stages and warps 8-15 the odd ones, so a warp pays its barrier round trips once per two k-groups and
+          // has two stage times for them. One-group units: sixteen warps = four k-groups x four quarters, every stage.
+          // Either way a warp's successive units are at most four apart (the ring holds four or more).
+          constexpr int kNG = C::kSpu;  // k-groups per warp and turn
+          const int ui = kNG == 2 ? ((dw >> 2) & 1) : (dw >> 2);
+          const bool mine = kNG == 2 ? ((stage_no & 1u) == uint32_t(dw >> 3)) : true;
+          if (mine) {
+            if (ui * kNG < ng) {
+              const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
+              const int anb = quarter >> 1, fh = quarter & 1;
+              int slot;
+              uint32_t par;
+              unit_at(ui, slot, par);
+              const uint32_t ta =
+                  tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(C::kACol0 + slot * C::kUnitCols);
+              bool free_slot = true;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s2[i] = 0;
+              for (int e = 0; e < kNG; ++e) {
+                const int gi = ui * kNG + e;
+                const bool have = ok && gi < ng;  // a unit at the end of a segment may lack its second k-group
+                // raw words of the k-group: the lane's two lo words of this half for the four k16 slabs, the matching
+                // hi words, the four scales
+                uint2 lv[4];
+                uint32_t h0[4], h1[4];
+                uint32_t s2[8];
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-              lv[k4] = make_uint2(0, 0);
-              h0[k4] = h1[k4] = 0;
-            }
-            if (have) {
-              const int rslot = anb * kGroupsPerStage + gi;
-              const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes + lane * 16 + fh * 8;
-              const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
-              const uint2 sv = *reinterpret_cast<const uint2*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl + 8 * fh);
-              s2[0] = __byte_perm(sv.x, 0, 0x1010);
-              s2[1] = __byte_perm(sv.x, 0, 0x3232);
-              s2[2] = __byte_perm(sv.y, 0, 0x1010);
-              s2[3] = __byte_perm(sv.y, 0, 0x3232);
+                for (int i = 0; i < 8; ++i) s2[i] = 0;
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) {
-                lv[k4] = *reinterpret_cast<const uint2*>(lo_g + k4 * 512);
-                if constexpr (BITS == 5) {
-                  h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 128 + lane * 4) >> (8 * fh);
-                } else if constexpr (BITS == 6) {
-                  h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 256 + lane * 8 + fh * 4);
-                } else if constexpr (BITS == 8) {
-                  const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + k4 * 512 + lane * 16 + fh * 8);
-                  h0[k4] = hv.x;
-                  h1[k4] = hv.y;
+                for (int k4 = 0; k4 < 4; ++k4) {
+                  lv[k4] = make_uint2(0, 0);
+                  h0[k4] = h1[k4] = 0;
                 }
-              }
-            }
-            int slot;
-            uint32_t par;
-            unit_at(ui, slot, par);
-            const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
-            tc_fence_after();
-            const uint32_t ta = tmem_base + (uint32_t(32 * quarter) << 16) +
-                                uint32_t(C::kACol0 + slot * C::kUnitCols + (gi % C::kSpu) * 32);
-            // rows 0-15 of the quarter (pairs j' = 0, 1), then rows 16-31 (j' = 2, 3): each an mma A fragment per slab
-            {
-              uint32_t f[16];
+                if (have) {
+                  const int rslot = anb * kGroupsPerStage + gi;
+                  const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes + lane * 16 + fh * 8;
+                  const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
+                  const uint2 sv =
+                      *reinterpret_cast<const uint2*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl + 8 * fh);
+                  s2[0] = __byte_perm(sv.x, 0, 0x1010);
+                  s2[1] = __byte_perm(sv.x, 0, 0x3232);
+                  s2[2] = __byte_perm(sv.y, 0, 0x1010);
+                  s2[3] = __byte_perm(sv.y, 0, 0x3232);
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) {
-                const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
-                const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
-                decode_fragment<BITS, 0>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
-              }
-              if (have && free_slot) tmem_st_16x128b_x8(ta, f);
+                  for (int k4 = 0; k4 < 4; ++k4) {
+                    lv[k4] = *reinterpret_cast<const uint2*>(lo_g + k4 * 512);
+                    if constexpr (BITS == 5) {
+                      h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 128 + lane * 4) >> (8 * fh);
+                    } else if constexpr (BITS == 6) {
+                      h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 256 + lane * 8 + fh * 4);
+                    } else if constexpr (BITS == 8) {
+                      const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + k4 * 512 + lane * 16 + fh * 8);
+                      h0[k4] = hv.x;
+                      h1[k4] = hv.y;
+                    }
+                  }
+                }
+                if (e == 0) {
+                  free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+                  tc_fence_after();
+                }
+                // rows 0-15 of the quarter (pairs j' = 0, 1), then rows 16-31 (j' = 2, 3): an mma A fragment per slab
+                uint32_t f[16];
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) {
-                const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
-                const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
-                decode_fragment<BITS, 1>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
+                for (int k4 = 0; k4 < 4; ++k4) {
+                  const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
+                  const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
+                  decode_fragment<BITS, 0>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
+                }
+                if (have && free_slot) tmem_st_16x128b_x8(ta + uint32_t(e * 32), f);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                  const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
+                  const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
+                  decode_fragment<BITS, 1>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
+                }
+                if (have && free_slot) tmem_st_16x128b_x8(ta + (16u << 16) + uint32_t(e * 32), f);
               }
-              if (have && free_slot) tmem_st_16x128b_x8(ta + (16u << 16), f);
+              tmem_wait_st();
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&op_full[slot]);
             }
-            tmem_wait_st();
-            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&op_full[slot]);
+            if (lane == 0) mbar_arrive(&raw_empty[s]);
           }
         } else {
+          const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
           const int g0 = C::kSpu == 2 ? 2 * half : half;  // first of this warp's two k-groups of the stage
           constexpr int kGStep = C::kSpu == 2 ? 1 : 2;      // distance to its second one
           if (g0 < ng) {
@@ -589,12 +613,15 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
             }
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[s]);
+        if constexpr (!ATM) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[s]);
+        }
         if (++s == C::kStages) {
           s = 0;
           s_par ^= 1u;
         }
+        ++stage_no;
         unit_at((ng + C::kSpu - 1) / C::kSpu, u_slot, u_par);
       }
 
