@@ -262,9 +262,17 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  // An allocation of all 512 columns can only start at lane 0, column 0. The weights-in-TMEM variant relies on that:
+  // with the base a compile-time constant the MMA's operand addresses are computed in uniform registers, which the
+  // instruction reads directly (a base loaded from shared memory costs a register move per operand and MMA).
+  const uint32_t tmem_alloc_base = *tmem_slot;
+  const bool base_ok = !ATM || tmem_alloc_base == 0;
+  const uint32_t tmem_base = ATM ? 0u : tmem_alloc_base;
+  if (!base_ok && tid == 0) report_error(0x30A);
 
-  if (warp == 0) {
+  if (!base_ok) {
+    // nothing runs; the allocation is released below
+  } else if (warp == 0) {
     // ------------------------------ raw-plane producer ------------------------------
     // Lane 0 waits for the slot and posts the byte count; then each copy of the stage is issued by its own lane.
     const uint64_t pol_w = policy_evict_first();
@@ -758,7 +766,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    tmem_dealloc(tmem_alloc_base, C::kTmemCols);
   }
 }
 

@@ -79,12 +79,25 @@ class Workspace:
                                       self.counters.numel())
 
 
-def time_gemm(pkg, copies, ws, m, config, iters=20):
+def make_epilogue(pkg, kind, m, n):
+    """The epilogue descriptor of one of the step's three GEMM kinds plus the tensors it points to."""
+    if kind == "residual":  # out-projections and down: residual += C, bf16 copy, partial sums of squares per 128 columns
+        res = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+        xbf = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        part = torch.empty((m, n // 128), dtype=torch.float32, device="cuda")
+        return pkg.GemmEpilogue(pkg.EPI_RESIDUAL, None, 0, 0, pkg.ptr(res), pkg.ptr(xbf), pkg.ptr(part), None, 0, 1e-6), (res, xbf, part)
+    if kind == "swiglu":    # gate/up: silu(gate) * up on interleaved column pairs
+        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+        return pkg.GemmEpilogue(pkg.EPI_SWIGLU, pkg.ptr(out), n // 2, 0, None, None, None, None, 0, 1e-6), (out,)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    return pkg.GemmEpilogue(pkg.EPI_STORE_BF16, pkg.ptr(out), n, 0, None, None, None, None, 0, 1e-6), (out,)
+
+
+def time_gemm(pkg, copies, ws, m, config, iters=20, epilogue="store"):
     K = pkg.kernels()
     w0 = copies[0].desc
     a = torch.randn((m, w0.k), device="cuda").to(torch.bfloat16)
-    out = torch.empty((m, w0.n), dtype=torch.bfloat16, device="cuda")
-    ep = pkg.GemmEpilogue(pkg.EPI_STORE_BF16, pkg.ptr(out), w0.n, 0, None, None, None, None, 0, 1e-6)
+    ep, keep = make_epilogue(pkg, epilogue, m, w0.n)
     st = torch.cuda.Stream()
 
     def launch(i):
@@ -125,6 +138,8 @@ def main(argv=None):
     ap.add_argument("--single", default="", help="n,k,bits: launch only this shape, --launches times, untimed")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--peak-gbs", type=float, default=0.0, help="HBM peak to print fractions of (GB/s)")
+    ap.add_argument("--epilogue", default="store", choices=["store", "residual", "swiglu", "step"],
+                    help="epilogue kind; 'step' = the kind each shape has in the model's step")
     args = ap.parse_args(argv)
 
     if not torch.cuda.is_available():
@@ -156,11 +171,14 @@ def main(argv=None):
             continue
         one = sum(plane_bytes(n, k, bits))
         copies = [Planes(pkg, n, k, bits) for _ in range(max(2, -(-2 * L2_BYTES // one)))]
+        kind = args.epilogue
+        if kind == "step":
+            kind = {"mlp_gate_up": "swiglu", "mlp_down": "residual", "gdn_out": "residual", "attn_o": "residual"}.get(name, "store")
         for m in ms:
             cands = configs_for(pkg, bits) if args.sweep else [args.config]
             best = None
             for c in cands:
-                us = time_gemm(pkg, copies, ws, m, c)
+                us = time_gemm(pkg, copies, ws, m, c, epilogue=kind)
                 if best is None or us < best[1]:
                     best = (c, us)
             c, us = best
