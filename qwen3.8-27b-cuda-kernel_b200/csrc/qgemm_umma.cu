@@ -10,21 +10,30 @@
 // Two rings:
 //   raw ring      the BQ planes of 4 k-groups per stage (contiguous per 64-column block: 1-D bulk copies, L2
 //                 evict-first), as deep as shared memory allows next to the operand ring;
-//   operand ring  units of one or two decoded bf16 slices [128 n][64 k] in the K-major 128-byte-swizzled layout a
-//                 UMMA descriptor reads, each with its activation slices [TOK][64] bf16 (2-D tensor map, same
-//                 swizzle, rows >= M zero-filled). One mbarrier per unit collects the decode warps' arrivals and
-//                 the activation copies' bytes; one tcgen05.commit hands the unit back.
+//   operand ring  units of one or two decoded 64-wide k-groups, each with its activation slices [TOK][64] bf16
+//                 (2-D tensor map, 128-byte swizzle, rows >= M zero-filled). One mbarrier per unit collects the
+//                 decode warps' arrivals and the activation copies' bytes; one tcgen05.commit hands the unit back.
+// Where the decoded weights live distinguishes the two variants of the kernel (template flag ATM):
+//   ATM = true    (tmem_* configurations, up to 256 tokens per pass; the dispatcher's choice) in tensor memory: a
+//                 decode warp writes its registers with tcgen05.st.16x128b - whose register <-> (lane, column)
+//                 mapping is the A-fragment layout of mma.m16n8k16, i.e. the layout the BQ planes are packed for -
+//                 and the MMA takes A from TMEM ([128 lanes][8 columns of bf16 pairs] per k16 step). TMEM holds the
+//                 accumulator (TOK columns) and the ring (32 columns per k-group); shared memory only the raw
+//                 planes and the activations. No bf16 weight tile crosses shared memory;
+//   ATM = false   (umma_* configurations, up to 512 tokens) in shared memory as [128 n][64 k] slices in the K-major
+//                 128-byte-swizzled layout of a UMMA descriptor, written with 4-byte bank-conflict-free stores.
 // Warp roles:
 //   warp 0       raw producer (six copies per stage, one lane each);
-//   warp 1       stays converged; one elected lane issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32) per 16-wide
-//                k step with descriptors precomputed by addition, and tcgen05.commit per unit / per accumulator;
+//   warp 1       stays converged; one elected lane issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32), four per
+//                k-group in one block (ATM) or one per k16 step, and tcgen05.commit per unit / per accumulator;
 //   warp 2       activation producer - the first thread that touches data of earlier kernels (griddepcontrol.wait);
 //                everything before it (set-up, TMEM allocation, weight prefetch and decode) overlaps the previous
 //                kernel's tail;
 //   warp 3       idle (keeps the decode warps aligned to the TMEM lane quarters);
-//   warps 4-19   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> 4-byte
-//                bank-conflict-free stores into a slice, two slabs per barrier round trip. The same warps run
-//                the epilogue out of TMEM (tcgen05.ld).
+//   warps 4-19   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> operand ring.
+//                ATM: a warp owns the TMEM lane quarter its index selects (32 of the tile's 128 columns = half a
+//                64-column block, all k); with two-group units it takes a whole unit quarter every other stage.
+//                The same warps run the epilogue out of TMEM (tcgen05.ld).
 // Partial tiles go through the caller's workspace; the tile's last-arriving CTA sums them in CTA order, so
 // results are bit-reproducible. Every wait is bounded; TMEM is always released before the kernel ends.
 #include <algorithm>
