@@ -36,7 +36,7 @@ q38_gemm_tuning_lookup g_tuning = nullptr;
 int auto_config(int m, const q38_bq_weight& w, const q38_gemm_workspace* ws) {
   (void)ws;
   if (m <= 8) return 0;
-  if (m <= 16) return w.n / 128 <= num_sms() ? 8 : 1;  // fewer tiles than SMs: the tcgen05 kernel's finer cut wins
+  if (m <= 16) return 1;  // (with the Store epilogue tmem_t32 is level or ahead on the 40-tile matrices, with their Residual epilogue it is not)
   if (m <= 32) return 8;
   if (m <= 64) return 9;
   if (m <= 128) return 10;

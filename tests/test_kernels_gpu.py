@@ -153,7 +153,7 @@ def test_qgemm_27b_shapes(n, k, bits):
     deq = torch.empty((n, k), dtype=torch.bfloat16, device="cuda")
     pkg.check(K().q38_bq_dequant(C.byref(w.desc), pkg.ptr(deq), None))
     assert torch.equal(deq[cols].float().cpu(), torch.from_numpy(wd))
-    for m in (1, 8, 64):
+    for m in (1, 8, 64, 300):  # streaming kernel, tcgen05 kernel with the weights in TMEM, two 256-token blocks per launch
         a = tl.bf16_round(rng.standard_normal((m, k)))
         want = np.zeros((m, len(cols)), np.float32)
         tl.oracle().qgemm(a, wd, None, 3, out=want, ldo=len(cols))
