@@ -309,6 +309,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_token_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------
+#ifndef Q38_ATTN_MIN_PAGES_PER_SPLIT
+#define Q38_ATTN_MIN_PAGES_PER_SPLIT 8
+#endif
+constexpr int kMinPagesPerSplit = Q38_ATTN_MIN_PAGES_PER_SPLIT;  // 64-token pages
+
 // Decode attention over int8 KV on tensor cores: one CTA per (split, kv head, sequence), two CTAs per SM.
 //   * a producer lane walks the sequence's block-table row and brings one (page, kv head) per stage with four
 //     1-D bulk copies: K 16 KB, V 16 KB and their two 512-byte scale rows are each contiguous in the page;
@@ -376,7 +381,9 @@ __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
   const int slot = decode_rows ? seq_slot[row] : seq_slot[tok_seq[row]];
   const int L = (decode_rows ? seq_pos0[row] : tok_pos[row]) + 1;
   const int pages = (L + kPage - 1) / kPage;
-  const int pages_per_split = (pages + num_splits - 1) / num_splits;
+  // a split takes at least kMinPagesPerSplit pages: a short sequence of a ragged batch uses fewer of the launch's
+  // splits (the others leave at once) instead of paying a CTA's fixed cost for one or two pages
+  const int pages_per_split = max(kMinPagesPerSplit, (pages + num_splits - 1) / num_splits);
   const int p0 = min(pages, split * pages_per_split), p1 = min(pages, (split + 1) * pages_per_split);
   if (p0 >= p1 && num_splits > 1) {  // a split beyond this sequence's pages: an empty state for the merge, nothing else
     if (tid < group) {
