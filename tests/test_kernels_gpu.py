@@ -166,6 +166,27 @@ def test_qgemm_27b_shapes(n, k, bits):
     sync_ok()
 
 
+@pytest.mark.parametrize("bits", [4, 5, 8])
+def test_qgemm_operand_paths_give_the_same_bits(bits):
+    """The tcgen05 kernel hands the decoded weights to the MMA either through shared memory (umma_*) or through
+    tensor memory (tmem_*); the MMAs, their order over k and the epilogue are the same, so the outputs must be
+    bit-identical, cut over k (with a workspace) or not."""
+    names = {K().q38_qgemm_config_name(c).decode(): c for c in range(K().q38_qgemm_num_configs())}
+    rng = np.random.default_rng(bits)
+    ws = tl.Workspace()
+    p = tl.make_bq(2048, 1536, bits, seed=40 + bits, std=0.05, fast=True)
+    w = tl.DeviceBQ(p)
+    for m, pairs in ((20, [("umma_t32", "tmem_t32")]), (64, [("umma_t64", "tmem_t64")]), (100, [("umma_t128", "tmem_t128")]),
+                     (300, [("umma_t256", "tmem_t256"), ("umma_t256x2", "tmem_t256x2")])):
+        a_dev = tl.to_dev_bf16(tl.bf16_round(rng.standard_normal((m, 1536))))
+        for smem_cfg, tmem_cfg in pairs:
+            for use_ws in (True, False):
+                x = run_gemm_f32(a_dev, m, w, ws.desc if use_ws else None, names[smem_cfg])
+                y = run_gemm_f32(a_dev, m, w, ws.desc if use_ws else None, names[tmem_cfg])
+                assert torch.equal(x, y), (bits, m, smem_cfg, tmem_cfg, use_ws)
+    sync_ok()
+
+
 @pytest.mark.parametrize("bits", [4, 5, 6, 8])
 def test_quantiser_on_gpu_equals_cpu(bits):
     """The MSE-search quantiser (reference tools/bqpack.py:40-102) is plain tensor arithmetic: run on the GPU it must
