@@ -662,14 +662,22 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
 
       auto finish_chunk = [&](const float (&v)[16], int col0) {
         if (a.kind == Q38_EPI_RESIDUAL) {
+          // the old values are requested four at a time before the first new one of the four is stored: a load
+          // placed after a store to the same array has to wait for it, and the chunk took sixteen round trips to memory
+          constexpr int kRG = 4;
+          float rv[kRG];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
+            if ((j & (kRG - 1)) == 0) {
+#pragma unroll
+              for (int i = 0; i < kRG; ++i)
+                rv[i] = col0 + j + i < m_here ? __ldcg(a.residual + (size_t)(row0 + col0 + j + i) * a.n + n_glob) : 0.0f;
+            }
             const int col = col0 + j;
             float r = 0.0f;
             if (col < m_here) {
-              float* rp = a.residual + (size_t)(row0 + col) * a.n + n_glob;
-              r = *rp + v[j];
-              *rp = r;
+              r = rv[j & (kRG - 1)] + v[j];
+              a.residual[(size_t)(row0 + col) * a.n + n_glob] = r;
               a.xbf[(size_t)(row0 + col) * a.n + n_glob] = __float2bfloat16_rn(r);
             }
             const float ss = warp_sum(r * r);
