@@ -148,6 +148,77 @@ __global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __re
   }
 }
 
+// The same for prefill-sized steps: one CTA per (128-channel head block, 8 consecutive tokens), state not rolled here.
+// A thread requests its channel's eleven inputs of the window (rows m0 - 3 .. m0 + 7 of `proj`) and the tokens' sequence
+// data before it computes anything, so the CTA pays one round trip to memory instead of one per token; the taps a
+// sequence's first three tokens take from the conv state are fetched on demand. The arithmetic per token is that of
+// gdn_conv_kernel, in the same order.
+constexpr int kConvBlock = 8;
+__global__ void __launch_bounds__(128) gdn_conv_block_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
+                                                             const float* __restrict__ conv_w, float* __restrict__ qkv,
+                                                             int conv_dim, int key_dim, int layer, int num_layers,
+                                                             const __nv_bfloat16* __restrict__ conv_state,
+                                                             const int* __restrict__ seq_start,
+                                                             const int* __restrict__ seq_slot,
+                                                             const int* __restrict__ tok_seq, int num_tokens) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
+  __shared__ float red[kConvBlock][4];
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int m0 = blockIdx.y * kConvBlock;
+  const int nt = min(kConvBlock, num_tokens - m0);
+  const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)c * 4);
+  float win[kConvBlock + 3];  // inputs of rows m0 - 3 + k
+#pragma unroll
+  for (int k = 0; k < kConvBlock + 3; ++k) {
+    const int row = m0 - 3 + k;
+    win[k] = row >= 0 && row < num_tokens ? __bfloat162float(proj[(size_t)row * ld_proj + c]) : 0.0f;
+  }
+  int seq[kConvBlock], idx[kConvBlock];
+#pragma unroll
+  for (int t = 0; t < kConvBlock; ++t) seq[t] = t < nt ? tok_seq[m0 + t] : 0;
+#pragma unroll
+  for (int t = 0; t < kConvBlock; ++t) idx[t] = t < nt ? m0 + t - seq_start[seq[t]] : 3;  // index inside its sequence's chunk
+  float y[kConvBlock];
+#pragma unroll
+  for (int t = 0; t < kConvBlock; ++t) {
+    float x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = win[t + j];  // input 3 - j steps back
+    if (t < nt && idx[t] < 3) {  // the sequence's chunk starts here: older inputs come from its conv state
+      const __nv_bfloat16* st = conv_state + ((size_t)seq_slot[seq[t]] * num_layers + layer) * 3 * conv_dim;
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const int back = 3 - j;
+        if (back > idx[t]) x[j] = __bfloat162float(st[(size_t)(3 + idx[t] - back) * conv_dim + c]);
+      }
+    }
+    float acc = 0.0f;
+    acc += w.x * x[0];
+    acc += w.y * x[1];
+    acc += w.z * x[2];
+    acc += w.w * x[3];
+    y[t] = silu_f(acc);
+  }
+  if (c < 2 * key_dim) {  // block-uniform: the 128 channels of a CTA are one q or k head
+#pragma unroll
+    for (int t = 0; t < kConvBlock; ++t) {
+      const float ss = warp_sum(y[t] * y[t]);
+      if ((threadIdx.x & 31) == 0) red[t][threadIdx.x >> 5] = ss;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < kConvBlock; ++t) {
+      const float total = red[t][0] + red[t][1] + red[t][2] + red[t][3];
+      y[t] *= 1.0f / sqrtf(total + 1e-6f);
+      if (c < key_dim) y[t] *= 0.08838834764831845f;  // 1 / sqrt(128)
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kConvBlock; ++t)
+    if (t < nt) qkv[(size_t)(m0 + t) * conv_dim + c] = y[t];
+}
+
 __global__ void __launch_bounds__(128) gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ proj, int ld_proj,
                                                              int conv_dim, int layer, int num_layers,
                                                              __nv_bfloat16* __restrict__ conv_state,
@@ -889,11 +960,19 @@ extern "C" int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d,
   const int roll = batch->max_tokens_per_seq == 1 ? 1 : 0;
   // decode-sized steps: one token per CTA (latency); prefill-sized steps: eight, to keep the CTA count in the thousands
   const int per_cta = batch->num_tokens >= 256 ? 8 : 1;
-  (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, (batch->num_tokens + per_cta - 1) / per_cta),
-                      dim3(128), 0, s, proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128,
-                      p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot, batch->tok_seq, roll,
-                      batch->num_tokens, per_cta);
-  Q38_LAUNCH_OK("gdn_conv_kernel");
+  if (per_cta == kConvBlock && !roll) {
+    (void)launch_kernel(gdn_conv_block_kernel, dim3(d->conv_dim / 128, (batch->num_tokens + kConvBlock - 1) / kConvBlock),
+                        dim3(128), 0, s, proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128,
+                        p->gdn_layer, st->num_gdn_layers, static_cast<const __nv_bfloat16*>(cs), batch->seq_start,
+                        batch->seq_slot, batch->tok_seq, batch->num_tokens);
+    Q38_LAUNCH_OK("gdn_conv_block_kernel");
+  } else {
+    (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, (batch->num_tokens + per_cta - 1) / per_cta),
+                        dim3(128), 0, s, proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128,
+                        p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot, batch->tok_seq, roll,
+                        batch->num_tokens, per_cta);
+    Q38_LAUNCH_OK("gdn_conv_kernel");
+  }
   if (roll) return Q38_OK;
   (void)launch_kernel(gdn_conv_state_kernel, dim3(d->conv_dim / 128, batch->num_seqs), dim3(128), 0, s, 
       proj, d->ld_proj, d->conv_dim, p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot);
