@@ -105,6 +105,10 @@ typedef struct q38_gemm_workspace {
 int q38_qgemm_num_configs(void);
 const char* q38_qgemm_config_name(int config);
 int q38_qgemm_config_tile_m(int config);
+/* The configuration q38_qgemm picks for Q38_GEMM_CONFIG_AUTO: the installed tuning lookup's answer if it has one,
+ * else the built-in rule (pure host logic, no device access; no counterpart in the reference, whose launcher keeps
+ * the choice to itself - tools use it to report what "auto" meant). */
+int q38_qgemm_auto_config(int bits, int n, int k, int m);
 /* C[M][N] = A[M][K] * W^T; A bf16 row-major with leading dimension K. (kernels::qgemm, kernels.h:120-121) */
 int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep,
               const q38_gemm_workspace* ws, void* stream, int config);

@@ -107,6 +107,7 @@ KERNEL_API = {
     "q38_qgemm_num_configs": (C.c_int, []),
     "q38_qgemm_config_name": (C.c_char_p, [C.c_int]),
     "q38_qgemm_config_tile_m": (C.c_int, [C.c_int]),
+    "q38_qgemm_auto_config": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "q38_qgemm": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(BQWeight), C.POINTER(GemmEpilogue),
                             C.POINTER(GemmWorkspace), C.c_void_p, C.c_int]),
     "q38_qgemm_static": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(BQWeight), C.POINTER(GemmEpilogue), C.c_void_p]),

@@ -85,6 +85,17 @@ extern "C" int q38_qgemm_num_configs(void) { return kNumConfigs; }
 extern "C" const char* q38_qgemm_config_name(int c) { return c >= 0 && c < kNumConfigs ? kConfigs[c].name : "?"; }
 extern "C" int q38_qgemm_config_tile_m(int c) { return c >= 0 && c < kNumConfigs ? kConfigs[c].tile_m : 0; }
 extern "C" void q38_set_qgemm_tuning(q38_gemm_tuning_lookup lookup) { g_tuning = lookup; }
+extern "C" int q38_qgemm_auto_config(int bits, int n, int k, int m) {
+  if (g_tuning) {
+    const int t = g_tuning(bits, n, k, m);
+    if (t >= 0 && t < kNumConfigs) return t;
+  }
+  q38_bq_weight w{};
+  w.bits = bits;
+  w.n = n;
+  w.k = k;
+  return auto_config(m, w, nullptr);
+}
 
 extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const q38_gemm_epilogue* ep,
                          const q38_gemm_workspace* ws, void* stream, int config) {

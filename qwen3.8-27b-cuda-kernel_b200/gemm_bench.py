@@ -182,7 +182,7 @@ def main(argv=None):
                 if best is None or us < best[1]:
                     best = (c, us)
             c, us = best
-            cname = K.q38_qgemm_config_name(c).decode() if c >= 0 else "auto"
+            cname = K.q38_qgemm_config_name(c if c >= 0 else K.q38_qgemm_auto_config(bits, n, k, m)).decode()
             gbs = one / us / 1e3
             frac = f"  {100 * gbs / args.peak_gbs:5.1f}% of peak" if args.peak_gbs else ""
             print(f"{name:12s} bq{bits} n={n:6d} k={k:6d} m={m:4d} -> {cname:10s} {us:9.1f} us {gbs:7.0f} GB/s{frac}"

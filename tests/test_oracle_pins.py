@@ -184,6 +184,12 @@ def test_c_abi_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), name
     assert lib.q38_qgemm_num_configs() >= 4
+    # the dispatcher's rule: streaming kernel up to 16 tokens, then the tcgen05 kernel with the weights in TMEM at the
+    # smallest token operand that fits, two 256-token blocks per launch above 256
+    picks = {m: lib.q38_qgemm_config_name(lib.q38_qgemm_auto_config(4, 34816, 5120, m)).decode()
+             for m in (1, 8, 9, 16, 17, 64, 65, 128, 256, 257, 512)}
+    assert picks == {1: "stream_m8", 8: "stream_m8", 9: "stream_m16", 16: "stream_m16", 17: "tmem_t32", 64: "tmem_t64",
+                     65: "tmem_t128", 128: "tmem_t128", 256: "tmem_t256", 257: "tmem_t256x2", 512: "tmem_t256x2"}, picks
     assert lib.q38_kv_page_bytes(0, 4) == 135168
     # about sixteen (sequence, kv head, split) work items per SM, within [1, max_splits]
     assert lib.q38_attention_decode_splits(64, 4, 148, 64) == 10
