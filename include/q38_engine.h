@@ -48,6 +48,12 @@ typedef struct q38e_runner_options {
 } q38e_runner_options;
 void q38e_default_runner_options(q38e_runner_options* o);
 
+/* The decision the runner applies to the library's device error word after every step (the word is collected by the
+ * step's last kernel, see q38_device_error_collect): 0 for a clean word; -1, with the failure text in
+ * q38e_last_error(), for any other value. A failed step delivers no tokens: ModelRunner throws
+ * qwen38::DeviceStepError, the Engine ends the step's requests with finish reason "error". Needs no GPU. */
+int q38e_step_status(unsigned int device_error_word, const char* where);
+
 /* qwen38::DecodeRow (model_runner.h:46-52) */
 typedef struct q38e_decode_row {
   int slot;

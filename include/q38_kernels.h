@@ -267,6 +267,15 @@ const char* q38_last_error(void);           /* message of the last failed launch
  * graph captures) made after the call. No counterpart in the reference. */
 void q38_set_dependent_launch(int allowed);
 unsigned int q38_device_error(int clear);   /* non-zero if a bounded device-side wait ran out (synchronises) */
+/* The same status without a synchronisation, as one more node of the caller's stream or graph: a one-thread kernel
+ * moves the first non-zero error word of the library into *dst (device memory or mapped pinned host memory) and
+ * clears the library's words; *dst is not written when nothing failed. A host engine enqueues it at the end of each
+ * step and reads *dst after its stream synchronisation: a step whose pipeline aborted (the results of that launch
+ * are meaningless) can then be failed instead of delivered. The first call on a device looks the words up and
+ * should come before any stream capture. No counterpart in the reference (its kernels have no bounded waits). */
+int q38_device_error_collect(unsigned int* dst, void* stream);
+/* Test hook: sets one of the library's error words from the host, as if a kernel had reported `code`. */
+int q38_device_error_inject(unsigned int code);
 int q38_num_sms(void);                      /* SM count of the current device as cached by the library */
 
 #ifdef __cplusplus

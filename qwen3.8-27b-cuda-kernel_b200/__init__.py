@@ -138,6 +138,8 @@ KERNEL_API = {
     "q38_last_error": (C.c_char_p, []),
     "q38_set_dependent_launch": (None, [C.c_int]),
     "q38_device_error": (C.c_uint, [C.c_int]),
+    "q38_device_error_collect": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "q38_device_error_inject": (C.c_int, [C.c_uint]),
     "q38_num_sms": (C.c_int, []),
 }
 

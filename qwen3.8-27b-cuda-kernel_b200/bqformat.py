@@ -165,10 +165,42 @@ def _nibbles_of(words: np.ndarray) -> np.ndarray:
     return np.stack([e0, e1], axis=-1).reshape(words.shape[0], 32, 16, 2)
 
 
+def _pack_on_device(codes: torch.Tensor, scales: torch.Tensor, bits: int) -> Packed:
+    """pack() as tensor arithmetic on the device the codes live on (same bytes; a 27B-sized matrix packs in well
+    under a second on a GPU where the numpy path needs half a minute)."""
+    n, k = codes.shape
+    dev = codes.device
+    nb, kb = n // 64, k // 16
+    u = codes.to(torch.int64) + (1 << (bits - 1))
+    #  n = 64 nb + 8 j + g ; k = 16 kb + 8 h + 2 t + e  ->  [slab, lane (g t), pair (j h), e]
+    lanes = u.reshape(nb, 8, 8, kb, 2, 4, 2).permute(0, 3, 2, 5, 1, 4, 6).reshape(nb * kb, 32, 16, 2)
+
+    def words(v, shifts):  # v [..., P, 2], shifts [P]: sum_p (v0 << s_p) | (v1 << (s_p + 16)) as little-endian u32 bytes
+        w = ((v[..., 0] << shifts) | (v[..., 1] << (shifts + 16))).sum(dim=-1)
+        return (w & 0xFFFFFFFF).to(torch.int32).contiguous().cpu().numpy().astype("<u4").tobytes()
+
+    ar = lambda cnt, step: step * torch.arange(cnt, dtype=torch.int64, device=dev)
+    lo = words((lanes & 15).reshape(-1, 32, 4, 4, 2), ar(4, 4))
+    top = lanes >> 4
+    if bits == 4:
+        hi = b""
+    elif bits == 5:
+        hi = words(top, ar(16, 1))
+    elif bits == 6:
+        hi = words(top.reshape(-1, 32, 2, 8, 2), ar(8, 2))
+    else:
+        hi = words(top.reshape(-1, 32, 4, 4, 2), ar(4, 4))
+    s16 = scales.to(torch.float32).to(torch.bfloat16).view(torch.int16)
+    s16 = s16.reshape(nb, 8, 8, k // GROUP).permute(0, 3, 2, 1).contiguous().cpu().numpy()
+    return Packed(bits, n, k, lo, hi, s16.astype("<i2").tobytes())
+
+
 def pack(codes: torch.Tensor, scales: torch.Tensor, bits: int) -> Packed:
     assert bits in BITS
     n, k = codes.shape
     assert n % 128 == 0 and k % GROUP == 0, (n, k)
+    if codes.is_cuda:
+        return _pack_on_device(codes, scales, bits)
     u = (codes.to(torch.int32).cpu().numpy() + (1 << (bits - 1))).astype(np.uint32)
     assert int(u.max()) < (1 << bits)
     lanes = _to_lanes(u)

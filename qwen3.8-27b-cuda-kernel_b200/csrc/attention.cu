@@ -668,6 +668,7 @@ int check_attention(const q38_attention_params* p, const q38_batch_desc* b, cons
 }  // namespace
 
 unsigned int attention_error(bool clear) { return read_tu_error(clear); }
+unsigned int* attention_error_address() { return tu_error_address(); }
 
 }  // namespace q38
 

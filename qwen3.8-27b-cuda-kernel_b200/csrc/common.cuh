@@ -32,6 +32,12 @@ static inline unsigned int read_tu_error(bool clear) {
   return v;
 }
 
+// Device address of this translation unit's error word (host code cannot use the symbol's name as an address).
+static inline unsigned int* tu_error_address() {
+  void* p = nullptr;
+  return cudaGetSymbolAddress(&p, g_tu_error) == cudaSuccess ? static_cast<unsigned int*>(p) : nullptr;
+}
+
 // Programmatic dependent launch: let the next kernel of the stream be scheduled / wait until everything the
 // previous kernels of the stream wrote is visible. Both are no-ops for a kernel launched without the attribute.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -928,6 +928,7 @@ __global__ void __launch_bounds__(kDv) gdn_norm_gate_kernel(const float* __restr
 }  // namespace
 
 unsigned int gdn_error(bool clear) { return read_tu_error(clear); }
+unsigned int* gdn_error_address() { return tu_error_address(); }
 
 }  // namespace q38
 

@@ -371,6 +371,7 @@ __global__ void __launch_bounds__(256) target_logprob_kernel(const float* __rest
 }  // namespace
 
 unsigned int misc_error(bool clear) { return read_tu_error(clear); }
+unsigned int* misc_error_address() { return tu_error_address(); }
 
 }  // namespace q38
 

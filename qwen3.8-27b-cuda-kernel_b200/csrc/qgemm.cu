@@ -1,6 +1,7 @@
 // GEMM dispatcher: argument validation, tile-configuration choice (tuning hook or M heuristic) and the
 // BQ dequantisation dump. Replaces the host part of the reference's src/kernels/qgemm.cu:470-616.
 #include <algorithm>
+#include <mutex>
 
 #include "bq_dequant.cuh"
 #include "common.cuh"
@@ -184,28 +185,33 @@ static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
 static __device__ __align__(256) int g_static_counters[kStaticCounters];
 
 struct StaticWs {
+  std::once_flag once;      // the lookup runs once per device, also with several host threads calling
   float* partials = nullptr;
   int* counters = nullptr;
+  int sms = 0;              // SM count of this device (the cached count of the library is the first device's)
+  cudaError_t status = cudaSuccess;
 };
 constexpr int kMaxDevices = 64;
 StaticWs g_static_ws[kMaxDevices];
 
 // The array names above are host-side stand-ins; the device addresses come from cudaGetSymbolAddress, looked up
 // once per device with that device current.
-int static_ws_for_current_device(StaticWs* out) {
+int static_ws_for_current_device(const StaticWs** out) {
   int dev = 0;
   Q38_CUDA_OK(cudaGetDevice(&dev));
   Q38_REQUIRE(dev >= 0 && dev < kMaxDevices, "qgemm_static: device index %d out of range", dev);
   StaticWs& ws = g_static_ws[dev];
-  if (ws.partials == nullptr) {
-    float* p = nullptr;
-    int* c = nullptr;
-    Q38_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials));
-    Q38_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&c), g_static_counters));
-    ws.counters = c;
-    ws.partials = p;
-  }
-  *out = ws;
+  std::call_once(ws.once, [&ws, dev] {
+    void* p = nullptr;
+    void* c = nullptr;
+    ws.status = cudaGetSymbolAddress(&p, g_static_partials);
+    if (ws.status == cudaSuccess) ws.status = cudaGetSymbolAddress(&c, g_static_counters);
+    if (ws.status == cudaSuccess) ws.status = cudaDeviceGetAttribute(&ws.sms, cudaDevAttrMultiProcessorCount, dev);
+    ws.partials = static_cast<float*>(p);
+    ws.counters = static_cast<int*>(c);
+  });
+  Q38_CUDA_OK(ws.status);
+  *out = &ws;
   return Q38_OK;
 }
 }  // namespace
@@ -217,15 +223,16 @@ extern "C" int q38_qgemm_static(const q38_bf16* a, int m, const q38_bq_weight* w
               kStaticM);
   Q38_REQUIRE(w->n > 0 && w->n / 128 <= kStaticCounters, "qgemm_static: n = %d exceeds the built-in workspace (%d columns)",
               w->n, 128 * kStaticCounters);
-  Q38_REQUIRE(num_sms() <= kStaticCtas, "qgemm_static: %d SMs exceed the built-in workspace (%d)", num_sms(), kStaticCtas);
-  StaticWs sws;
+  const StaticWs* sws = nullptr;
   const int rc = static_ws_for_current_device(&sws);
   if (rc != Q38_OK) return rc;
-  Q38_CUDA_OK(cudaMemsetAsync(sws.counters, 0, sizeof(int) * kStaticCounters, as_stream(stream)));
-  const q38_gemm_workspace ws{sws.partials, kStaticPartialFloats, sws.counters, kStaticCounters};
+  Q38_REQUIRE(sws->sms <= kStaticCtas, "qgemm_static: %d SMs exceed the built-in workspace (%d)", sws->sms, kStaticCtas);
+  Q38_CUDA_OK(cudaMemsetAsync(sws->counters, 0, sizeof(int) * kStaticCounters, as_stream(stream)));
+  const q38_gemm_workspace ws{sws->partials, kStaticPartialFloats, sws->counters, kStaticCounters};
   return q38_qgemm(a, m, w, ep, &ws, stream, Q38_GEMM_CONFIG_AUTO);
 }
 
 namespace q38 {
 unsigned int qgemm_dispatch_error(bool clear) { return read_tu_error(clear); }
+unsigned int* qgemm_dispatch_error_address() { return tu_error_address(); }
 }

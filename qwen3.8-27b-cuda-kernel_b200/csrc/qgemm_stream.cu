@@ -453,5 +453,6 @@ int qgemm_stream_launch(int mt, const __nv_bfloat16* a, int m, const q38_bq_weig
 }
 
 unsigned int qgemm_stream_error(bool clear) { return read_tu_error(clear); }
+unsigned int* qgemm_stream_error_address() { return tu_error_address(); }
 
 }  // namespace q38

@@ -919,5 +919,6 @@ int qgemm_umma_launch(int tok, int mblocks, bool a_in_tmem, const __nv_bfloat16*
 }
 
 unsigned int qgemm_umma_error(bool clear) { return read_tu_error(clear); }
+unsigned int* qgemm_umma_error_address() { return tu_error_address(); }
 
 }  // namespace q38

@@ -272,4 +272,9 @@ inline void pack_ragged(const int* seq_count, const int* seq_pos0, int num_seqs,
   detail::ok(q38_pack_ragged(seq_count, seq_pos0, num_seqs, num_tokens, seq_start, tok_pos, tok_seq, stream));
 }
 
+// Extension: the library's device error status as a node of the step (see q38_device_error_collect).
+inline void collect_device_errors(unsigned int* dst, cudaStream_t stream) {
+  detail::ok(q38_device_error_collect(dst, stream));
+}
+
 }  // namespace qwen38::kernels

@@ -41,6 +41,21 @@ class Error : public std::runtime_error {
   using std::runtime_error::runtime_error;
 };
 
+// A step whose kernels reported a pipeline abort (a bounded device-side wait ran out, a page id outside the pool, a
+// tensor-memory allocation at an unexpected base): the step's outputs are meaningless and were not delivered. The
+// CUDA context is intact; later steps can run. Extension: the reference's kernels have no such status.
+class DeviceStepError : public Error {
+ public:
+  DeviceStepError(unsigned int code, const std::string& where);
+  unsigned int code() const { return code_; }
+
+ private:
+  unsigned int code_ = 0;
+};
+// Message of a step failure for error word `code` ("" when code == 0): the pure decision the runner applies after
+// every step, callable without a GPU.
+std::string device_step_failure(unsigned int code, const std::string& where);
+
 [[noreturn]] void fail(const std::string& message);
 std::string format_check_failure(const char* expr, const char* file, int line, const std::string& msg);
 

@@ -84,6 +84,12 @@ void q38e_default_runner_options(q38e_runner_options* o) {
   o->verbose = d.verbose;
 }
 
+int q38e_step_status(unsigned int device_error_word, const char* where) {
+  return guard([&] {
+    if (device_error_word != 0) throw DeviceStepError(device_error_word, where ? where : "step");
+  });
+}
+
 int q38e_tuning_load(const char* path) {
   return guard([&] {
     if (path == nullptr || path[0] == '\0') install_tuning({});

@@ -157,10 +157,19 @@ bool Engine::step() {
     }
     if (!rows.empty()) {
       const double t = now();
-      const StepResult res = runner_->prefill_batch(rows);
+      StepResult res;
+      bool step_ok = true;
+      try {
+        res = runner_->prefill_batch(rows);
+      } catch (const DeviceStepError& e) {
+        // the step's kernels gave up: nothing of it is delivered; its sequences end with an error result, the
+        // engine and the other sequences carry on
+        step_ok = false;
+        for (Sequence* s : owners) finish(*s, FinishReason::Error, e.what());
+      }
       stats_.prefill_s += now() - t;
       size_t sampled = 0;
-      for (size_t i = 0; i < rows.size(); ++i) {
+      for (size_t i = 0; step_ok && i < rows.size(); ++i) {
         Sequence& s = *owners[i];
         const int n = int(rows[i].tokens.size());
         stats_.prefill_tokens += n;
@@ -192,13 +201,22 @@ bool Engine::step() {
   }
   if (!rows.empty()) {
     const double t = now();
-    const StepResult res = runner_->decode(rows);
+    StepResult res;
+    bool step_ok = true;
+    try {
+      res = runner_->decode(rows);
+    } catch (const DeviceStepError& e) {
+      step_ok = false;
+      for (Sequence* s : owners) finish(*s, FinishReason::Error, e.what());
+    }
     stats_.decode_s += now() - t;
-    stats_.decode_tokens += int64_t(rows.size());
-    ++stats_.decode_steps;
-    for (size_t i = 0; i < owners.size(); ++i) {
-      owners[i]->position += 1;  // the consumed token now sits in the cache
-      deliver(*owners[i], res.tokens[i], res.logprobs[i]);
+    if (step_ok) {
+      stats_.decode_tokens += int64_t(rows.size());
+      ++stats_.decode_steps;
+      for (size_t i = 0; i < owners.size(); ++i) {
+        owners[i]->position += 1;  // the consumed token now sits in the cache
+        deliver(*owners[i], res.tokens[i], res.logprobs[i]);
+      }
     }
     drop_finished();
   }

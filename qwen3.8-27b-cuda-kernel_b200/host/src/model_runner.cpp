@@ -69,6 +69,17 @@ const kernels::SamplingParamsDev kGreedy{0.0f, 0, 1.0f, 0.0f, 0.0f, 1.0f, 0};
 
 }  // namespace
 
+std::string device_step_failure(unsigned int code, const std::string& where) {
+  if (code == 0) return {};
+  std::ostringstream os;
+  os << where << ": a kernel of the step reported pipeline abort 0x" << std::hex << code
+     << " (a bounded device-side wait ran out or an index left its pool); the step's results were discarded";
+  return os.str();
+}
+
+DeviceStepError::DeviceStepError(unsigned int code, const std::string& where)
+    : Error(device_step_failure(code, where)), code_(code) {}
+
 std::string MemoryPlan::describe() const {
   std::ostringstream os;
   os << "device memory free at start " << mib(free_at_start) << ": weights " << mib(weights) << ", workspace "
@@ -122,6 +133,10 @@ struct ModelRunner::Impl {
   MetaMap meta;
   uint8_t* meta_dev = nullptr;
   PinnedBuffer meta_host, out_host;
+  // The library's device error status of the current step: one word of mapped pinned memory that the last kernel of
+  // every step writes when some kernel of the step aborted its pipeline; read on the host after the step's sync.
+  PinnedBuffer status_host;
+  unsigned int* status_dev = nullptr;
   struct BucketGraphs {
     Graph step, core;
   };
@@ -178,6 +193,15 @@ struct ModelRunner::Impl {
     kernels::pack_ragged(dmeta<int>(meta.seq_count), dmeta<int>(meta.seq_pos0), seqs, tokens, dmeta<int>(meta.seq_start),
                          dmeta<int>(meta.tok_pos), dmeta<int>(meta.tok_seq), stream.get());
   }
+  void collect_status() { kernels::collect_device_errors(status_dev, stream.get()); }
+  // After the step's stream synchronisation: throws if a kernel of the step gave up, and re-arms the word.
+  void check_status(const char* where) {
+    volatile unsigned int* word = status_host.as<volatile unsigned int>();
+    const unsigned int code = *word;
+    if (code == 0) return;
+    *word = 0;
+    throw DeviceStepError(code, where);
+  }
   void forward(int m, const kernels::BatchDesc& batch, bool decode);
   void lm_head(const __nv_bfloat16* x, const float* part, int rows);
   void run_sampler(int rows);
@@ -210,6 +234,7 @@ struct ModelRunner::Impl {
     forward(bucket, batch, true);
     lm_head(xbf, partials, bucket);
     run_sampler(bucket);
+    collect_status();
   }
   void single_chunk_meta(int slot, int pos0, std::span<const int32_t> tokens, const SamplingParams* sample, int step);
 };
@@ -305,6 +330,12 @@ void ModelRunner::Impl::setup() {
   meta_host = PinnedBuffer(meta.host_bytes, false);
   std::memset(meta_host.get(), 0, meta.host_bytes);
   out_host = PinnedBuffer(R * 8, false);
+  status_host = PinnedBuffer(64, true);
+  std::memset(status_host.get(), 0, 64);
+  status_dev = static_cast<unsigned int*>(status_host.device_ptr());
+  collect_status();  // looks the library's error words up once, outside any capture
+  stream.sync();
+  *status_host.as<volatile unsigned int>() = 0;  // whatever an earlier user of the library left behind is not ours
   graphs_enabled = opt.cuda_graphs;
   if (opt.verbose) std::cerr << "qwen38: " << plan.describe() << "\n";
 }
@@ -560,11 +591,13 @@ StepResult ModelRunner::prefill_batch(std::span<const PrefillRow> rows) {
     }
     I.run_sampler(samples);
   }
+  I.collect_status();
   I.t_end.record(s);
   I.timed = true;
   if (samples > 0) I.download(samples);
   I.stream.sync();
   I.collect_marks();
+  I.check_status("prefill step");
   if (samples > 0) result = I.results(samples);
   return result;
 }
@@ -630,6 +663,7 @@ StepResult ModelRunner::decode(std::span<const DecodeRow> rows) {
   I.timed = true;
   I.stream.sync();
   I.collect_marks();
+  I.check_status("decode step");
   StepResult r = I.results(bucket);
   r.tokens.resize(size_t(n));
   r.logprobs.resize(size_t(n));
@@ -661,8 +695,10 @@ std::vector<float> ModelRunner::score(int slot, int pos0, std::span<const int32_
     }
     std::vector<float> chunk(static_cast<size_t>(n));
     QWEN38_CUDA(cudaMemcpyAsync(chunk.data(), I.logprob_rows, size_t(n) * 4, cudaMemcpyDeviceToHost, s));
+    I.collect_status();
     I.stream.sync();
     I.collect_marks();
+    I.check_status("score step");
     out.insert(out.end(), chunk.begin(), chunk.end());
     pos += n;
   }
@@ -686,9 +722,11 @@ std::vector<float> ModelRunner::prefill_logits(int slot, int pos0, std::span<con
     const int rows = std::min(I.max_rows, n - r0);
     I.lm_head(I.xbf + size_t(r0) * H, I.partials + size_t(r0) * nb, rows);
     QWEN38_CUDA(cudaMemcpyAsync(out.data() + size_t(r0) * V, I.logits, size_t(rows) * V * 4, cudaMemcpyDeviceToHost, s));
+    I.collect_status();
     I.stream.sync();
   }
   I.collect_marks();
+  I.check_status("prefill step");
   return out;
 }
 

@@ -3,6 +3,8 @@ reference's own CPU model (`qwen38-ref`, engine mode, int8 KV) produced for the 
 against the whole-model oracle. Mirrors reference tests/gpu/test_e2e.cpp and adds ragged multi-sequence steps,
 page-id checks and error paths."""
 
+import warnings
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 import numpy as np
@@ -43,15 +45,23 @@ def top1_agreement(got, want, tol=2e-2):
     return int(same.sum()), len(same), int((same & decisive).sum()), int(decisive.sum())
 
 
-def check_agreement(tag, counts):
-    agree, total, dagree, dtotal = counts
-    print(f"top-1 {agree}/{total}, decisive rows {dagree}/{dtotal}")
-    assert dagree == dtotal, "a clearly separated argmax differs from the reference"
-    # Raw agreement counts the near-ties too (a third of the rows of these 1024-word random models are not
-    # decisive), so it moves by a row or two with any change of summation order: the O(1)-activation model is held
-    # to 98 % of its rows, the N(0, 0.02) model (all logits within +-2) to the reference's own end-to-end bar of
-    # 95 % (reference tests/gpu/test_e2e.cpp:86).
-    assert agree >= (0.98 if tag == "_unit" else 0.95) * total
+def check_agreement(tag, counts, record=None, bar=None):
+    """Asserts 100 % agreement on decisive rows and `bar` on all rows; the raw counts go into the test report
+    (a user property and a warning line, so that a passing run records them too)."""
+    agree, total, dagree, dtotal = (int(x) for x in counts)
+    line = f"top-1{tag or '_n002'}: {agree}/{total} rows ({agree / max(1, total):.4f}), decisive rows {dagree}/{dtotal}"
+    print(line)
+    if record is not None:
+        record("top1" + (tag or "_n002"), line)
+    warnings.warn(line)
+    assert dagree == dtotal, "a clearly separated argmax differs from the reference: " + line
+    # The O(1)-activation model is held to the 99 % greedy agreement the engine is specified to reach. The N(0, 0.02)
+    # model's 1024 logits all lie within +-2 and a third of its rows are near-ties (top-2 margin below twice the allowed
+    # logit error), which no summation order reproduces: it is held to the reference's own end-to-end bar of 95 %
+    # (reference tests/gpu/test_e2e.cpp:86) and its raw figure is reported.
+    if bar is None:
+        bar = 0.99 if tag == "_unit" else 0.95
+    assert agree >= bar * total, line
 
 
 def prefill_all(runner, slot, tokens, chunk):
@@ -64,7 +74,7 @@ def prefill_all(runner, slot, tokens, chunk):
 
 @pytest.mark.parametrize("tag", ["", "_unit"])
 @pytest.mark.parametrize("chunk", [64, 128])
-def test_prefill_logits_match_reference_model(gold, tag, chunk):
+def test_prefill_logits_match_reference_model(gold, tag, chunk, record_property):
     model = eng.Model(GOLD / f"tiny_cfg1{tag}.q38")
     runner = eng.Runner(model, tiny_options(prefill_chunk=chunk))
     counts = np.zeros(4, dtype=int)
@@ -78,13 +88,13 @@ def test_prefill_logits_match_reference_model(gold, tag, chunk):
         counts += top1_agreement(got, want)
     print(f"prefill{tag} chunk {chunk}: rel_max {worst:.3e}")
     assert worst <= 2e-2
-    check_agreement(tag, counts)
+    check_agreement(tag, counts, record_property)  # every prefill position of the four prompts + continuations: 404 rows
     runner.close()
     model.close()
 
 
 @pytest.mark.parametrize("tag", ["", "_unit"])
-def test_ragged_batch_decode_matches_reference_step_by_step(gold, tag):
+def test_ragged_batch_decode_matches_reference_step_by_step(gold, tag, record_property):
     """Config 1: the four prompts prefilled (one ragged step per chunk round), then 32 greedy decode steps as
     one ragged batch with teacher forcing on the reference's tokens; logits compared at every step."""
     model = eng.Model(GOLD / f"tiny_cfg1{tag}.q38")
@@ -116,7 +126,9 @@ def test_ragged_batch_decode_matches_reference_step_by_step(gold, tag):
             assert int(toks[s]) == int(logits[s].argmax()), "greedy token = lowest-id argmax of the logits"
     print(f"decode{tag}: rel_max {worst:.3e}; first sampled tokens {first} vs reference {[int(g[0]) for g in gens]}")
     assert worst <= 2e-2
-    check_agreement(tag, counts)
+    # 128 rows: one flipped near-tie is 0.8 %, so this small sample is held to two rows; the 404-row prefill test
+    # above carries the 99 % bar
+    check_agreement(tag, counts, record_property, bar=(126 / 128 if tag == "_unit" else 0.95))
     runner.close()
     model.close()
 
@@ -307,4 +319,130 @@ def test_sampled_generation_is_reproducible_and_scores_match_logits():
     want = logits[np.arange(50), targets] - np.log(np.exp(logits - logits.max(-1, keepdims=True)).sum(-1)) - logits.max(-1)
     assert np.allclose(lp, want, atol=2e-4)
     runner.close()
+    model.close()
+
+
+# ---------------------------------------------------------------------------------------------------
+# the benchmarked geometry end to end
+# ---------------------------------------------------------------------------------------------------
+def test_27b_geometry_truncated_model_matches_oracle(tmp_path_factory, record_property):
+    """The 27B model's geometry (hidden 5120, 24 q / 4 kv heads, GDN 16 key / 48 value heads, MLP 17408) cut to its
+    first four layers [GDN, GDN, GDN, attention] with a 1024-row vocabulary (the reference's CPU model refuses more
+    than 3e9 parameters, reference src/ref/ref_model.cpp:21-58), N(0, 0.02) weights, default recipe through the real
+    quantiser. 36 sequences: ragged prefill in steps of at most 512 tokens, then 16 decode steps as one batch of 36
+    (the tcgen05 kernel with the weights in tensor memory, 64-token configuration, and its Residual / SwiGLU
+    epilogues), greedy with the engine's own tokens fed back. The oracle model runs every sequence on its own host
+    thread with the same tokens; logits are compared at every sampled position."""
+    from q38b200 import synth
+    import torch
+
+    cfg = synth.model_config(hidden=5120, vocab=1024, layers=4, intermediate=17408, nq=24, nkv=4, lk=16, lv=48)
+    path = tmp_path_factory.mktemp("q38") / "geom27b_4layers.q38"
+    synth.write_q38(path, cfg, synth.random_checkpoint(cfg, seed=27, init="n002"), recipe="default", device="cuda")
+    torch.cuda.empty_cache()
+    B, STEPS = 36, 16
+    rng = np.random.default_rng(11)
+    lens = [int(x) for x in rng.integers(2, 9, size=B)]
+    lens[0], lens[1] = 70, 130  # two prompts that cross KV pages and GDN chunks
+    prompts = [rng.integers(0, 1000, size=n).astype(np.int32) for n in lens]
+
+    model = eng.Model(path)
+    runner = eng.Runner(model, eng.default_runner_options(max_batch=64, prefill_chunk=512, kv_dtype=0, kv_tokens=64 * 256,
+                                                          max_context=1024, verbose=0))
+    g = eng.greedy()
+    got = [[] for _ in range(B)]       # logits rows per sequence, in sampling order
+    fed = [list(p) for p in prompts]   # tokens each sequence has consumed
+    for s in range(B):
+        runner.reset_slot(s)
+        assert runner.kv_ensure(s, lens[s] + STEPS + 1)
+    # ragged prefill: whole prompts packed into steps of at most 512 tokens
+    nxt = [0] * B
+    rows, used = [], 0
+    order = []
+    def flush():
+        nonlocal rows, used
+        if not rows:
+            return
+        toks, _ = runner.prefill(rows)
+        logits = runner.last_logits(len(rows))
+        for i, (slot, *_rest) in enumerate(rows):
+            got[slot].append(logits[i].copy())
+            nxt[slot] = int(toks[i])
+        rows, used = [], 0
+    for s in range(B):
+        if used + lens[s] > 512:
+            flush()
+        rows.append((s, 0, prompts[s], g, 0))
+        used += lens[s]
+    flush()
+    for step in range(STEPS):
+        drows = [(s, lens[s] + step, nxt[s], g, step + 1) for s in range(B)]
+        for s in range(B):
+            fed[s].append(nxt[s])
+        toks, _ = runner.decode(drows)
+        logits = runner.last_logits(B)
+        for s in range(B):
+            got[s].append(logits[s].copy())
+            nxt[s] = int(toks[s])
+    runner.close()
+    model.close()
+
+    om = OracleModel(path, kv_dtype=2, max_positions=160)
+
+    def reference_rows(s):
+        seq = om.new_sequence()
+        out = [om.forward(seq, fed[s][:lens[s]])[0]]
+        for t in fed[s][lens[s]:lens[s] + STEPS]:
+            out.append(om.forward(seq, [t])[0])
+        return out
+
+    with ThreadPoolExecutor(max_workers=16) as pool:
+        want = list(pool.map(reference_rows, range(B)))
+    worst, counts = 0.0, np.zeros(4, dtype=int)
+    for s in range(B):
+        assert len(got[s]) == STEPS + 1 and len(want[s]) == STEPS + 1
+        for a, b in zip(got[s], want[s]):
+            worst = max(worst, rel_max(a, b))
+            counts += top1_agreement(a, b)
+    record_property("rel_max_27b_geometry", worst)
+    warnings.warn(f"27B geometry, 4 layers, batch {B}: max rel logit error {worst:.3e}")
+    assert worst <= 2e-2
+    check_agreement("_geom27b", counts, record_property, bar=0.95)
+
+
+def test_a_device_error_word_fails_the_step_and_the_engine_carries_on():
+    """Every kernel reports a pipeline abort (a bounded wait that ran out, a page id outside the pool) through the
+    library's device error word. The failure is made on the host here: the word is set with the library's test hook,
+    no kernel misbehaves. The next step must raise instead of returning tokens, the word must be re-armed, and the
+    Engine must end that step's requests with an error result and serve the next request normally."""
+    K = tl.pkg.kernels()
+    model = eng.Model(GOLD / "tiny_cfg1_unit.q38")
+    runner = eng.Runner(model, tiny_options())
+    g = eng.greedy()
+    tokens = np.random.default_rng(5).integers(0, 1000, size=20).astype(np.int32)
+    runner.reset_slot(0)
+    assert runner.kv_ensure(0, 64)
+    toks, _ = runner.prefill([(0, 0, tokens, g, 0)])
+    good, _ = runner.decode([(0, 20, int(toks[0]), g, 1)])
+    tl.pkg.check(K.q38_device_error_inject(0x303))
+    with pytest.raises(eng.EngineError, match="0x303"):
+        runner.decode([(0, 21, int(good[0]), g, 2)])
+    again, _ = runner.decode([(0, 21, int(good[0]), g, 2)])  # same step once more: clean
+    assert again.shape == (1,)
+    tl.pkg.check(K.q38_device_error_inject(0x212))
+    with pytest.raises(eng.EngineError, match="prefill step"):
+        runner.prefill([(0, 22, tokens[:5], g, 3)])
+    assert K.q38_device_error(1) == 0, "the collected word is cleared in the library"
+    runner.close()
+
+    e = eng.Engine(model, tiny_options())
+    first = e.submit(tokens, g, max_new_tokens=8, ignore_eos=True)
+    tl.pkg.check(K.q38_device_error_inject(0x305))
+    e.run()
+    second = e.submit(tokens, g, max_new_tokens=8, ignore_eos=True)
+    e.run()
+    done = {r.id: r for r in e.take_finished()}
+    assert done[first].finish == "error" and "0x305" in done[first].error
+    assert done[second].finish == "length" and len(done[second].tokens) == 8
+    e.close()
     model.close()

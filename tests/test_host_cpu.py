@@ -75,3 +75,27 @@ def test_tuning_table_round_trip(tmp_path):
     (tmp_path / "bad.json").write_text("{not json")
     with pytest.raises(eng.EngineError, match="malformed tuning table"):
         eng.load_tuning(tmp_path / "bad.json")
+
+
+def test_step_status_turns_a_device_error_word_into_a_failed_step():
+    """The runner reads the library's device error word after every step's synchronisation. A clean word lets the
+    step through; any other value fails it with a message that names the step and the word (no GPU involved: this is
+    the host-side decision alone)."""
+    lib = eng.lib()
+    assert lib.q38e_step_status(0, b"decode step") == 0
+    assert lib.q38e_step_status(0x303, b"decode step") == -1
+    msg = lib.q38e_last_error().decode()
+    assert "decode step" in msg and "0x303" in msg and "discarded" in msg
+    assert lib.q38e_step_status(0x212, b"prefill step") == -1
+    assert "prefill step" in lib.q38e_last_error().decode()
+
+
+@pytest.mark.parametrize("bits", [4, 5, 6, 8])
+def test_tensor_packer_gives_the_numpy_packers_bytes(bits):
+    """pack() on a GPU tensor runs as tensor arithmetic; the same routine on CPU tensors must produce the planes of
+    the numpy packer (which the golden fixtures pin to the reference's bytes)."""
+    import torch
+    g = torch.Generator().manual_seed(bits)
+    codes, scales = tl.bq.quantize_absmax(torch.randn((256, 320), generator=g) * 0.02, bits)
+    a, b = tl.bq.pack(codes, scales, bits), tl.bq._pack_on_device(codes, scales, bits)
+    assert (a.lo, a.hi, a.scales) == (b.lo, b.hi, b.scales)

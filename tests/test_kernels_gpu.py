@@ -83,58 +83,85 @@ def test_qgemm_matches_oracle_all_configs(bits):
     assert int(ws.counters.abs().sum()) == 0, "tile counters must reset themselves"
 
 
-@pytest.mark.parametrize("m", [1, 5, 16, 77])
-def test_qgemm_epilogues(m):
-    rng = np.random.default_rng(7)
+def _epilogue_case(m, H, I, n_in, n_store, seed, bits=(5, 4, 6)):
+    """Inputs and oracle results of the three fused epilogues for one token count."""
+    rng = np.random.default_rng(seed)
     o = tl.oracle()
-    H, I = 512, 1024
-    ws = tl.Workspace()
     residual = tl.bf16_round(rng.standard_normal((m, H)) * 3)
     xbf = tl.bf16_round(residual)
     partials = np.stack([o.norm_partials(residual[i]) for i in range(m)])
     rs = np.array([o.norm_row_scale(partials[i], H, 1e-6) for i in range(m)], np.float32)
-    xbf_dev, part_dev = tl.to_dev_bf16(xbf), torch.from_numpy(partials).cuda()
-
+    c = {"m": m, "H": H, "I": I, "n_in": n_in, "n_store": n_store, "residual": residual, "partials": partials,
+         "xbf_dev": tl.to_dev_bf16(xbf), "part_dev": torch.from_numpy(partials).cuda()}
     # StoreBF16 + folded-norm row scale, with padded rows trimmed by n_store
-    p = tl.make_bq(1152, H, 5, seed=1, std=0.05)
-    w, wd = tl.DeviceBQ(p, rows=1100), o.dequant(p)
-    want = np.zeros((m, 1152), np.float32)
-    o.qgemm(xbf, wd, rs, 0, out=want, ldo=1152)
-    out = torch.full((m, 1152), 7.0, dtype=torch.bfloat16, device="cuda")
-    ep = pkg.GemmEpilogue(pkg.EPI_STORE_BF16, pkg.ptr(out), 1152, 1100, None, None, None, pkg.ptr(part_dev), H, 1e-6)
-    pkg.check(K().q38_qgemm(pkg.ptr(xbf_dev), m, C.byref(w.desc), C.byref(ep), C.byref(ws.desc), None, -1))
-    got = out.float().cpu().numpy()
-    assert np.all(np.abs(got[:, :1100] - want[:, :1100]) <= 1e-3 + 2e-2 * np.abs(want[:, :1100]))
-    assert np.all(got[:, 1100:] == 7.0), "columns beyond n_store must not be written"
-
+    p = tl.make_bq(n_in, H, bits[0], seed=seed + 1, std=0.05, fast=True)
+    c["w_store"], wd = tl.DeviceBQ(p, rows=n_store), o.dequant(p)
+    c["want_store"] = np.zeros((m, n_in), np.float32)
+    o.qgemm(xbf, wd, rs, 0, out=c["want_store"], ldo=n_in)
     # SwiGLU on interleaved gate/up columns
-    p = tl.make_bq(2 * I, H, 4, seed=2, std=0.05)
-    w, wd = tl.DeviceBQ(p), o.dequant(p)
-    want = np.zeros((m, I), np.float32)
-    o.qgemm(xbf, wd, rs, 1, out=want, ldo=I)
-    out = torch.empty((m, I), dtype=torch.bfloat16, device="cuda")
-    ep = pkg.GemmEpilogue(pkg.EPI_SWIGLU, pkg.ptr(out), I, 0, None, None, None, pkg.ptr(part_dev), H, 1e-6)
-    pkg.check(K().q38_qgemm(pkg.ptr(xbf_dev), m, C.byref(w.desc), C.byref(ep), C.byref(ws.desc), None, -1))
-    got = out.float().cpu().numpy()
-    assert np.all(np.abs(got - want) <= 2e-2 * (np.abs(want) + 1e-3 * np.abs(want).max()))
-
+    p = tl.make_bq(2 * I, H, bits[1], seed=seed + 2, std=0.05, fast=True)
+    c["w_swiglu"], wd = tl.DeviceBQ(p), o.dequant(p)
+    c["want_swiglu"] = np.zeros((m, I), np.float32)
+    o.qgemm(xbf, wd, rs, 1, out=c["want_swiglu"], ldo=I)
     # Residual: residual += C, xbf == bf16(residual) exactly, next-norm partials
-    p = tl.make_bq(H, I, 6, seed=3, std=0.05)
-    w, wd = tl.DeviceBQ(p), o.dequant(p)
+    p = tl.make_bq(H, I, bits[2], seed=seed + 3, std=0.05, fast=True)
+    c["w_res"], wd = tl.DeviceBQ(p), o.dequant(p)
     act = tl.bf16_round(rng.standard_normal((m, I)) * 0.5)
-    res_want, xbf_want, part_want = residual.copy(), np.zeros_like(residual), np.zeros_like(partials)
-    o.qgemm(act, wd, None, 2, residual=res_want, xbf=xbf_want, partials=part_want)
-    res_dev = torch.from_numpy(residual.copy()).cuda()
+    c["act_dev"] = tl.to_dev_bf16(act)
+    c["res_want"], c["xbf_want"], c["part_want"] = residual.copy(), np.zeros_like(residual), np.zeros_like(partials)
+    o.qgemm(act, wd, None, 2, residual=c["res_want"], xbf=c["xbf_want"], partials=c["part_want"])
+    return c
+
+
+def _check_epilogues(c, ws, config):
+    m, H, I, n_in, n_store = c["m"], c["H"], c["I"], c["n_in"], c["n_store"]
+    tag = (m, K().q38_qgemm_config_name(config) if config >= 0 else "auto")
+    out = torch.full((m, n_in), 7.0, dtype=torch.bfloat16, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_STORE_BF16, pkg.ptr(out), n_in, n_store, None, None, None, pkg.ptr(c["part_dev"]), H, 1e-6)
+    pkg.check(K().q38_qgemm(pkg.ptr(c["xbf_dev"]), m, C.byref(c["w_store"].desc), C.byref(ep), C.byref(ws.desc), None, config))
+    got, want = out.float().cpu().numpy(), c["want_store"]
+    assert np.all(np.abs(got[:, :n_store] - want[:, :n_store]) <= 1e-3 + 2e-2 * np.abs(want[:, :n_store])), tag
+    assert np.all(got[:, n_store:] == 7.0), ("columns beyond n_store must not be written", tag)
+
+    out = torch.empty((m, I), dtype=torch.bfloat16, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_SWIGLU, pkg.ptr(out), I, 0, None, None, None, pkg.ptr(c["part_dev"]), H, 1e-6)
+    pkg.check(K().q38_qgemm(pkg.ptr(c["xbf_dev"]), m, C.byref(c["w_swiglu"].desc), C.byref(ep), C.byref(ws.desc), None, config))
+    got, want = out.float().cpu().numpy(), c["want_swiglu"]
+    assert np.all(np.abs(got - want) <= 2e-2 * (np.abs(want) + 1e-3 * np.abs(want).max())), tag
+
+    res_dev = torch.from_numpy(c["residual"].copy()).cuda()
     xbf_out = torch.empty((m, H), dtype=torch.bfloat16, device="cuda")
     part_out = torch.empty((m, H // 128), dtype=torch.float32, device="cuda")
     ep = pkg.GemmEpilogue(pkg.EPI_RESIDUAL, None, 0, 0, pkg.ptr(res_dev), pkg.ptr(xbf_out), pkg.ptr(part_out), None, 0, 1e-6)
-    act_d = tl.to_dev_bf16(act)
-    pkg.check(K().q38_qgemm(pkg.ptr(act_d), m, C.byref(w.desc), C.byref(ep), C.byref(ws.desc), None, -1))
+    pkg.check(K().q38_qgemm(pkg.ptr(c["act_dev"]), m, C.byref(c["w_res"].desc), C.byref(ep), C.byref(ws.desc), None, config))
     sync_ok()
     res_got = res_dev.cpu().numpy()
-    assert np.all(np.abs(res_got - res_want) <= 1e-3 + 1e-3 * np.abs(res_want))
-    assert np.array_equal(xbf_out.float().cpu().numpy(), tl.bf16_round(res_got))
-    assert np.all(np.abs(part_out.cpu().numpy() - part_want) <= 1e-3 + 1e-4 * np.abs(part_want))
+    assert np.all(np.abs(res_got - c["res_want"]) <= 1e-3 + 1e-3 * np.abs(c["res_want"])), tag
+    assert np.array_equal(xbf_out.float().cpu().numpy(), tl.bf16_round(res_got)), tag
+    assert np.all(np.abs(part_out.cpu().numpy() - c["part_want"]) <= 1e-3 + 1e-4 * np.abs(c["part_want"])), tag
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 33, 64, 77, 130, 257, 300])
+def test_qgemm_epilogues(m):
+    """StoreBF16 (+ n_store trimming), SwiGLU and Residual through the dispatcher's own choice and through every
+    tile configuration of both kernels (a configuration smaller than m is applied to row blocks)."""
+    c = _epilogue_case(m, H=512, I=1024, n_in=1152, n_store=1100, seed=7)
+    ws = tl.Workspace()
+    for config in range(-1, K().q38_qgemm_num_configs()):
+        _check_epilogues(c, ws, config)
+    assert int(ws.counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("m", [33, 64])
+def test_qgemm_epilogues_27b_width(m):
+    """The epilogues at the 27B hidden size (40 weight tiles for the Residual projections, the cut of every tile over
+    three CTAs) and a 4-bit gate/up block of 68 tiles, decode-batch token counts."""
+    c = _epilogue_case(m, H=5120, I=4352, n_in=2048, n_store=2000, seed=11)
+    ws = tl.Workspace()
+    names = {K().q38_qgemm_config_name(i).decode(): i for i in range(K().q38_qgemm_num_configs())}
+    for config in (-1, names["tmem_t64"], names["tmem_t128"], names["umma_t64"], names["stream_m16"]):
+        _check_epilogues(c, ws, config)
+    assert int(ws.counters.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("n,k,bits", [(34816, 5120, 4), (5120, 17408, 6)])
@@ -362,17 +389,62 @@ def test_attention_ragged_batch_gqa4_long_context():
         assert np.all(np.abs(out_pf - out_got) <= 2e-2 * (np.abs(out_got) + 0.02 * np.abs(out_got).max()))
 
 
+def fill_kv_random(pool, layer, nq, nkv, slot, upto, qn_dev, kn_dev, gen):
+    """Appends `upto` tokens of N(0, 1) projections (drawn on the device) to a sequence's cache, 512 at a time."""
+    ld = 2 * nq * 256 + 2 * nkv * 256
+    for p0 in range(0, upto, 512):
+        n = min(512, upto - p0)
+        proj_d = torch.randn((n, ld), generator=gen, device="cuda").to(torch.bfloat16)
+        batch = tl.Batch([(slot, p0, n)])
+        q16 = torch.empty((n, nq, 256), dtype=torch.float16, device="cuda")
+        qp = pkg.QkNormRopeParams(pkg.ptr(proj_d), ld, pkg.ptr(qn_dev), pkg.ptr(kn_dev), 1e-6, 1e7, nq, nkv, pkg.ptr(q16), layer)
+        pkg.check(K().q38_qk_norm_rope_append(C.byref(qp), C.byref(batch.desc), C.byref(pool.desc), None))
+
+
+def test_attention_decode_16_sequences_up_to_32768():
+    """The decode step of a 16-sequence ragged batch, 24 q / 4 kv heads, contexts log-uniform in 128..32768 (seed 3)
+    with the longest forced to 32768, page ids from a seeded shuffle."""
+    nq, nkv, layer = 24, 4, 0
+    ld = 2 * nq * 256 + 2 * nkv * 256
+    r3 = np.random.default_rng(3)
+    ctx = [int(round(np.exp(u))) for u in r3.uniform(np.log(128), np.log(32768), size=16)]
+    ctx[5] = 32768
+    qn = (1 + 0.2 * r3.standard_normal(256)).astype(np.float32)
+    kn = (1 + 0.2 * r3.standard_normal(256)).astype(np.float32)
+    qn_dev, kn_dev = torch.from_numpy(qn).cuda(), torch.from_numpy(kn).cuda()
+    need = [(c + 63) // 64 for c in ctx]
+    pool = tl.KvPool(nkv, layers=1, num_pages=sum(need) + 5, slots=16, max_pages_per_seq=max(need), dtype=0)
+    perm = np.random.default_rng(5).permutation(sum(need) + 5).astype(np.int32)
+    used = 0
+    for s, pages in enumerate(need):
+        pool.table[s, :pages] = torch.from_numpy(perm[used:used + pages]).cuda()
+        used += pages
+    gen = torch.Generator(device="cuda").manual_seed(33)
+    for s, c in enumerate(ctx):
+        fill_kv_random(pool, layer, nq, nkv, s, c - 1, qn_dev, kn_dev, gen)
+    proj = tl.bf16_round(np.random.default_rng(34).standard_normal((16, ld)))
+    batch = tl.Batch([(s, c - 1, 1) for s, c in enumerate(ctx)])
+    q_got, out_got = run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decode=True, split_rows=64)
+    o = tl.oracle()
+    for s, c in enumerate(ctx):
+        kd, vd = pool.read_sequence(layer, s, c)
+        seen = tl.OracleKv(o, nkv, c)
+        seen.k[:], seen.v[:] = kd, vd
+        want = seen.attend(nq, q_got[s], proj[s, nq * 256:2 * nq * 256], c - 1)
+        assert np.all(np.abs(out_got[s] - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())), (s, c)
+
+
 # ---------------------------------------------------------------------------------------------------
 # Gated DeltaNet
 # ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("chunked", [False, True])
-@pytest.mark.parametrize("nk,nv", [(2, 6), (2, 2)])
-def test_gdn_matches_oracle(nk, nv, chunked):
-    """Chunk lengths {37, 64, 1, 1, 100, 1, 17} on slot 1 of 3, GDN layer 1 of 2; a second sequence runs in
-    the same ragged batch on slot 2 with its own lengths."""
+@pytest.mark.parametrize("nk,nv,H", [(2, 6, 512), (2, 2, 512), (16, 32, 5120), (16, 48, 5120)])
+def test_gdn_matches_oracle(nk, nv, H, chunked):
+    """Chunk lengths {37, 64, 1, 1, 100, 1, 17, 300} on slot 1 of 3, GDN layer 1 of 2; a second sequence runs in
+    the same ragged batch on slot 2 with its own lengths. Head counts: small ones, 16 key / 32 value heads (value
+    heads share a key head in pairs) and the 27B model's 16 / 48 at its hidden size 5120."""
     rng = np.random.default_rng(5)
     o = tl.oracle()
-    H = 512
     conv_dim = 2 * nk * 128 + nv * 128
     ld = conv_dim + nv * 128
     layers, layer, slots = 2, 1, 3

@@ -20,7 +20,8 @@ def test_static_workspace_gemm_matches_the_caller_workspace_gemm_twice():
     K = pkg.kernels()
     rng = np.random.default_rng(17)
     ws = tl.Workspace()
-    for bits, n, k in ((4, 1536, 512), (5, 5120, 1024), (8, 256, 6144)):
+    # the last shape has more than four 128-column tiles per SM: the even cut over all SMs, two partial tiles per CTA
+    for bits, n, k in ((4, 1536, 512), (5, 5120, 1024), (8, 256, 6144), (4, 76800, 256)):
         w = tl.DeviceBQ(tl.make_bq(n, k, bits, seed=bits, std=0.05, fast=True))
         for m in (1, 7, 16):
             a = tl.to_dev_bf16(rng.standard_normal((m, k)))
