@@ -432,4 +432,185 @@ float orc_target_logprob(const float* logits, int vocab, int target) {
   return float(double(logits[target]) - mx - std::log(z));
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Stochastic sampler (restates the engine's sampling kernel, which follows the definition of the reference's
+// src/kernels/sampling.cu:137-310: penalties once per distinct history token, top-k / min-p / top-p cuts on the
+// ordered logit keys, 2^-40 fixed-point masses, splitmix64 inverse-CDF draw in index order). The reference has no CPU
+// sampler; this restatement and the kernel share one arithmetic definition made of IEEE operations only (explicit
+// single / double roundings, fused multiply-adds, no library exp or log), so the two must agree bit for bit.
+// ---------------------------------------------------------------------------------------------------
+namespace {
+
+inline uint32_t order_key(float x) {
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+inline float key_to_float(uint32_t key) {
+  const uint32_t u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+  float x;
+  std::memcpy(&x, &u, 4);
+  return x;
+}
+
+#if defined(__x86_64__)
+__attribute__((target("fma"))) double poly_fma_hw(double f) {
+  double p = 1.3691488853904128e-12;
+  const double c[] = {2.5678435993488206e-11, 4.4455382718708116e-10, 7.054911620801123e-09, 1.01780860092397e-07,
+                      1.321548679014431e-06,  1.5252733804059841e-05, 0.0001540353039338161, 0.0013333558146428443,
+                      0.009618129107628477,   0.05550410866482158,    0.24022650695910072,   0.6931471805599453,
+                      1.0};
+  for (double ck : c) p = __builtin_fma(p, f, ck);
+  return p;
+}
+#endif
+double poly_fma_sw(double f) {
+  double p = 1.3691488853904128e-12;
+  const double c[] = {2.5678435993488206e-11, 4.4455382718708116e-10, 7.054911620801123e-09, 1.01780860092397e-07,
+                      1.321548679014431e-06,  1.5252733804059841e-05, 0.0001540353039338161, 0.0013333558146428443,
+                      0.009618129107628477,   0.05550410866482158,    0.24022650695910072,   0.6931471805599453,
+                      1.0};
+  for (double ck : c) p = std::fma(p, f, ck);  // correctly rounded in software where the CPU has no FMA unit
+  return p;
+}
+double exp2_fraction(double f) {
+#if defined(__x86_64__)
+  static const bool hw = __builtin_cpu_supports("fma");
+  if (hw) return poly_fma_hw(f);
+#endif
+  return poly_fma_sw(f);
+}
+
+// 2^40 * exp((l - max) * inv_t), truncated: the operation sequence of the kernel's fixed_mass().
+uint64_t fixed_mass(float l, float max_logit, float inv_t) {
+  volatile float d = l - max_logit;  // volatile: each step rounds to its declared width
+  volatile float x = d * inv_t;
+  volatile double y = double(x) * 1.4426950408889634;
+  if (!(y > -64.0)) return 0;
+  if (y > 0.0) return uint64_t(1) << 40;
+  volatile double yh = y + 0.5;
+  const double n = std::floor(yh);
+  volatile double f = y - n;
+  const double p = exp2_fraction(f);
+  const int64_t e = int64_t(n) + 40;
+  const uint64_t bits = uint64_t(1023 + e) << 52;
+  double scale;
+  std::memcpy(&scale, &bits, 8);
+  volatile double scaled = p * scale;
+  return uint64_t(scaled);
+}
+
+uint32_t min_p_key(float max_logit, float inv_t, float min_p) {
+  volatile double c = double(min_p) * 1099511627776.0;
+  const uint64_t cut = uint64_t(c);
+  uint32_t lo = 0x00800000u, hi = order_key(max_logit);
+  if (hi < lo) return hi;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    if (fixed_mass(key_to_float(mid), max_logit, inv_t) >= cut) hi = mid;
+    else lo = mid + 1;
+  }
+  return hi;
+}
+
+inline uint64_t mix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+}  // namespace
+
+// Penalties in place: every distinct token among the first min(len, cap) history entries is penalised once.
+void orc_sample_penalties(float* logits, int vocab, const int32_t* history, int len, int cap, float presence,
+                          float repetition) {
+  if (presence == 0.0f && repetition == 1.0f) return;
+  std::vector<bool> seen(size_t(vocab), false);
+  const int n = std::min(len, cap);
+  for (int i = 0; i < n; ++i) {
+    const int t = history[i];
+    if (t < 0 || t >= vocab || seen[size_t(t)]) continue;
+    seen[size_t(t)] = true;
+    volatile float l = logits[t];
+    if (repetition != 1.0f) l = l > 0.0f ? l / repetition : l * repetition;
+    volatile float r = l - presence;
+    logits[t] = r;
+  }
+}
+
+// `count` draws from one (already penalised) logits row with one parameter set and per-draw (seed, step).
+// tokens_out / logprob_out as the kernel reports them; temperature <= 0 gives the lowest-id argmax and logprob 0.
+void orc_sample_draws(const float* logits, int vocab, float temperature, int top_k, float top_p, float min_p,
+                      const uint64_t* seeds, const int32_t* steps, int count, int32_t* tokens_out, float* logprob_out) {
+  int best = 0;
+  for (int i = 1; i < vocab; ++i)
+    if (logits[i] > logits[best]) best = i;
+  if (temperature <= 0.0f) {
+    for (int d = 0; d < count; ++d) {
+      tokens_out[d] = best;
+      logprob_out[d] = 0.0f;
+    }
+    return;
+  }
+  const float M = logits[best];
+  volatile float inv_t_v = 1.0f / temperature;
+  const float inv_t = inv_t_v;
+  std::vector<uint64_t> mass(static_cast<size_t>(vocab));
+  std::vector<uint32_t> key(static_cast<size_t>(vocab));
+  uint64_t all_sum = 0;
+  for (int i = 0; i < vocab; ++i) {
+    mass[size_t(i)] = fixed_mass(logits[i], M, inv_t);
+    key[size_t(i)] = order_key(logits[i]);
+    all_sum += mass[size_t(i)];
+  }
+  uint32_t thresh = 0;
+  if (top_k > 0 && top_k < vocab) {  // the k-th largest key: every logit that ties with it stays
+    std::vector<uint32_t> tmp(key);
+    std::nth_element(tmp.begin(), tmp.begin() + (top_k - 1), tmp.end(), std::greater<uint32_t>());
+    thresh = tmp[size_t(top_k - 1)];
+  }
+  if (min_p > 0.0f) thresh = std::max(thresh, min_p_key(M, inv_t, min_p));
+  if (top_p < 1.0f) {
+    std::vector<std::pair<uint32_t, uint64_t>> cand;
+    uint64_t kept = 0;
+    for (int i = 0; i < vocab; ++i)
+      if (key[size_t(i)] >= thresh) {
+        cand.emplace_back(key[size_t(i)], mass[size_t(i)]);
+        kept += mass[size_t(i)];
+      }
+    volatile double tv = double(top_p) * double(kept);
+    uint64_t target = uint64_t(tv);
+    if (target == 0) target = 1;
+    std::sort(cand.begin(), cand.end(), [](const auto& a, const auto& b) { return a.first > b.first; });
+    uint64_t cum = 0;
+    uint32_t cut = thresh;
+    for (size_t i = 0; i < cand.size();) {  // whole groups of equal keys: the largest key whose tail mass reaches the target
+      size_t j = i;
+      while (j < cand.size() && cand[j].first == cand[i].first) cum += cand[j++].second;
+      if (cum >= target) {
+        cut = cand[i].first;
+        break;
+      }
+      i = j;
+    }
+    thresh = std::max(thresh, cut);
+  }
+  std::vector<uint64_t> prefix(static_cast<size_t>(vocab) + 1, 0);  // kept mass before index i
+  for (int i = 0; i < vocab; ++i) prefix[size_t(i) + 1] = prefix[size_t(i)] + (key[size_t(i)] >= thresh ? mass[size_t(i)] : 0);
+  const uint64_t total = prefix[size_t(vocab)];
+  for (int d = 0; d < count; ++d) {
+    const uint64_t r = mix64(seeds[d] ^ (0xD1B54A32D192ED03ull * uint64_t(steps[d] + 1)));
+    volatile double u01 = double(r >> 11) * (1.0 / 9007199254740992.0);
+    volatile double ud = u01 * double(total);
+    uint64_t u = uint64_t(ud);
+    if (u >= total) u = total - 1;
+    // first index whose inclusive kept mass exceeds u
+    const size_t at = size_t(std::upper_bound(prefix.begin() + 1, prefix.end(), u) - (prefix.begin() + 1));
+    tokens_out[d] = int32_t(at);
+    const double p = double(mass[at]) / double(all_sum > 0 ? all_sum : 1);
+    logprob_out[d] = float(std::log(p > 0.0 ? p : 1e-300));
+  }
+}
+
 }  // extern "C"

@@ -121,9 +121,15 @@ __global__ void __launch_bounds__(1024) pack_ragged_kernel(const int* __restrict
 // top-p keeps the smallest set of largest logits whose mass reaches top_p of the kept mass, and the
 // token is drawn by inverse CDF in index order. All masses are integers in 2^-40 fixed point, so the
 // draw is a pure function of (logits, params, seed, step).
+//
+// Where this departs from the reference kernel: the reference takes exp((l - max) / T) from the special-function
+// unit (__expf) and the min-p bound from logf, whose bit patterns belong to one GPU generation and to no CPU. Here
+// both come from fixed_mass(), a sequence of IEEE single / double operations with explicit roundings (no contraction,
+// no library call), so a host restatement of this file gives the same integer masses, the same thresholds and
+// therefore the same token for every (logits, params, seed, step). The min-p bound is the smallest logit whose mass
+// reaches min_p * 2^40, found by bisection over the ordered float keys.
 // ---------------------------------------------------------------------------------------------------
 constexpr int kSampleThreads = 1024;
-constexpr double kFix = 1099511627776.0;  // 2^40
 
 struct SampleShared {
   uint32_t seen[(256 * 1024) / 32];
@@ -145,6 +151,54 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
   x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
   x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
   return x ^ (x >> 31);
+}
+
+// 2^40 * exp((l - max) * inv_t), truncated, in operations that round the same way on every IEEE machine:
+// x = fl32(fl32(l - max) * inv_t); y = fl64(x * log2 e); n = floor(y + 1/2); f = y - n (exact); 2^f by a degree-13
+// Taylor polynomial in Horner form with fused multiply-adds; the scaling by 2^(n + 40) is exact.
+__device__ __forceinline__ unsigned long long fixed_mass(float l, float max_logit, float inv_t) {
+  const float x = __fmul_rn(__fsub_rn(l, max_logit), inv_t);
+  const double y = __dmul_rn(double(x), 1.4426950408889634);
+  if (!(y > -64.0)) return 0ull;  // below 2^-24 of one fixed-point unit (also NaN and -inf)
+  if (y > 0.0) return 1ull << 40; // l above the maximum cannot happen; keeps the shift below in range
+  const double n = floor(__dadd_rn(y, 0.5));
+  const double f = __dsub_rn(y, n);
+  double p = 1.3691488853904128e-12;
+  p = fma(p, f, 2.5678435993488206e-11);
+  p = fma(p, f, 4.4455382718708116e-10);
+  p = fma(p, f, 7.054911620801123e-09);
+  p = fma(p, f, 1.01780860092397e-07);
+  p = fma(p, f, 1.321548679014431e-06);
+  p = fma(p, f, 1.5252733804059841e-05);
+  p = fma(p, f, 0.0001540353039338161);
+  p = fma(p, f, 0.0013333558146428443);
+  p = fma(p, f, 0.009618129107628477);
+  p = fma(p, f, 0.05550410866482158);
+  p = fma(p, f, 0.24022650695910072);
+  p = fma(p, f, 0.6931471805599453);
+  p = fma(p, f, 1.0);
+  const long long e = (long long)n + 40;  // -24 .. 40
+  const double scale = __longlong_as_double((1023ll + e) << 52);
+  return (unsigned long long)__dmul_rn(p, scale);
+}
+
+__device__ __forceinline__ float key_to_float(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// Smallest ordered key whose logit keeps a mass of at least min_p * 2^40 (bisection between -FLT_MAX and the maximum).
+__device__ uint32_t min_p_key(float max_logit, float inv_t, float min_p) {
+  const unsigned long long cut = (unsigned long long)__dmul_rn(double(min_p), 1099511627776.0);
+  uint32_t lo = 0x00800000u;  // key of -FLT_MAX
+  uint32_t hi = (__float_as_uint(max_logit) & 0x80000000u) ? ~__float_as_uint(max_logit)
+                                                           : (__float_as_uint(max_logit) | 0x80000000u);
+  if (hi < lo) return hi;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    if (fixed_mass(key_to_float(mid), max_logit, inv_t) >= cut) hi = mid;
+    else lo = mid + 1u;
+  }
+  return hi;
 }
 
 __device__ unsigned long long cta_sum_u64(unsigned long long v, SampleShared& sm) {
@@ -225,8 +279,9 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(q38_sampling_
       const uint32_t bit = 1u << (t & 31);
       if (atomicOr(&sm.seen[t >> 5], bit) & bit) continue;
       float l = logits[t];
-      if (prm.repetition_penalty != 1.0f) l = l > 0.0f ? l / prm.repetition_penalty : l * prm.repetition_penalty;
-      logits[t] = l - prm.presence_penalty;
+      if (prm.repetition_penalty != 1.0f)
+        l = l > 0.0f ? __fdiv_rn(l, prm.repetition_penalty) : __fmul_rn(l, prm.repetition_penalty);
+      logits[t] = __fsub_rn(l, prm.presence_penalty);  // explicit roundings: no multiply-subtract contraction
     }
     __syncthreads();
   }
@@ -268,15 +323,13 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(q38_sampling_
     return;
   }
   const float M = best;
-  const float inv_t = 1.0f / prm.temperature;
-  auto mass = [&](float l) -> unsigned long long {
-    return (unsigned long long)(double(__expf((l - M) * inv_t)) * kFix);
-  };
+  const float inv_t = __fdiv_rn(1.0f, prm.temperature);
+  auto mass = [&](float l) -> unsigned long long { return fixed_mass(l, M, inv_t); };
 
   uint32_t thresh = 0u;
   if (prm.top_k > 0 && prm.top_k < V)
     thresh = radix_threshold(logits, V, 0u, (unsigned long long)prm.top_k, sm, [](float) { return 1ull; });
-  if (prm.min_p > 0.0f) thresh = max(thresh, order_key(M + prm.temperature * logf(prm.min_p)));
+  if (prm.min_p > 0.0f) thresh = max(thresh, min_p_key(M, inv_t, prm.min_p));
   if (prm.top_p < 1.0f) {
     unsigned long long local = 0ull;
     for (int i = tid; i < V; i += kSampleThreads) {
@@ -284,7 +337,7 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(q38_sampling_
       if (order_key(l) >= thresh) local += mass(l);
     }
     const unsigned long long kept = cta_sum_u64(local, sm);
-    const unsigned long long target = (unsigned long long)(double(prm.top_p) * double(kept));
+    const unsigned long long target = (unsigned long long)__dmul_rn(double(prm.top_p), double(kept));
     thresh = max(thresh, radix_threshold(logits, V, thresh, target > 0 ? target : 1ull, sm, mass));
   }
 
@@ -316,8 +369,9 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(q38_sampling_
 
   const int step = a.step ? a.step[b] : 0;
   const uint64_t r = mix64(prm.seed ^ (0xD1B54A32D192ED03ull * uint64_t(step + 1)));
-  const double u01 = double(r >> 11) * (1.0 / 9007199254740992.0);
-  const unsigned long long u = (unsigned long long)(u01 * double(total));
+  const double u01 = __dmul_rn(double(r >> 11), 1.0 / 9007199254740992.0);
+  unsigned long long u = (unsigned long long)__dmul_rn(u01, double(total));
+  if (u >= total) u = total - 1ull;  // double(total) may round up beyond 2^53: the draw stays inside the kept mass
   if (own > 0 && u >= before && u < before + own) {
     unsigned long long cum = before;
     int tok = -1, last = -1;

@@ -295,6 +295,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         const int ng = min(kGroupsPerStage, kg_b - g);
         int ok = 1;
         if (lane == 0) {
+          // a reused stage is free once the decode warps are through with it, and they in turn wait for MMAs that need
+          // the previous kernel's output: from here on the bounded waits run on this kernel's time only
+          if (it == uint32_t(C::kStages)) pdl_wait();
           ok = wait_flag(&raw_empty[s], ((it / C::kStages) & 1) ^ 1, flags, 0x301) ? 1 : 0;
           if (ok)
             mbar_expect_tx(&raw_full[s], uint32_t(ng) * 2u * (G::kLoGroupBytes + G::kHiGroupBytes + G::kScGroupBytes));
@@ -363,6 +366,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       const uint64_t desc0 = smem_desc_sw128(smem_u32(units));
       uint32_t uc = 0, seg = 0;
       bool alive = true;
+      // Everything this warp waits for needs the activations, which the previous kernel of the stream produces: the
+      // bounded waits below start counting only once that kernel is complete.
+      pdl_wait();
       for (long long u = u0; u < u1 && alive; ++seg) {
         const int kg_a = int(u % a.kg);
         const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
@@ -425,6 +431,16 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     const int cchunk = dw >> 2;        // which chunk of the token columns it handles in the epilogue
     const bool epi_active = cchunk < C::kEpiChunks;
     const int et = tid - kFirstDecodeWarp * 32;  // 0..511 among the decode threads
+    bool dep_passed = false;
+    // Wait for an operand slot. Its first use is free; a reused slot is handed back by the MMA warp, whose work needs
+    // the previous kernel's output, so the bounded wait starts counting only after that kernel is complete.
+    auto wait_slot = [&](int slot, uint32_t par) {
+      if (par != 0 && !dep_passed) {
+        pdl_wait();
+        dep_passed = true;
+      }
+      return wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+    };
     // destination of pair (j, h) of slab ks: row 64 dnb + 8 j + gl, 16-byte chunk (2 ks + h) ^ gl
     const uint32_t row_off = uint32_t(dnb) * 8192u + uint32_t(gl) * 128u + 4u * uint32_t(tl);
     const uint32_t c0_off = row_off + (uint32_t((2 * ks) ^ gl) << 4);
@@ -551,7 +567,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                   }
                 }
                 if (e == 0) {
-                  free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+                  free_slot = wait_slot(slot, par);
                   tc_fence_after();
                 }
                 // rows 0-15 of the quarter (pairs j' = 0, 1), then rows 16-31 (j' = 2, 3): an mma A fragment per slab
@@ -598,7 +614,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
               int slot;
               uint32_t par;
               unit_at(half, slot, par);
-              const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+              const bool free_slot = wait_slot(slot, par);
               uint8_t* base = units + (size_t)slot * C::kUnitBytes;
               if (ok && free_slot) store_slice(base, w);
               if (two) {
@@ -620,7 +636,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                   int slot;
                   uint32_t par;
                   unit_at(g0 + kGStep * e, slot, par);
-                  const bool free_slot = wait_flag(&op_empty[slot], par ^ 1u, flags, 0x306);
+                  const bool free_slot = wait_slot(slot, par);
                   if (ok && free_slot) store_slice(units + (size_t)slot * C::kUnitBytes, w);
                   fence_async_smem();
                   __syncwarp();
@@ -643,10 +659,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       }
 
       // ---- epilogue of this tile segment ----
+      if (seg == 0) pdl_wait();  // the accumulator needs the previous kernel's output; so do the row scales below
       const bool got = __all_sync(0xffffffffu, wait_flag(acc_full, seg & 1, flags, 0x307));
       tc_fence_after();
       if (seg == 0 || a.mblocks > 1) {  // the row scales of the folded RMSNorm for this token block
-        if (seg == 0) pdl_wait();       // first use of activations-side data by these warps
         row_scales_to_smem(a.partials_in ? a.partials_in + (size_t)row0 * (a.hidden / 128) : nullptr, a.m - row0, TOK,
                            a.hidden, a.eps, rs_sm, et, kDecodeThreads);
         named_bar_sync(1, kDecodeThreads);

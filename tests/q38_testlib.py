@@ -94,6 +94,25 @@ class CpuOps:
         return out
 
 
+    def sample_penalties(self, logits: np.ndarray, history, presence: float, repetition: float, cap: int) -> np.ndarray:
+        """Penalised copy of one logits row (every distinct history token once)."""
+        out = _np(logits, np.float32).copy()
+        h = _np(history, np.int32)
+        self.fn("sample_penalties")(_vp(out), C.c_int(out.size), _vp(h), C.c_int(h.size), C.c_int(cap),
+                                    C.c_float(presence), C.c_float(repetition))
+        return out
+
+    def sample_draws(self, logits: np.ndarray, temperature, top_k, top_p, min_p, seeds, steps):
+        """Tokens and log-probabilities of len(seeds) draws from one (already penalised) logits row."""
+        lg = _np(logits, np.float32)
+        sd, st = _np(seeds, np.uint64), _np(steps, np.int32)
+        toks = np.empty(sd.size, dtype=np.int32)
+        lps = np.empty(sd.size, dtype=np.float32)
+        self.fn("sample_draws")(_vp(lg), C.c_int(lg.size), C.c_float(temperature), C.c_int(top_k), C.c_float(top_p),
+                                C.c_float(min_p), _vp(sd), _vp(st), C.c_int(sd.size), _vp(toks), _vp(lps))
+        return toks, lps
+
+
 class OracleKv:
     """Dequantised KV store of one sequence and one layer, [kv_heads][capacity][256], for either library."""
 

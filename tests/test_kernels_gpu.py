@@ -666,6 +666,57 @@ def test_sampling_filters_and_determinism():
     assert np.isclose(lg_after[0, 5], (l5 / 2.0 if l5 > 0 else l5 * 2.0) - 0.5)
 
 
+def test_sampler_draws_equal_the_cpu_restatement():
+    """The stochastic sampler against its CPU restatement (oracle/q38_oracle.cpp): sampled token ids must be
+    identical, draw for draw, on the 27B vocabulary (248,320 logits) for top-k, top-p, min-p, their combinations and
+    penalties: 10,240 draws = 10 parameter sets x 4 logit rows x 256 (seed, step) pairs. Both sides compute the
+    fixed-point masses and thresholds with the same IEEE operations, so there is no tolerance on the ids; the reported
+    log-probability goes through a library log and is compared to 1e-5."""
+    V, D = 248320, 256
+    rng = np.random.default_rng(90)
+    o = tl.oracle()
+    rows = [(2.0 * rng.standard_normal(V)).astype(np.float32),            # flat: thousands of candidates
+            (6.0 * rng.standard_normal(V)).astype(np.float32),            # peaked
+            np.round(3.0 * rng.standard_normal(V)).astype(np.float32),    # heavy ties (integer logits)
+            (0.02 * rng.standard_normal(V)).astype(np.float32) * 70.0]    # the range of a random-weight model
+    psets = [dict(t=1.0, k=50), dict(t=0.7, k=0, p=0.9), dict(t=1.3, minp=0.05), dict(t=0.8, k=20, p=0.95),
+             dict(t=1.0, k=1000, p=0.5, minp=0.001), dict(t=0.6), dict(t=2.5, p=0.99), dict(t=1.0, k=40, pres=0.7, rep=1.3),
+             dict(t=0.9, p=0.8, pres=-0.5, rep=0.8), dict(t=1.0, k=5, minp=0.2, rep=2.0)]
+    cap = 64
+    mism = 0
+    for pi, ps in enumerate(psets):
+        for ri, row in enumerate(rows):
+            seeds = rng.integers(1, 2 ** 63, size=D, dtype=np.uint64)
+            steps = rng.integers(0, 5000, size=D).astype(np.int32)
+            order = np.argsort(row)
+            hist = np.concatenate([order[-20:], order[-5:], rng.integers(0, V, size=cap - 25)]).astype(np.int32)
+            assert hist.shape == (cap,)  # the kernel addresses history rows of exactly `cap` entries
+            use_hist = ("pres" in ps) or ("rep" in ps)
+            prm = [P(t=ps["t"], k=ps.get("k", 0), p=ps.get("p", 1.0), minp=ps.get("minp", 0.0), pres=ps.get("pres", 0.0),
+                     rep=ps.get("rep", 1.0), seed=int(sd)) for sd in seeds]
+            lg = torch.from_numpy(row).cuda().repeat(D, 1).contiguous()
+            prm_dev = torch.frombuffer(bytearray(bytes((pkg.SamplingParamsDev * D)(*prm))), dtype=torch.uint8).cuda()
+            slot = torch.arange(D, dtype=torch.int32, device="cuda")
+            steps_d = torch.from_numpy(steps).cuda()
+            hl = torch.full((D,), len(hist) if use_hist else 0, dtype=torch.int32, device="cuda")
+            hist_d = torch.from_numpy(np.tile(hist, (D, 1))).cuda().contiguous()
+            out = torch.full((D,), -1, dtype=torch.int32, device="cuda")
+            lp = torch.empty(D, dtype=torch.float32, device="cuda")
+            a = pkg.SamplingArgs(pkg.ptr(lg), V, V, pkg.ptr(prm_dev), pkg.ptr(slot), pkg.ptr(hist_d), pkg.ptr(hl), cap,
+                                 pkg.ptr(steps_d), pkg.ptr(out), pkg.ptr(lp))
+            pkg.check(K().q38_sample(C.byref(a), D, None))
+            sync_ok()
+            pen = o.sample_penalties(row, hist if use_hist else [], ps.get("pres", 0.0), ps.get("rep", 1.0), cap)
+            assert np.array_equal(lg[0].cpu().numpy(), pen), "penalised logits differ"
+            want, want_lp = o.sample_draws(pen, ps["t"], ps.get("k", 0), ps.get("p", 1.0), ps.get("minp", 0.0), seeds, steps)
+            got = out.cpu().numpy()
+            mism += int((got != want).sum())
+            assert np.array_equal(got, want), (pi, ri, int((got != want).sum()), got[:8], want[:8])
+            assert np.allclose(lp.cpu().numpy(), want_lp, atol=1e-5, rtol=1e-5), (pi, ri)
+            assert len(np.unique(got)) > 1 or ps.get("k", 0) == 1
+    assert mism == 0
+
+
 def test_target_logprobs_matches_oracle():
     rng = np.random.default_rng(2)
     V, rows = 4096, 5

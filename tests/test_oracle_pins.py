@@ -196,3 +196,34 @@ def test_c_abi_library_exports_every_declared_symbol():
     assert lib.q38_attention_decode_splits(1, 4, 148, 64) == 64
     assert lib.q38_attention_decode_splits(4096, 4, 148, 64) == 1
     assert lib.q38_attention_decode_splits(64, 4, 148, 4) == 4
+
+
+def test_sampler_restatement_obeys_its_definition():
+    """The CPU sampler (the checker of the GPU sampler's token ids) on the 27B vocabulary: top-k = 1 is the argmax,
+    top-k keeps the k largest, min-p keeps only tokens whose probability ratio to the maximum reaches min_p, a draw is
+    a pure function of (seed, step), and top-3 frequencies follow the softmax."""
+    V = 248320
+    rng = np.random.default_rng(1)
+    o = tl.oracle()
+    row = (2.0 * rng.standard_normal(V)).astype(np.float32)
+    seeds = rng.integers(1, 2 ** 63, size=256, dtype=np.uint64)
+    steps = rng.integers(0, 5000, size=256).astype(np.int32)
+    tok, _ = o.sample_draws(row, 1.0, 1, 1.0, 0.0, seeds, steps)
+    assert set(tok.tolist()) == {int(row.argmax())}
+    tok, lp = o.sample_draws(row, 1.0, 50, 1.0, 0.0, seeds, steps)
+    assert set(tok.tolist()) <= set(np.argsort(row)[-50:].tolist()) and len(set(tok.tolist())) > 20
+    again, lp2 = o.sample_draws(row, 1.0, 50, 1.0, 0.0, seeds, steps)
+    assert np.array_equal(tok, again) and np.array_equal(lp, lp2)
+    tok, _ = o.sample_draws(row, 1.3, 0, 1.0, 0.05, seeds, steps)
+    assert np.exp((row[tok] - row.max()) / 1.3).min() >= 0.05 * (1 - 1e-6)
+    many = rng.integers(1, 2 ** 63, size=20000, dtype=np.uint64)
+    tok, _ = o.sample_draws(row, 1.0, 3, 1.0, 0.0, many, np.zeros(20000, np.int32))
+    top = np.argsort(row)[-3:]
+    pr = np.exp(row[top] - row[top].max())
+    pr /= pr.sum()
+    for i, p in zip(top, pr):
+        assert abs((tok == i).mean() - p) < 5 * np.sqrt(p * (1 - p) / 20000)
+    pen = o.sample_penalties(row, [5, 5, 7], 0.5, 2.0, 16)
+    for t in (5, 7):
+        assert pen[t] == np.float32(np.float32(row[t] / 2 if row[t] > 0 else row[t] * 2) - np.float32(0.5))
+    assert np.array_equal(np.delete(pen, [5, 7]), np.delete(row, [5, 7]))
