@@ -121,6 +121,7 @@ typedef struct q38e_engine_options {
   q38e_runner_options runner;
   uint64_t seed;
   int ragged_prefill;
+  int mixed_steps;     /* generating sequences' tokens ride in the prefill step while prompts are pending */
 } q38e_engine_options;
 int q38e_engine_create(const q38e_model* m, const q38e_engine_options* o, q38e_engine** out);
 void q38e_engine_destroy(q38e_engine* e);

@@ -137,6 +137,13 @@ int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, int hidden, f
 int q38_residual_update(const float* delta, int m, int hidden, float* residual, q38_bf16* xbf, float* partials,
                         void* stream);
 
+/* Packs rows rows[0..n) of the step's LM-head inputs (bf16 hidden rows x [M][hidden] and their norm partial sums
+ * [M][hidden / 128]) into rows 0..n-1 of x_out / partials_out: the last-token rows of the sequences that sample in a
+ * ragged step. Replaces the per-row device copies of the reference's prefill path (src/model_runner.cpp:471-489 reads
+ * one row; a ragged step has up to one per sequence). `rows` is a device array. */
+int q38_gather_rows(const q38_bf16* x, const float* partials, const int* rows, int n, int hidden, q38_bf16* x_out,
+                    float* partials_out, void* stream);
+
 /* kernels::QkNormRopeParams + qk_norm_rope_append, kernels.h:140-155 */
 typedef struct q38_qk_norm_rope_params {
   const q38_bf16* proj; /* [M][ld_proj]: [q | gate | k | v] */
@@ -164,6 +171,11 @@ typedef struct q38_attention_params {
   int attn_layer;
   float* split_scratch;  /* [B][nq][max_splits][256 + 2] floats */
   int max_splits;
+  /* Extension (not in the reference's struct): rows B the scratch was sized for. Decode needs one row per sequence
+   * and ignores the field. Prefill cuts the keys of its query tiles over several CTAs only when there are few tiles
+   * for the GPU (one long request, a tensor-parallel rank with one kv head) and only if the scratch holds one row
+   * per prompt token of the step: scratch_rows >= num_tokens. 0 = sized for the decode batch only (never split). */
+  int scratch_rows;
 } q38_attention_params;
 int q38_attention_decode_splits(int batch_seqs, int kv_heads, int num_sms, int max_splits);
 int q38_attention_decode(const q38_attention_params* p, const q38_batch_desc* batch, const q38_kv_cache_desc* kv,

@@ -65,7 +65,7 @@ class QkNormRopeParams(C.Structure):
 class AttentionParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int), ("out", C.c_void_p),
                 ("num_q_heads", C.c_int), ("num_kv_heads", C.c_int), ("attn_layer", C.c_int),
-                ("split_scratch", C.c_void_p), ("max_splits", C.c_int)]
+                ("split_scratch", C.c_void_p), ("max_splits", C.c_int), ("scratch_rows", C.c_int)]
 
 
 class GdnDims(C.Structure):
@@ -115,6 +115,7 @@ KERNEL_API = {
     "q38_bq_dequant": (C.c_int, [C.POINTER(BQWeight), C.c_void_p, C.c_void_p]),
     "q38_embed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "q38_residual_update": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "q38_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "q38_qk_norm_rope_append": (C.c_int, [C.POINTER(QkNormRopeParams), C.POINTER(BatchDesc), C.POINTER(KvCacheDesc),
                                           C.c_void_p]),
     "q38_attention_decode_splits": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),

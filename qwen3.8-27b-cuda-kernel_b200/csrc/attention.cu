@@ -6,6 +6,7 @@
 // reference (src/kernels/kernels.h:140-179; src/kernels/qk_norm_rope.cu, attention_decode.cu,
 // attention_prefill.cu). Page layout per (layer, page): K [kv_head][64][256], V same, then (int8) fp16
 // scales K [kv_head][64][4], V same (reference docs/FORMAT.md 3.1).
+#include <algorithm>
 #include <cmath>
 
 #include "common.cuh"
@@ -589,6 +590,315 @@ __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Chunked-prefill attention over int8 pages, query-tiled (flash attention 2 on the tensor cores).
+// Replaces the reference's attention_prefill kernel (src/kernels/attention_prefill.cu:154-313) for int8 KV.
+//
+// One CTA per (KV split, kv head, tile of `tq` consecutive prompt tokens of one sequence). The tile's rows are its
+// (token, query head of the kv head's group) pairs, at most 64 = four warps of 16 rows; a fifth warp's lane streams
+// the (page, kv head) blocks of the keys the tile may see (causal: positions 0 .. last token of the tile) through
+// a two-stage shared-memory ring with the same four bulk copies per page as the decode kernel. Every K / V byte is
+// fetched once per tile instead of once per prompt token and query row.
+// Per 32-key half page a warp computes S = Q K^T with m16n8k16 f16 MMAs: Q rows are the A operand (fp16, staged in
+// shared memory once per tile), the keys are the B operand, dequantised in registers to fp16(int8) * fp16(scale)
+// (the rounding of the reference's prefill kernel); the dims of a k-step are permuted as in the decode kernel so a
+// lane reads 16 contiguous bytes per key. Online softmax in the log2 domain on the accumulator fragments (the
+// O accumulator is rescaled only when a row maximum of the warp moved), then O += P V with P as the A operand -
+// multiplied per 64-dim group by the V scales of its keys - and V's int8 bytes, two keys of one dim per register,
+// as exact fp16 integers. Only blocks that reach past a row's position are masked; blocks entirely beyond the
+// warp's last position are skipped. A single split normalises, applies the sigmoid output gate and writes bf16;
+// with several splits the (O, m, l) states go to the scratch for attn_merge_kernel.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kPfWarps = 4;
+constexpr int kPfRows = kPfWarps * 16;
+constexpr int kPfThreads = (kPfWarps + 1) * 32;
+constexpr int kPfStages = 2;
+constexpr int kPfQStride = 2 * kHd + 8;        // bytes per staged fp16 query row (the pad spreads rows over banks)
+constexpr int kPfOStride = kHd + 4;            // floats per staged output row
+constexpr int kPfRingBytes = kPfStages * kStageBytes;
+static_assert(kPfRows * kPfOStride * 4 <= kPfRingBytes, "the output staging aliases the drained ring");
+constexpr int kPfSmem = kPfRingBytes + kPfRows * kPfQStride + 256;
+
+__global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
+    const __half* __restrict__ q, const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ out,
+    int nq, int group, int layer, int tq, int tiles_per_seq, float* __restrict__ scratch, int max_splits, int num_splits,
+    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0, KvView kv) {
+  pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
+  pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
+  extern __shared__ __align__(128) uint8_t dsm[];
+  uint8_t* qs = dsm + kPfRingBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(qs + kPfRows * kPfQStride);
+  uint64_t* empty = full + kPfStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kPfStages);
+  const int split = blockIdx.x, kvh = blockIdx.y;
+  const int b = blockIdx.z / tiles_per_seq, ti = blockIdx.z % tiles_per_seq;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int s_first = seq_start[b], n_seq = seq_start[b + 1] - s_first;
+  const int i0 = ti * tq;
+  if (i0 >= n_seq) return;                       // this sequence's chunk has fewer tiles
+  const int nt = min(tq, n_seq - i0);            // tokens of the tile
+  const int rows = nt * group;                   // (token, head) rows, <= 64
+  const int m0 = s_first + i0;                   // first token row of the tile in the step's arrays
+  const int pos0 = seq_pos0[b] + i0;             // its position; row r sees keys 0 .. pos0 + r / group
+  const int slot = seq_slot[b];
+  const int L = pos0 + nt;
+  const int pages = (L + kPage - 1) / kPage;
+  const int pages_per_split = (pages + num_splits - 1) / num_splits;
+  const int p0 = min(pages, split * pages_per_split), p1 = min(pages, (split + 1) * pages_per_split);
+  if (p0 >= p1) {  // (only with several splits) nothing to do here: empty states for the merge
+    for (int r = tid; r < rows; r += kPfThreads) {
+      float* dst = scratch + (((size_t)(m0 + r / group) * nq + (size_t)kvh * group + r % group) * max_splits + split) * (kHd + 2);
+      dst[kHd] = -INFINITY;
+      dst[kHd + 1] = 0.0f;
+    }
+    return;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kPfStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kPfWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  // stage the tile's query rows (fp16), zero rows beyond the tile
+  for (int i = tid; i < kPfRows * (kHd / 4); i += kPfThreads) {
+    const int r = i / (kHd / 4), c = i % (kHd / 4);
+    uint2 v = make_uint2(0u, 0u);
+    if (r < rows)
+      v = *reinterpret_cast<const uint2*>(q + ((size_t)(m0 + r / group) * nq + (size_t)kvh * group + r % group) * kHd + 4 * c);
+    *reinterpret_cast<uint2*>(qs + (size_t)r * kPfQStride + 8 * c) = v;
+  }
+  __syncthreads();
+
+  if (warp == kPfWarps) {
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_normal();  // the tiles of a chunk share their pages through L2
+      const int* table = kv.block_table + (size_t)slot * kv.max_pages_per_seq;
+      for (int p = p0, it = 0; p < p1; ++p, ++it) {
+        const int s = it % kPfStages;
+        if (*abort_flag || !mbar_wait(&empty[s], ((it / kPfStages) & 1) ^ 1, 0x221)) {
+          *abort_flag = 1;
+          break;
+        }
+        const int page = table[p];
+        if (page < 0 || page >= kv.num_pages) {
+          report_error(0x222);
+          *abort_flag = 1;
+          break;
+        }
+        const uint8_t* base = kv.pool + (size_t)layer * kv.layer_stride + (size_t)page * kv.page_bytes;
+        uint8_t* st = dsm + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full[s], 2 * 16384 + 2 * 512);
+        bulk_g2s(st + kStageK, base + kv.k_off(kvh, 0), 16384, &full[s], pol);
+        bulk_g2s(st + kStageV, base + kv.v_off(kvh, 0), 16384, &full[s], pol);
+        bulk_g2s(st + kStageKs, base + kv.ks_off(kvh, 0), 512, &full[s], pol);
+        bulk_g2s(st + kStageVs, base + kv.vs_off(kvh, 0), 512, &full[s], pol);
+      }
+    }
+    return;
+  }
+
+  const int g = lane >> 2, t = lane & 3;
+  const int ra = 16 * warp + g, rb = ra + 8;                   // this lane's two rows of the tile
+  const bool warp_live = 16 * warp < rows;
+  const int pos_a = ra < rows ? pos0 + ra / group : -1;        // last key position a row may see (-1: padding row)
+  const int pos_b = rb < rows ? pos0 + rb / group : -1;
+  const int warp_last = pos0 + (min(rows, 16 * warp + 16) - 1) / group;  // largest position among the warp's rows
+  const uint8_t* qa_ptr = qs + (size_t)ra * kPfQStride + 32 * t;
+  const uint8_t* qb_ptr = qs + (size_t)rb * kPfQStride + 32 * t;
+  float o[32][4];
+#pragma unroll
+  for (int T = 0; T < 32; ++T)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[T][c] = 0.0f;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;  // l: this lane's share of the row sums
+  constexpr float kScale = kLog2e / 16.0f;
+
+  for (int p = p0, it = 0; p < p1; ++p, ++it) {
+    const int s = it % kPfStages;
+    bool ok = !*abort_flag && mbar_wait(&full[s], (it / kPfStages) & 1, 0x223);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) *abort_flag = 1;
+    const uint8_t* st = dsm + (size_t)s * kStageBytes;
+#pragma unroll 1
+    for (int hb = 0; hb < 2; ++hb) {
+      const int kbase = p * kPage + 32 * hb;  // first key of this half page
+      if (!ok || !warp_live || kbase > warp_last) continue;
+      const uint8_t* Kb = st + kStageK + (size_t)(32 * hb) * kHd;
+      const uint8_t* Vb = st + kStageV + (size_t)(32 * hb) * kHd;
+      const __half* Ksc = reinterpret_cast<const __half*>(st + kStageKs) + 32 * hb * 4;
+      const __half* Vsc = reinterpret_cast<const __half*>(st + kStageVs) + 32 * hb * 4;
+      // ---- S = Q K^T: rows = this warp's 16 query rows, columns = 32 keys (4 n-tiles of 8) ----
+      float sacc[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sacc[j][c] = 0.0f;
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        uint32_t kw[4][4];
+        uint32_t ks2[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 kr = *reinterpret_cast<const uint4*>(Kb + (size_t)(8 * j + g) * kHd + 64 * grp + 16 * t);
+          kw[j][0] = kr.x ^ 0x80808080u;
+          kw[j][1] = kr.y ^ 0x80808080u;
+          kw[j][2] = kr.z ^ 0x80808080u;
+          kw[j][3] = kr.w ^ 0x80808080u;
+          const uint32_t h = __half_as_ushort(Ksc[(8 * j + g) * 4 + grp]);
+          ks2[j] = h | (h << 16);
+        }
+#pragma unroll
+        for (int ss = 0; ss < 4; ++ss) {
+          const uint2 qa = *reinterpret_cast<const uint2*>(qa_ptr + 128 * grp + 8 * ss);
+          const uint2 qb = *reinterpret_cast<const uint2*>(qb_ptr + 128 * grp + 8 * ss);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t lo = bytes_to_half2<0x4140>(kw[j][ss]), hi = bytes_to_half2<0x4342>(kw[j][ss]);
+            const __half2 sc = *reinterpret_cast<const __half2*>(&ks2[j]);
+            const __half2 b0 = __hmul2(*reinterpret_cast<const __half2*>(&lo), sc);
+            const __half2 b1 = __hmul2(*reinterpret_cast<const __half2*>(&hi), sc);
+            mma_f16_16816(sacc[j], qa.x, qb.x, qa.y, qb.y, *reinterpret_cast<const uint32_t*>(&b0),
+                          *reinterpret_cast<const uint32_t*>(&b1));
+          }
+        }
+      }
+      // ---- online softmax (log2 domain); keys beyond a row's position are masked ----
+      float bm_a = -INFINITY, bm_b = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int key = kbase + 8 * j + 2 * t + (c & 1);
+          const bool seen = key <= ((c & 2) ? pos_b : pos_a);
+          sacc[j][c] = seen ? sacc[j][c] * kScale : -INFINITY;
+          if (c & 2) bm_b = fmaxf(bm_b, sacc[j][c]);
+          else bm_a = fmaxf(bm_a, sacc[j][c]);
+        }
+      bm_a = fmaxf(bm_a, __shfl_xor_sync(0xffffffffu, bm_a, 1));
+      bm_a = fmaxf(bm_a, __shfl_xor_sync(0xffffffffu, bm_a, 2));
+      bm_b = fmaxf(bm_b, __shfl_xor_sync(0xffffffffu, bm_b, 1));
+      bm_b = fmaxf(bm_b, __shfl_xor_sync(0xffffffffu, bm_b, 2));
+      const float mn_a = fmaxf(m_a, bm_a), mn_b = fmaxf(m_b, bm_b);
+      const float ref_a = mn_a == -INFINITY ? 0.0f : mn_a, ref_b = mn_b == -INFINITY ? 0.0f : mn_b;  // no inf - inf
+      const float c_a = exp2f(m_a - ref_a), c_b = exp2f(m_b - ref_b);
+      float ps_a = 0.0f, ps_b = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sacc[j][0] = exp2f(sacc[j][0] - ref_a);
+        sacc[j][1] = exp2f(sacc[j][1] - ref_a);
+        sacc[j][2] = exp2f(sacc[j][2] - ref_b);
+        sacc[j][3] = exp2f(sacc[j][3] - ref_b);
+        ps_a += sacc[j][0] + sacc[j][1];
+        ps_b += sacc[j][2] + sacc[j][3];
+      }
+      l_a = l_a * c_a + ps_a;
+      l_b = l_b * c_b + ps_b;
+      const bool moved = (m_a != mn_a) || (m_b != mn_b);
+      m_a = mn_a;
+      m_b = mn_b;
+      if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+        for (int T = 0; T < 32; ++T) {
+          o[T][0] *= c_a;
+          o[T][1] *= c_a;
+          o[T][2] *= c_b;
+          o[T][3] *= c_b;
+        }
+      }
+      // ---- O += P V: 2 k-steps of 16 keys; P carries the V scale of its key and 64-dim group ----
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const uint2 v0 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t) * 4);
+        const uint2 v1 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t + 1) * 4);
+        const uint2 v2 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t + 8) * 4);
+        const uint2 v3 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t + 9) * 4);
+        const uint32_t sw0[2] = {v0.x, v0.y}, sw1[2] = {v1.x, v1.y}, sw2[2] = {v2.x, v2.y}, sw3[2] = {v3.x, v3.y};
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+          const int sh = 16 * (grp & 1);
+          const float f0 = __half2float(__ushort_as_half((unsigned short)(sw0[grp >> 1] >> sh)));
+          const float f1 = __half2float(__ushort_as_half((unsigned short)(sw1[grp >> 1] >> sh)));
+          const float f2 = __half2float(__ushort_as_half((unsigned short)(sw2[grp >> 1] >> sh)));
+          const float f3 = __half2float(__ushort_as_half((unsigned short)(sw3[grp >> 1] >> sh)));
+          const __half2 a0 = __floats2half2_rn(sacc[2 * kk][0] * f0, sacc[2 * kk][1] * f1);
+          const __half2 a1 = __floats2half2_rn(sacc[2 * kk][2] * f0, sacc[2 * kk][3] * f1);
+          const __half2 a2 = __floats2half2_rn(sacc[2 * kk + 1][0] * f2, sacc[2 * kk + 1][1] * f3);
+          const __half2 a3 = __floats2half2_rn(sacc[2 * kk + 1][2] * f2, sacc[2 * kk + 1][3] * f3);
+          const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&a0), pa1 = *reinterpret_cast<const uint32_t*>(&a1);
+          const uint32_t pa2 = *reinterpret_cast<const uint32_t*>(&a2), pa3 = *reinterpret_cast<const uint32_t*>(&a3);
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const int J = 2 * grp + jj;  // 32-dim group: n-tile 4 J + I holds dims 32 J + 4 n + I, n = 0..7
+            const uint8_t* vp = Vb + (size_t)(16 * kk) * kHd + 32 * J + 4 * g;
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vp + (2 * t) * kHd) ^ 0x80808080u;
+            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 1) * kHd) ^ 0x80808080u;
+            const uint32_t w2 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 8) * kHd) ^ 0x80808080u;
+            const uint32_t w3 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 9) * kHd) ^ 0x80808080u;
+            mma_f16_16816(o[4 * J + 0], pa0, pa1, pa2, pa3, byte_pair_to_half2<0>(w0, w1), byte_pair_to_half2<0>(w2, w3));
+            mma_f16_16816(o[4 * J + 1], pa0, pa1, pa2, pa3, byte_pair_to_half2<1>(w0, w1), byte_pair_to_half2<1>(w2, w3));
+            mma_f16_16816(o[4 * J + 2], pa0, pa1, pa2, pa3, byte_pair_to_half2<2>(w0, w1), byte_pair_to_half2<2>(w2, w3));
+            mma_f16_16816(o[4 * J + 3], pa0, pa1, pa2, pa3, byte_pair_to_half2<3>(w0, w1), byte_pair_to_half2<3>(w2, w3));
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+
+  // ---- finish: row sums across the four lanes of a row, then through shared memory (the drained ring) for
+  //      coalesced gate reads and stores ----
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  named_bar_sync(1, kPfWarps * 32);  // every warp is through with the ring
+  float* os = reinterpret_cast<float*>(dsm);
+  const float inv_a = (num_splits == 1 && l_a > 0.0f) ? 1.0f / l_a : 1.0f;
+  const float inv_b = (num_splits == 1 && l_b > 0.0f) ? 1.0f / l_b : 1.0f;
+#pragma unroll
+  for (int T = 0; T < 32; ++T) {
+    const int dim = 32 * (T >> 2) + 8 * t + (T & 3);  // column 2 t of n-tile T; column 2 t + 1 is 4 dims further
+    os[(size_t)ra * kPfOStride + dim] = o[T][0] * inv_a;
+    os[(size_t)ra * kPfOStride + dim + 4] = o[T][1] * inv_a;
+    os[(size_t)rb * kPfOStride + dim] = o[T][2] * inv_b;
+    os[(size_t)rb * kPfOStride + dim + 4] = o[T][3] * inv_b;
+  }
+  __syncwarp();
+  for (int rr = 0; rr < 16; ++rr) {
+    const int r = 16 * warp + rr;
+    if (r >= rows) break;
+    const int m = m0 + r / group, qh = kvh * group + r % group;
+    const float4 x0 = *reinterpret_cast<const float4*>(os + (size_t)r * kPfOStride + 8 * lane);
+    const float4 x1 = *reinterpret_cast<const float4*>(os + (size_t)r * kPfOStride + 8 * lane + 4);
+    const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    if (num_splits == 1) {
+      const uint4 graw = *reinterpret_cast<const uint4*>(gate + (size_t)m * ld_gate + (size_t)qh * kHd + 8 * lane);
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&graw);
+      __nv_bfloat162 res[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        res[i] = __floats2bfloat162_rn(x[2 * i] * sigmoid_f(__low2float(gp[i])), x[2 * i + 1] * sigmoid_f(__high2float(gp[i])));
+      *reinterpret_cast<uint4*>(out + (size_t)m * nq * kHd + (size_t)qh * kHd + 8 * lane) = *reinterpret_cast<uint4*>(res);
+    } else {
+      float* dst = scratch + (((size_t)m * nq + qh) * max_splits + split) * (kHd + 2);
+      *reinterpret_cast<float2*>(dst + 8 * lane) = make_float2(x[0], x[1]);
+      *reinterpret_cast<float2*>(dst + 8 * lane + 2) = make_float2(x[2], x[3]);
+      *reinterpret_cast<float2*>(dst + 8 * lane + 4) = make_float2(x[4], x[5]);
+      *reinterpret_cast<float2*>(dst + 8 * lane + 6) = make_float2(x[6], x[7]);
+      // the row's (m, l) sit in the lanes that own it: rows 16 w + g (first half) and + 8 (second half)
+      const float mr = __shfl_sync(0xffffffffu, rr < 8 ? m_a : m_b, 4 * (rr & 7));
+      const float lr = __shfl_sync(0xffffffffu, rr < 8 ? l_a : l_b, 4 * (rr & 7));
+      if (lane == 0) {
+        dst[kHd] = mr;
+        dst[kHd + 1] = lr;
+      }
+    }
+  }
+}
+
 // Merge of the splits + normalisation + sigmoid gate -> bf16 (reference attention_decode.cu:241-257).
 __global__ void __launch_bounds__(kHd) attn_merge_kernel(const float* __restrict__ scratch, int max_splits,
                                                          int num_splits, const __nv_bfloat16* __restrict__ gate,
@@ -597,7 +907,7 @@ __global__ void __launch_bounds__(kHd) attn_merge_kernel(const float* __restrict
   pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
   pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   const int qh = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
-  const int m = seq_start[row];
+  const int m = seq_start ? seq_start[row] : row;  // decode: a sequence's token row; prefill tiles: the token row itself
   const float* base = scratch + ((size_t)row * nq + qh) * max_splits * (kHd + 2);
   float mm = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, base[(size_t)s * (kHd + 2) + kHd]);
@@ -744,8 +1054,37 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
   if (batch->num_tokens == 0) return Q38_OK;
   const int group = p->num_q_heads / p->num_kv_heads;
   if (kv->dtype != Q38_KV_INT8) return dispatch_group(group, *p, *batch, *kv, false, 1, as_stream(stream));
-  // int8 KV: the tensor-core kernel, one CTA per (kv head, prompt token); neighbouring tokens walk the same pages, so
-  // all but the first reader of a page are served by L2
+  if (batch->max_tokens_per_seq > 1 && group >= 1 && group <= kPfRows) {
+    // chunks of more than one token: the query-tiled kernel. With few tiles for the GPU (one long request, or a
+    // tensor-parallel rank with one kv head) the keys are cut over several CTAs per tile when the caller's scratch
+    // (laid out [token][q head][max_splits][258]) allows it.
+    static const cudaError_t attr_pf =
+        cudaFuncSetAttribute(attn_prefill_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
+    Q38_CUDA_OK(attr_pf);
+    const int tq = kPfRows / group;
+    const int tiles_per_seq = (batch->max_tokens_per_seq + tq - 1) / tq;
+    const int tiles = (batch->num_tokens + tq - 1) / tq + batch->num_seqs;  // upper bound of the live tiles
+    int splits = 1;
+    if (p->split_scratch && p->max_splits > 1 && p->scratch_rows >= batch->num_tokens) {
+      splits = (2 * num_sms()) / std::max(1, tiles * p->num_kv_heads);
+      splits = std::max(1, std::min(splits, std::min(p->max_splits, 16)));
+    }
+    const cudaStream_t s = as_stream(stream);
+    const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p->gate);
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p->out);
+    (void)launch_kernel(attn_prefill_tile_kernel, dim3(splits, p->num_kv_heads, batch->num_seqs * tiles_per_seq),
+                        dim3(kPfThreads), kPfSmem, s, reinterpret_cast<const __half*>(p->q), gate, p->ld_gate, out,
+                        p->num_q_heads, group, p->attn_layer, tq, tiles_per_seq, p->split_scratch, p->max_splits, splits,
+                        batch->seq_start, batch->seq_slot, batch->seq_pos0, make_view(*kv));
+    Q38_LAUNCH_OK("attn_prefill_tile_kernel");
+    if (splits > 1) {
+      (void)launch_kernel(attn_merge_kernel, dim3(p->num_q_heads, batch->num_tokens), dim3(kHd), 0, s, p->split_scratch,
+                          p->max_splits, splits, gate, p->ld_gate, out, p->num_q_heads, static_cast<const int*>(nullptr));
+      Q38_LAUNCH_OK("attn_merge_kernel");
+    }
+    return Q38_OK;
+  }
+  // single-token chunks: the decode kernel, one CTA per (kv head, token)
   Q38_REQUIRE(group >= 1 && group <= 8, "attention: GQA group %d is not implemented (1..8)", group);
   static const cudaError_t attr =
       cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);

@@ -429,7 +429,39 @@ unsigned int* misc_error_address() { return tu_error_address(); }
 
 }  // namespace q38
 
+namespace q38 {
+namespace {
+// Rows `rows[i]` of the step's normalised-input arrays (bf16 hidden row + its norm partial sums) packed into
+// rows i = 0..n-1: the LM-head input of the sequences that sample in a ragged step.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const float* __restrict__ partials,
+                                                          const int* __restrict__ rows, int hidden, int blocks,
+                                                          __nv_bfloat16* __restrict__ x_out,
+                                                          float* __restrict__ partials_out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x, src = rows[i];
+  const uint4* from = reinterpret_cast<const uint4*>(x + (size_t)src * hidden);
+  uint4* to = reinterpret_cast<uint4*>(x_out + (size_t)i * hidden);
+  for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) to[c] = from[c];
+  for (int c = threadIdx.x; c < blocks; c += blockDim.x) partials_out[(size_t)i * blocks + c] = partials[(size_t)src * blocks + c];
+}
+}  // namespace
+}  // namespace q38
+
 using namespace q38;
+
+extern "C" int q38_gather_rows(const q38_bf16* x, const float* partials, const int* rows, int n, int hidden,
+                               q38_bf16* x_out, float* partials_out, void* stream) {
+  if (n == 0) return Q38_OK;
+  Q38_REQUIRE(x && partials && rows && x_out && partials_out, "gather_rows: null argument");
+  Q38_REQUIRE(n > 0 && hidden > 0 && hidden % 128 == 0, "gather_rows: n %d hidden %d", n, hidden);
+  (void)launch_kernel(gather_rows_kernel, dim3(n), dim3(256), 0, as_stream(stream),
+                      reinterpret_cast<const __nv_bfloat16*>(x), partials, rows, hidden, hidden / 128,
+                      reinterpret_cast<__nv_bfloat16*>(x_out), partials_out);
+  Q38_LAUNCH_OK("gather_rows_kernel");
+  return Q38_OK;
+}
 
 extern "C" int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, int hidden, float* residual,
                          q38_bf16* xbf, float* partials, void* stream) {

@@ -40,7 +40,7 @@ class PrefillRow(C.Structure):
 
 
 class EngineOptions(C.Structure):
-    _fields_ = [("runner", RunnerOptions), ("seed", C.c_uint64), ("ragged_prefill", C.c_int)]
+    _fields_ = [("runner", RunnerOptions), ("seed", C.c_uint64), ("ragged_prefill", C.c_int), ("mixed_steps", C.c_int)]
 
 
 class Stats(C.Structure):
@@ -244,9 +244,9 @@ class Engine:
     REASONS = ("none", "stop", "length", "error")
 
     def __init__(self, model: Model, runner_options: RunnerOptions | None = None, seed: int = 0x5eed,
-                 ragged_prefill: bool = False):
+                 ragged_prefill: bool = False, mixed_steps: bool = False):
         self.model = model
-        o = EngineOptions(runner_options or default_runner_options(), seed, int(ragged_prefill))
+        o = EngineOptions(runner_options or default_runner_options(), seed, int(ragged_prefill), int(mixed_steps))
         self.h = C.c_void_p()
         _ok(lib().q38e_engine_create(model.h, C.byref(o), C.byref(self.h)))
         rh = C.c_void_p()

@@ -158,9 +158,11 @@ struct AttentionParams {
   int num_q_heads = 0, num_kv_heads = 0, attn_layer = 0;
   float* split_scratch = nullptr;
   int max_splits = 0;
+  int scratch_rows = 0;  // extension: rows the scratch holds (prefill may split its keys if >= the step's tokens)
   q38_attention_params c() const {
     return {reinterpret_cast<const q38_f16*>(q), reinterpret_cast<const q38_bf16*>(gate), ld_gate,
-            reinterpret_cast<q38_bf16*>(out), num_q_heads, num_kv_heads, attn_layer, split_scratch, max_splits};
+            reinterpret_cast<q38_bf16*>(out), num_q_heads, num_kv_heads, attn_layer, split_scratch, max_splits,
+            scratch_rows};
   }
 };
 inline int attention_decode_splits(int batch_seqs, int kv_heads, int num_sms, int max_splits) {
@@ -270,6 +272,13 @@ inline void target_logprobs(const float* logits, int ld, int vocab, const int32_
 inline void pack_ragged(const int* seq_count, const int* seq_pos0, int num_seqs, int num_tokens, int* seq_start,
                         int* tok_pos, int* tok_seq, cudaStream_t stream) {
   detail::ok(q38_pack_ragged(seq_count, seq_pos0, num_seqs, num_tokens, seq_start, tok_pos, tok_seq, stream));
+}
+
+// Extension: LM-head input rows of a ragged step packed by one kernel (see q38_gather_rows).
+inline void gather_rows(const __nv_bfloat16* x, const float* partials, const int* rows, int n, int hidden,
+                        __nv_bfloat16* x_out, float* partials_out, cudaStream_t stream) {
+  detail::ok(q38_gather_rows(reinterpret_cast<const q38_bf16*>(x), partials, rows, n, hidden,
+                             reinterpret_cast<q38_bf16*>(x_out), partials_out, stream));
 }
 
 // Extension: the library's device error status as a node of the step (see q38_device_error_collect).

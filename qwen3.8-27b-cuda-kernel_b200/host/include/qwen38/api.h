@@ -535,6 +535,10 @@ struct EngineOptions {
   // Extension: let one scheduler iteration prefill chunks of several waiting prompts together (one ragged
   // step of at most prefill_chunk tokens) instead of one sequence's chunk. Off = reference behaviour.
   bool ragged_prefill = false;
+  // Extension: while prompts are being prefilled, the generating sequences' next tokens ride in the same ragged step
+  // as the prefill chunk (one pass over the weights instead of a prefill step followed by a decode step; the single
+  // tokens count against the step's prefill_chunk token budget). Off = reference behaviour.
+  bool mixed_steps = false;
 };
 
 struct EngineStats {

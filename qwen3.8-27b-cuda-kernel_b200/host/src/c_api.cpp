@@ -243,6 +243,7 @@ int q38e_engine_create(const q38e_model* m, const q38e_engine_options* o, q38e_e
     eo.runner = from_c(o->runner);
     eo.seed = o->seed;
     eo.ragged_prefill = o->ragged_prefill != 0;
+    eo.mixed_steps = o->mixed_steps != 0;
     auto h = std::make_unique<q38e_engine>();
     h->e = std::make_unique<Engine>(*m->file, eo);
     h->runner_view.r = &h->e->runner();

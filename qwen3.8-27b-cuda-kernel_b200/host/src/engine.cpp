@@ -1,7 +1,7 @@
 // Engine: FIFO admission with whole-sequence KV reservation, then per scheduler iteration at most one
 // prefill step and one batched decode step. Scheduling rules, stop conditions, error results and the
 // statistics follow the reference (src/engine.cpp:19-194); `ragged_prefill` additionally lets the prefill
-// step carry chunks of several prompts.
+// step carry chunks of several prompts, `mixed_steps` lets it carry the generating sequences' tokens as well.
 #include <algorithm>
 
 #include "qwen38/api.h"
@@ -133,15 +133,45 @@ bool Engine::step() {
   if (active_.empty()) return !waiting_.empty();
   const int chunk = runner_->options().prefill_chunk;
 
+  // Rows of the decode step: every generating sequence with a sampled token to consume (up to the batch capacity).
+  std::vector<DecodeRow> drows;
+  std::vector<Sequence*> downers;
+  auto collect_decode_rows = [&] {
+    drows.clear();
+    downers.clear();
+    for (auto& sp : active_) {
+      Sequence& s = *sp;
+      if (!s.generating() || s.pending < 0 || int(drows.size()) == runner_->num_slots()) continue;
+      DecodeRow r;
+      r.slot = s.slot;
+      r.position = s.position;
+      r.token = s.pending;
+      r.sampling = s.config.sampling;
+      r.step = s.samples;
+      drows.push_back(r);
+      downers.push_back(&s);
+    }
+  };
+  bool prompts_pending = false;
+  for (auto& sp : active_) prompts_pending = prompts_pending || !sp->generating();
+  // A mixed step carries the decode rows inside the prefill step; it needs room for them and for at least as many
+  // prompt tokens again (otherwise the two separate steps serve the prompts better).
+  bool mixed = false;
+  if (opt_.mixed_steps && prompts_pending) {
+    collect_decode_rows();
+    mixed = !drows.empty() && 2 * int(drows.size()) <= chunk;
+  }
+
   // 1) one prefill step: the oldest unfinished prompt's next chunk (plus, with ragged_prefill, chunks of
-  //    the following prompts while the token budget lasts)
+  //    the following prompts while the token budget lasts; plus, in a mixed step, the decode rows)
   {
     std::vector<PrefillRow> rows;
     std::vector<Sequence*> owners;
-    int budget = chunk;
+    int budget = chunk - (mixed ? int(drows.size()) : 0);
     for (auto& sp : active_) {
       Sequence& s = *sp;
       if (s.generating() || budget <= 0) continue;
+      if (int(rows.size()) + (mixed ? int(drows.size()) : 0) >= runner_->num_slots()) break;
       const int prompt = int(s.result.prompt.size());
       const int n = std::min(budget, prompt - s.prefilled);
       PrefillRow r;
@@ -154,6 +184,24 @@ bool Engine::step() {
       owners.push_back(&s);
       budget -= n;
       if (!opt_.ragged_prefill) break;
+    }
+    const size_t prompt_rows = rows.size();
+    std::vector<int32_t> pending_tokens;  // storage the decode rows' one-token spans point into
+    if (mixed && prompt_rows > 0) {
+      pending_tokens.reserve(drows.size());
+      for (size_t i = 0; i < drows.size(); ++i) {
+        pending_tokens.push_back(drows[i].token);
+        PrefillRow r;
+        r.slot = drows[i].slot;
+        r.pos0 = drows[i].position;
+        r.tokens = std::span<const int32_t>(pending_tokens.data() + i, 1);
+        r.sample = &downers[i]->config.sampling;
+        r.step = drows[i].step;
+        rows.push_back(r);
+        owners.push_back(downers[i]);
+      }
+    } else {
+      mixed = false;
     }
     if (!rows.empty()) {
       const double t = now();
@@ -171,34 +219,32 @@ bool Engine::step() {
       size_t sampled = 0;
       for (size_t i = 0; step_ok && i < rows.size(); ++i) {
         Sequence& s = *owners[i];
-        const int n = int(rows[i].tokens.size());
-        stats_.prefill_tokens += n;
-        s.prefilled += n;
-        s.position = s.prefilled;
+        if (i < prompt_rows) {
+          const int n = int(rows[i].tokens.size());
+          stats_.prefill_tokens += n;
+          s.prefilled += n;
+          s.position = s.prefilled;
+        } else {
+          s.position += 1;  // the consumed token now sits in the cache
+        }
         if (rows[i].sample) {
           deliver(s, res.tokens[sampled], res.logprobs[sampled]);
           ++sampled;
         }
       }
+      if (step_ok && mixed) {
+        stats_.decode_tokens += int64_t(drows.size());
+        ++stats_.decode_steps;
+      }
       drop_finished();
     }
   }
+  if (mixed) return true;
 
   // 2) one decode step over every generating sequence (up to the batch capacity)
-  std::vector<DecodeRow> rows;
-  std::vector<Sequence*> owners;
-  for (auto& sp : active_) {
-    Sequence& s = *sp;
-    if (!s.generating() || s.pending < 0 || int(rows.size()) == runner_->num_slots()) continue;
-    DecodeRow r;
-    r.slot = s.slot;
-    r.position = s.position;
-    r.token = s.pending;
-    r.sampling = s.config.sampling;
-    r.step = s.samples;
-    rows.push_back(r);
-    owners.push_back(&s);
-  }
+  collect_decode_rows();
+  const std::vector<DecodeRow>& rows = drows;
+  const std::vector<Sequence*>& owners = downers;
   if (!rows.empty()) {
     const double t = now();
     StepResult res;

@@ -35,7 +35,7 @@ int bucket_for(int n, int max_batch) {
 // Byte offsets of the step metadata block. The first part is written by the host and uploaded with one
 // copy; the second part is produced on the device by the packing kernel.
 struct MetaMap {
-  size_t tokens = 0, seq_count = 0, seq_pos0 = 0, seq_slot = 0, row_slot = 0, step = 0, params = 0;
+  size_t tokens = 0, seq_count = 0, seq_pos0 = 0, seq_slot = 0, row_slot = 0, step = 0, params = 0, sample_row = 0;
   size_t host_bytes = 0;
   size_t seq_start = 0, tok_pos = 0, tok_seq = 0;
   size_t bytes = 0;
@@ -54,6 +54,7 @@ struct MetaMap {
     row_slot = take(size_t(max_rows) * 4);
     step = take(size_t(max_rows) * 4);
     params = take(size_t(max_rows) * sizeof(kernels::SamplingParamsDev));
+    sample_row = take(size_t(max_rows) * 4);
     host_bytes = at;
     seq_start = take(size_t(max_rows + 1) * 4);
     tok_pos = take(size_t(max_tokens) * 4);
@@ -168,6 +169,20 @@ struct ModelRunner::Impl {
     return b;
   }
 
+  // The sequences [first_seq, first_seq + seqs) of the step as a batch of their own. Their token rows stay where they
+  // are in the step's arrays (seq_start keeps absolute rows), so the kernels that walk a batch by sequence - attention,
+  // the GDN recurrence - can serve the chunk rows and the single-token rows of a mixed step with the kernel that
+  // suits each, while embed, the GEMMs, q/k-norm and the conv run once over all tokens.
+  kernels::BatchDesc sub_batch(int first_seq, int first_token, int seqs, int tokens, int max_per_seq) const {
+    kernels::BatchDesc b = batch_desc(seqs, tokens, max_per_seq);
+    b.seq_start += first_seq;
+    b.seq_slot += first_seq;
+    b.seq_pos0 += first_seq;
+    b.tok_pos += first_token;
+    b.tok_seq += first_token;
+    return b;
+  }
+
   void mark(const char* name) {
     if (!profiling) return;
     auto ev = std::make_unique<Event>(true);
@@ -202,7 +217,10 @@ struct ModelRunner::Impl {
     *word = 0;
     throw DeviceStepError(code, where);
   }
-  void forward(int m, const kernels::BatchDesc& batch, bool decode);
+  // multi_seqs / multi_tokens: the leading sequences of the batch that bring more than one token, and their tokens;
+  // the rest of the batch are single-token rows (a pure decode step has multi_seqs == 0, a pure prefill step none of
+  // the latter)
+  void forward(int m, const kernels::BatchDesc& batch, bool decode, int multi_seqs = -1, int multi_tokens = 0);
   void lm_head(const __nv_bfloat16* x, const float* part, int rows);
   void run_sampler(int rows);
   void download(int rows) {
@@ -341,8 +359,17 @@ void ModelRunner::Impl::setup() {
 }
 
 // The kernel sequence of one step over m tokens (reference src/model_runner.cpp:292-410).
-void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool decode) {
+void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool decode, int multi_seqs, int multi_tokens) {
   cudaStream_t s = stream.get();
+  if (multi_seqs < 0 || multi_seqs >= batch.num_seqs) {  // not a mixed step
+    multi_seqs = decode ? 0 : batch.num_seqs;
+    multi_tokens = decode ? 0 : m;
+  }
+  const int single_seqs = batch.num_seqs - multi_seqs;  // rows of one token each, placed after the chunk rows
+  const bool mixed = multi_seqs > 0 && single_seqs > 0;
+  const kernels::BatchDesc chunk_part = mixed ? sub_batch(0, 0, multi_seqs, multi_tokens, batch.max_tokens_per_seq) : batch;
+  const kernels::BatchDesc single_part =
+      mixed ? sub_batch(multi_seqs, multi_tokens, single_seqs, single_seqs, 1) : batch;
   const int H = cfg.hidden_size;
   const float eps = cfg.rms_norm_eps;
   const kernels::KvCacheDesc kvd = kv->desc();
@@ -406,8 +433,19 @@ void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool dec
       ap.attn_layer = attn_i;
       ap.split_scratch = split;
       ap.max_splits = kMaxSplits;
-      if (decode) kernels::attention_decode(ap, batch, kvd, s);
-      else kernels::attention_prefill(ap, batch, kvd, s);
+      if (decode) {
+        kernels::attention_decode(ap, batch, kvd, s);
+      } else if (mixed) {
+        // chunk rows through the query-tiled kernel (no key split: the scratch serves the single-token rows), the
+        // single-token rows through split-KV flash decoding
+        kernels::attention_decode(ap, single_part, kvd, s);
+        ap.split_scratch = nullptr;
+        kernels::attention_prefill(ap, chunk_part, kvd, s);
+      } else {  // the scratch of max_rows x kMaxSplits states seen as one row per prompt token of this step
+        ap.max_splits = std::min(kMaxSplits, int(size_t(max_rows) * kMaxSplits / size_t(std::max(1, m))));
+        ap.scratch_rows = ap.max_splits > 1 ? m : 0;
+        kernels::attention_prefill(ap, batch, kvd, s);
+      }
       mark(decode ? "attn.decode" : "attn.prefill");
       ++attn_i;
     } else {
@@ -433,10 +471,11 @@ void ModelRunner::Impl::forward(int m, const kernels::BatchDesc& batch, bool dec
       rp.out = mixer;
       rp.gdn_layer = gdn_i;
       // runs of prefill length take the chunked form (token-parallel preparation + per-chunk state scan)
-      if (gdn_scratch && batch.max_tokens_per_seq >= kGdnChunkedMinRun)
-        kernels::gdn_recurrence_chunked(rp, gd, batch, sd, gdn_scratch, gdn_scratch_floats, s);
+      if (gdn_scratch && chunk_part.max_tokens_per_seq >= kGdnChunkedMinRun)
+        kernels::gdn_recurrence_chunked(rp, gd, chunk_part, sd, gdn_scratch, gdn_scratch_floats, s);
       else
-        kernels::gdn_recurrence(rp, gd, batch, sd, s);
+        kernels::gdn_recurrence(rp, gd, chunk_part, sd, s);
+      if (mixed) kernels::gdn_recurrence(rp, gd, single_part, sd, s);  // the state-streaming decode kernel
       mark("gdn.recurrence");
       ++gdn_i;
     }
@@ -540,53 +579,63 @@ StepResult ModelRunner::prefill_batch(std::span<const PrefillRow> rows) {
   Impl& I = *impl_;
   const int nseq = int(rows.size());
   QWEN38_CHECK(nseq > 0 && nseq <= I.opt.max_batch, "prefill: ", nseq, " sequences in one step (max ", I.opt.max_batch, ")");
+  // Order inside the step: rows that bring a chunk of several tokens first, single-token rows (a generating sequence's
+  // next token, or a one-token tail of a prompt) after them, each group in the caller's order. The forward pass then
+  // serves the two groups with the attention / recurrence kernel that suits each; results keep the caller's order.
+  std::vector<int> order;
+  order.reserve(size_t(nseq));
+  int multi_seqs = 0, multi_tokens = 0;
+  for (int pass = 0; pass < 2; ++pass)
+    for (int i = 0; i < nseq; ++i) {
+      const bool single = rows[size_t(i)].tokens.size() == 1;
+      if (single == (pass == 1)) order.push_back(i);
+    }
+  std::vector<int> last_token_row(size_t(nseq), 0);  // per caller row: the step's token row of its last token
   int total = 0, longest = 0, samples = 0;
-  for (int i = 0; i < nseq; ++i) {
+  for (int k = 0; k < nseq; ++k) {
+    const int i = order[size_t(k)];
     const PrefillRow& r = rows[size_t(i)];
     const int n = int(r.tokens.size());
     QWEN38_CHECK(n > 0, "prefill: empty chunk");
     QWEN38_CHECK(r.slot >= 0 && r.slot < I.opt.max_batch, "prefill: slot out of range");
     QWEN38_CHECK(I.kv->pages_of(r.slot) * kernels::kPageTokens >= r.pos0 + n, "prefill: KV pages not reserved");
     for (int j = 0; j < i; ++j) QWEN38_CHECK(rows[size_t(j)].slot != r.slot, "prefill: a slot appears twice in one step");
+    QWEN38_CHECK(total + n <= I.max_tokens, "prefill: step of more than ", I.max_tokens, " tokens");
     std::memcpy(I.hmeta<int32_t>(I.meta.tokens) + total, r.tokens.data(), size_t(n) * 4);
-    I.set_row(i, r.slot, r.pos0, n, 0, kGreedy);
+    I.set_row(k, r.slot, r.pos0, n, 0, kGreedy);
     total += n;
     longest = std::max(longest, n);
+    last_token_row[size_t(i)] = total - 1;
+    if (n > 1) {
+      ++multi_seqs;
+      multi_tokens += n;
+    }
   }
   QWEN38_CHECK(total <= I.opt.prefill_chunk, "prefill: chunk of ", total, " tokens (max ", I.opt.prefill_chunk, ")");
-  // sampler rows are compact: row j of the sampler = j-th sequence that asked for a sample
-  std::vector<int> sample_token_row;
-  {
-    int at = 0;
-    for (int i = 0; i < nseq; ++i) {
-      const PrefillRow& r = rows[size_t(i)];
-      at += int(r.tokens.size());
-      if (!r.sample) continue;
-      I.hmeta<int>(I.meta.row_slot)[samples] = r.slot;
-      I.hmeta<int>(I.meta.step)[samples] = r.step;
-      I.hmeta<kernels::SamplingParamsDev>(I.meta.params)[samples] = to_dev(*r.sample);
-      sample_token_row.push_back(at - 1);
-      ++samples;
-    }
+  // sampler rows are compact: row j of the sampler = j-th sequence (in the caller's order) that asked for a sample
+  for (int i = 0; i < nseq; ++i) {
+    const PrefillRow& r = rows[size_t(i)];
+    if (!r.sample) continue;
+    I.hmeta<int>(I.meta.row_slot)[samples] = r.slot;
+    I.hmeta<int>(I.meta.step)[samples] = r.step;
+    I.hmeta<kernels::SamplingParamsDev>(I.meta.params)[samples] = to_dev(*r.sample);
+    I.hmeta<int>(I.meta.sample_row)[samples] = last_token_row[size_t(i)];
+    ++samples;
   }
   cudaStream_t s = I.stream.get();
   I.kv->sync(s);
   I.upload_meta();
   I.t_begin.record(s);
   I.pack(nseq, total);
-  I.forward(total, I.batch_desc(nseq, total, longest), false);
+  I.forward(total, I.batch_desc(nseq, total, longest), false, multi_seqs, multi_tokens);
   StepResult result;
   if (samples > 0) {
     const int H = I.cfg.hidden_size, nb = I.cfg.norm_blocks();
     if (samples == 1) {
-      I.lm_head(I.xbf + size_t(sample_token_row[0]) * H, I.partials + size_t(sample_token_row[0]) * nb, 1);
+      const int row = I.hmeta<int>(I.meta.sample_row)[0];
+      I.lm_head(I.xbf + size_t(row) * H, I.partials + size_t(row) * nb, 1);
     } else {
-      for (int j = 0; j < samples; ++j) {
-        QWEN38_CUDA(cudaMemcpyAsync(I.lm_x + size_t(j) * H, I.xbf + size_t(sample_token_row[size_t(j)]) * H, size_t(H) * 2,
-                                    cudaMemcpyDeviceToDevice, s));
-        QWEN38_CUDA(cudaMemcpyAsync(I.lm_partials + size_t(j) * nb, I.partials + size_t(sample_token_row[size_t(j)]) * nb,
-                                    size_t(nb) * 4, cudaMemcpyDeviceToDevice, s));
-      }
+      kernels::gather_rows(I.xbf, I.partials, I.dmeta<int>(I.meta.sample_row), samples, H, I.lm_x, I.lm_partials, s);
       I.lm_head(I.lm_x, I.lm_partials, samples);
     }
     I.run_sampler(samples);

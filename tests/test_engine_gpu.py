@@ -203,8 +203,10 @@ def test_engine_batches_independent_sequences(gold):
         e.run()
         alone.append(e.take_finished()[0].tokens)
     e.close()
-    for ragged in (False, True):
-        e = eng.Engine(model, tiny_options(), ragged_prefill=ragged)
+    # mixed: the generating sequences' tokens ride in the prefill steps of the prompts still pending (prompts 17 and 64
+    # finish in the first step and decode inside the steps that prefill 65 and 130)
+    for ragged, mixed in ((False, False), (True, False), (True, True), (False, True)):
+        e = eng.Engine(model, tiny_options(), ragged_prefill=ragged, mixed_steps=mixed)
         for p in prompts:
             e.submit(p, eng.greedy(), max_new_tokens=32, ignore_eos=True)
         e.run()
@@ -229,7 +231,7 @@ def test_engine_batches_independent_sequences(gold):
                 prefix += 1
             gold_same += prefix
             assert prefix >= 1, "the first generated token must match the reference"
-        print(f"ragged={ragged}: batched vs alone {same}/{total}; common prefix with the reference tokens {gold_same}/128")
+        print(f"ragged={ragged} mixed={mixed}: batched vs alone {same}/{total}; common prefix with the reference tokens {gold_same}/128")
         assert same >= 0.9 * 128
         assert gold_same >= 0.5 * 128
         e.close()

@@ -287,9 +287,11 @@ def run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decod
     out = torch.empty((n, nq * 256), dtype=torch.bfloat16, device="cuda")
     qp = pkg.QkNormRopeParams(pkg.ptr(proj_dev), ld, pkg.ptr(qn_dev), pkg.ptr(kn_dev), 1e-6, 1e7, nq, nkv, pkg.ptr(q16), layer)
     pkg.check(K().q38_qk_norm_rope_append(C.byref(qp), C.byref(batch.desc), C.byref(pool.desc), None))
-    split = torch.empty(max(split_rows, batch.desc.num_seqs) * nq * 64 * 258, dtype=torch.float32, device="cuda")
+    scratch_rows = max(split_rows, batch.desc.num_seqs)
+    max_splits = 64 if scratch_rows <= 64 else 16
+    split = torch.empty(scratch_rows * nq * max_splits * 258, dtype=torch.float32, device="cuda")
     ap = pkg.AttentionParams(pkg.ptr(q16), pkg.ptr(proj_dev) + nq * 256 * 2, ld, pkg.ptr(out), nq, nkv, layer,
-                             pkg.ptr(split), 64)
+                             pkg.ptr(split), max_splits, scratch_rows)
     fn = K().q38_attention_decode if decode else K().q38_attention_prefill
     pkg.check(fn(C.byref(ap), C.byref(batch.desc), C.byref(pool.desc), None))
     sync_ok()
@@ -432,6 +434,50 @@ def test_attention_decode_16_sequences_up_to_32768():
         seen.k[:], seen.v[:] = kd, vd
         want = seen.attend(nq, q_got[s], proj[s, nq * 256:2 * nq * 256], c - 1)
         assert np.all(np.abs(out_got[s] - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())), (s, c)
+
+
+@pytest.mark.parametrize("nq,nkv,split_rows", [(24, 4, 4), (3, 1, 800)])
+def test_attention_prefill_ragged_chunks_at_long_prefixes(nq, nkv, split_rows):
+    """One ragged prefill step of three sequences: a 512-token chunk behind an 8,200-token prefix, a 200-token chunk
+    behind 300 tokens and a 65-token chunk at position 0 (query tiles that start inside a page, end inside a page and
+    span pages). 24 q / 4 kv heads is the 27B layer (ten tokens x six heads per tile); 3 q / 1 kv head is one rank of
+    the 8-way tensor-parallel layout, where the few tiles cut their keys over several CTAs and the merge kernel
+    finishes (the scratch is sized per token for it). The oracle attends over the cache as the kernel wrote it, on a
+    sample of the prompt tokens (every position of the short chunks, every 29th and the ends of the long one)."""
+    ld = 2 * nq * 256 + 2 * nkv * 256
+    r3 = np.random.default_rng(3)
+    qn = (1 + 0.2 * r3.standard_normal(256)).astype(np.float32)
+    kn = (1 + 0.2 * r3.standard_normal(256)).astype(np.float32)
+    qn_dev, kn_dev = torch.from_numpy(qn).cuda(), torch.from_numpy(kn).cuda()
+    prefix, chunk, slots, layer = [8200, 300, 0], [512, 200, 65], [2, 0, 1], 1
+    need = [(a + c + 63) // 64 for a, c in zip(prefix, chunk)]
+    pool = tl.KvPool(nkv, layers=2, num_pages=sum(need) + 3, slots=3, max_pages_per_seq=max(need), dtype=0)
+    perm = np.random.default_rng(5).permutation(sum(need) + 3).astype(np.int32)
+    used = 0
+    for s, pages in zip(slots, need):
+        pool.table[s, :pages] = torch.from_numpy(perm[used:used + pages]).cuda()
+        used += pages
+    gen = torch.Generator(device="cuda").manual_seed(44)
+    for s, a in zip(slots, prefix):
+        fill_kv_random(pool, layer, nq, nkv, s, a, qn_dev, kn_dev, gen)
+    n = sum(chunk)
+    proj = tl.bf16_round(np.random.default_rng(45).standard_normal((n, ld)))
+    batch = tl.Batch([(s, a, c) for s, a, c in zip(slots, prefix, chunk)])
+    q_got, out_got = run_attention_chunk(pool, layer, nq, nkv, proj, batch, qn_dev, kn_dev, decode=False,
+                                         split_rows=split_rows)
+    o = tl.oracle()
+    row0 = 0
+    for s, a, c in zip(slots, prefix, chunk):
+        kd, vd = pool.read_sequence(layer, s, a + c)
+        picks = sorted(set(range(c)) if c <= 200 else set(range(0, c, 29)) | {1, 63, 64, c - 2, c - 1})
+        for i in picks:
+            pos = a + i
+            seen = tl.OracleKv(o, nkv, pos + 1)
+            seen.k[:], seen.v[:] = kd[:, :pos + 1], vd[:, :pos + 1]
+            want = seen.attend(nq, q_got[row0 + i], proj[row0 + i, nq * 256:2 * nq * 256], pos)
+            got = out_got[row0 + i]
+            assert np.all(np.abs(got - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())), (s, i, pos)
+        row0 += c
 
 
 # ---------------------------------------------------------------------------------------------------
