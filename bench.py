@@ -211,44 +211,122 @@ def weight_macs():
     return {"pair": gdn + attn, "all_layers": 48 * gdn + 16 * attn, "lm_head": V * H}
 
 
-def run_trace(args, eng, model, rank, world, dist, config, barrier):
-    """The whole trace through the Engine (scheduler, ragged chunked prefill, CUDA-graph decode): requests are dealt
-    round-robin over the ranks, every rank offers its share at t = 0 and serves it with 64 slots."""
-    import torch
-    from q38b200 import sharding
-    reqs = sharding.shard_requests(sharding.trace_requests(args.trace, seed=11), rank, world)
-    rng = np.random.default_rng(SEED + rank)
-    B = args.batch
-    kv_tokens = B * (8192 + 1024 + 128)
-    e = eng.Engine(model, eng.default_runner_options(max_batch=B, prefill_chunk=512, kv_tokens=kv_tokens,
-                                                     max_context=args.max_context, verbose=int(rank == 0)),
-                   ragged_prefill=True)
+def serve_trace(eng, model, reqs, arrivals, batch, max_context, seed, mixed, verbose=0):
+    """One replica serves its requests as they arrive (arrival times in seconds from the start; None = all offered
+    at t = 0) through the Engine. Returns (wall seconds, finished results, engine stats)."""
+    kv_tokens = batch * (8192 + 1024 + 128)
+    e = eng.Engine(model, eng.default_runner_options(max_batch=batch, prefill_chunk=512, kv_tokens=kv_tokens,
+                                                     max_context=max_context, verbose=verbose),
+                   ragged_prefill=True, mixed_steps=mixed)
     g = eng.greedy()
-    for _, (plen, olen) in reqs:
-        e.submit(rng.integers(1000, 150000, size=plen).astype(np.int32), g, max_new_tokens=olen, ignore_eos=True)
-    barrier()
+    rng = np.random.default_rng(seed)
+    prompts = [rng.integers(1000, 150000, size=plen).astype(np.int32) for _, (plen, _) in reqs]
     t0 = time.perf_counter()
-    e.run()
-    torch.cuda.synchronize()
+    nxt = 0
+    while nxt < len(reqs) or not e.idle():
+        now = time.perf_counter() - t0
+        while nxt < len(reqs) and (arrivals is None or arrivals[nxt] <= now):
+            e.submit(prompts[nxt], g, max_new_tokens=reqs[nxt][1][1], ignore_eos=True)
+            nxt += 1
+        if e.idle():
+            time.sleep(min(0.002, max(0.0, arrivals[nxt] - now)))  # nothing to run until the next arrival
+            continue
+        e.step()
     wall = time.perf_counter() - t0
     done = e.take_finished()
     st = e.stats()
+    e.close()
+    return wall, done, st
+
+
+def run_trace(args, eng, model, rank, world, dist, config, barrier, num_requests=None, quiet=False):
+    """The trace through the Engine (scheduler, ragged chunked prefill, mixed prefill + decode steps, CUDA-graph decode):
+    requests arrive as a Poisson process of `--arrival-rate` requests per second and GPU (0 = all at t = 0), are dealt
+    round-robin over the ranks in arrival order, and every rank serves its share with 64 slots."""
+    import torch
+    from q38b200 import sharding
+    n = num_requests or args.trace
+    all_reqs = sharding.trace_requests(n, seed=11)
+    rate = args.arrival_rate * world
+    all_arr = sharding.poisson_arrivals(n, rate, seed=11) if rate > 0 else None
+    reqs = sharding.shard_requests(all_reqs, rank, world)
+    arrivals = [all_arr[i] for i, _ in reqs] if all_arr else None
+    barrier()
+    wall, done, st = serve_trace(eng, model, reqs, arrivals, args.batch, args.max_context, SEED + rank,
+                                 mixed=not args.no_mixed_steps, verbose=int(rank == 0 and not quiet))
+    torch.cuda.synchronize()
     prompt_tokens = sum(p for _, (p, _) in reqs)
     out_tokens = sum(len(f.tokens) for f in done)
     wall_max, = sharding.max_over_ranks([wall], dist, device="cuda")
     tot = torch.tensor([prompt_tokens, out_tokens, len(done)], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(tot)
-    if rank == 0:
-        print(json.dumps({
-            "metric": "trace_tok_per_s", "value": float(tot[0] + tot[1]) / wall_max, "unit": "tok/s (prompt + generated)",
-            "n_gpus": world, "requests": int(tot[2]), "wall_s": wall_max, "prompt_tokens": int(tot[0]),
-            "generated_tokens": int(tot[1]), "generated_tok_per_s": float(tot[1]) / wall_max,
-            "rank0_engine_stats": {"prefill_tokens": int(st.prefill_tokens), "prefill_s": st.prefill_s,
-                                   "decode_tokens": int(st.decode_tokens), "decode_s": st.decode_s,
-                                   "decode_steps": int(st.decode_steps)},
-            "scaling": "weak" if world == 1 else "strong", "data": "synthetic", "config": config}))
-    e.close()
+    lat = [f.times[2] - f.times[0] for f in done if len(f.times) == 3]
+    return {
+        "metric": "trace_tok_per_s", "value": float(tot[0] + tot[1]) / wall_max, "unit": "tok/s (prompt + generated)",
+        "n_gpus": world, "requests": int(tot[2]), "wall_s": wall_max, "prompt_tokens": int(tot[0]),
+        "generated_tokens": int(tot[1]), "generated_tok_per_s": float(tot[1]) / wall_max,
+        "arrivals": (f"Poisson, {rate:.2f} requests/s over the job ({args.arrival_rate:.2f} per GPU)" if rate > 0
+                     else "all offered at t = 0"),
+        "mixed_steps": not args.no_mixed_steps,
+        "rank0_mean_request_latency_s": float(np.mean(lat)) if lat else None,
+        "rank0_engine_stats": {"prefill_tokens": int(st.prefill_tokens), "prefill_s": st.prefill_s,
+                               "decode_tokens": int(st.decode_tokens), "decode_s": st.decode_s,
+                               "decode_steps": int(st.decode_steps)},
+        "scaling": "strong", "data": "synthetic", "config": config}
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU baselines of the per-kernel configurations (the reference's own CPU operations on bounded samples)
+# ----------------------------------------------------------------------------------------------------
+def cpu_reference_op_samples():
+    """Seconds of the reference's CPU code (oracle/_ref: qwen38-ref and the ref:: operations behind a C shim), one
+    core, on bounded samples of the per-kernel workloads: the tiny model end to end, one BQ GEMM row block, attention
+    over a cached context, Gated DeltaNet tokens. Reported beside the GPU numbers; not a target."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import q38_testlib as tl
+    out = {}
+    exe, ops = tl.reference_binary(), tl.reference_ops()
+    if exe is None or ops is None:
+        return {"unavailable": "oracle/_ref has not been built"}
+    td = Path(tempfile.mkdtemp())
+    tok = td / "t.i32"
+    np.random.default_rng(7).integers(0, 1000, size=130 + 32).astype("<i4").tofile(tok)
+    t = time.time()
+    subprocess.run([str(exe), "--model", str(ROOT / "tests" / "golden" / "tiny_cfg1.q38"), "--tokens", str(tok), "--out",
+                    str(td / "l.f32"), "--kv", "int8"], check=True, stderr=subprocess.DEVNULL)
+    out["config1_tiny_model_162_tokens_s"] = round(time.time() - t, 3)
+    rng = np.random.default_rng(1)
+    w = rng.standard_normal((256, 5120)).astype(np.float32) * 0.02
+    a = tl.bf16_round(rng.standard_normal((8, 5120)))
+    res = np.zeros((8, 256), np.float32)
+    t = time.time()
+    ops.qgemm(a, w, None, 3, out=res, ldo=256)
+    dt = time.time() - t
+    out["config2_qgemm_tflops_one_core"] = round(2.0 * 8 * 256 * 5120 / dt / 1e12, 6)
+    out["config2_sample"] = "ref::qgemm, 8 tokens x 256 of the 34816 gate/up columns x k 5120 (dequantised weights)"
+    kv = tl.OracleKv(ops, 4, 2048)
+    kv.k[:] = rng.standard_normal(kv.k.shape).astype(np.float32)
+    kv.v[:] = rng.standard_normal(kv.v.shape).astype(np.float32)
+    q, gate = rng.standard_normal(24 * 256).astype(np.float32), rng.standard_normal(24 * 256).astype(np.float32)
+    t = time.time()
+    kv.attend(24, q, gate, 2047)
+    dt = time.time() - t
+    out["config3_attention_context_tokens_per_s_one_core"] = round(2048 / dt, 1)
+    out["config3_sample"] = "ref::attention_token, one query token, 24 q / 4 kv heads over a 2048-token context"
+    lk, lv = 16, 48
+    conv_dim = 2 * lk * 128 + lv * 128
+    state, conv = np.zeros(lv * 128 * 128, np.float32), np.zeros(3 * conv_dim, np.float32)
+    args = (rng.standard_normal(conv_dim + lv * 128).astype(np.float32), rng.standard_normal(2 * lv).astype(np.float32),
+            (0.4 * rng.standard_normal((conv_dim, 4))).astype(np.float32), (-rng.uniform(0.5, 8, lv)).astype(np.float32),
+            (0.5 * rng.standard_normal(lv)).astype(np.float32), (1 + 0.2 * rng.standard_normal(128)).astype(np.float32))
+    t = time.time()
+    for _ in range(4):
+        ops.gdn_token(lk, lv, 1e-6, args[0], args[1], args[2], args[3], args[4], args[5], state, conv)
+    out["config4_gdn_tokens_per_s_one_core"] = round(4 / (time.time() - t), 2)
+    out["config4_sample"] = "ref::gdn_token, 4 tokens of one layer with 16 key / 48 value heads (128 x 128 states)"
+    out["cores"] = 1
+    return out
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -268,7 +346,14 @@ def main():
                     help="A/B aid: classic stream order instead of programmatic dependent launch")
     ap.add_argument("--trace", type=int, default=0, metavar="N",
                     help="run the continuous-batching trace instead (N requests, prompts log-uniform 64..8192, outputs "
-                         "uniform 64..1024, all offered at t = 0, 64 slots per GPU) through the Engine and report it")
+                         "uniform 64..1024, Poisson arrivals, 64 slots per GPU) through the Engine and report it")
+    ap.add_argument("--arrival-rate", type=float, default=4.0,
+                    help="trace: Poisson arrival rate in requests per second and GPU (one B200 finishes about 4.5 such "
+                         "requests per second, so the 64 slots stay occupied); 0 = all requests offered at t = 0")
+    ap.add_argument("--no-mixed-steps", action="store_true",
+                    help="trace: a prefill step and a separate decode step per iteration (the reference's schedule)")
+    ap.add_argument("--trace-slice", type=int, default=64,
+                    help="requests of the trace that the default run serves after the decode measurement (0 = none)")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: reserve the KV pages but leave them zero-filled (the line is then not a bench value)")
     args = ap.parse_args()
@@ -327,7 +412,9 @@ def main():
     model = eng.Model(model_path)
     B = args.batch
     if args.trace:
-        run_trace(args, eng, model, rank, world, dist, config, barrier)
+        res = run_trace(args, eng, model, rank, world, dist, config, barrier)
+        if rank == 0:
+            print(json.dumps(res))
         model.close()
         if dist is not None:
             dist.destroy_process_group()
@@ -460,9 +547,15 @@ def main():
         base = cpu_reference_sample(args.recipe)
         line["cpu_baseline"] = base if base else {"value": None, "unit": "tok/s", "cores": 0, "kind": "reference",
                                                   "sample": "oracle/_ref/qwen38-ref not built"}
+        line["cpu_baseline_kernel_configs"] = cpu_reference_op_samples()
+    runner.close()
+    if args.trace_slice > 0 and args.layers == 64:
+        # a bounded slice of the continuous-batching trace (Poisson arrivals, mixed steps) on every rank's own engine
+        tr = run_trace(args, eng, model, rank, world, dist, config, barrier, num_requests=args.trace_slice * world, quiet=True)
+        tr.pop("config", None)
+        line["trace_slice"] = tr
     if rank == 0:
         print(json.dumps(line))
-    runner.close()
     model.close()
     if dist is not None:
         dist.destroy_process_group()

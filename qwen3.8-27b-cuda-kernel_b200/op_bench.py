@@ -1,4 +1,4 @@
-"""Micro-benchmark of the two state-streaming decode kernels at the 27B geometry: paged int8 decode attention
+"""Micro-benchmark of the state-streaming decode kernels and of the prefill attention at the 27B geometry: paged int8 decode attention
 (24 q heads / 4 kv heads, head_dim 256, 64-token pages in a shuffled page table, contexts log-uniform in
 128..32768) and the Gated DeltaNet decode recurrence (48 value heads / 16 key heads, 128x128 fp32 state).
 
@@ -9,6 +9,9 @@ working set of either kernel is far larger than L2.
   python qwen3.8-27b-cuda-kernel_b200/op_bench.py                       # both kernels, 64 sequences
   python qwen3.8-27b-cuda-kernel_b200/op_bench.py --op attn --seqs 16 --launches 3 --untimed
       # a few plain launches and nothing else: the small case to put under a profiler
+  python qwen3.8-27b-cuda-kernel_b200/op_bench.py --op prefill --prefix 2048,32768,131072
+      # the query-tiled prefill attention: one 512-token chunk behind a cached prefix, for the 27B layer (24 q / 4 kv
+      # heads) and for one rank of the 8-way tensor-parallel layout (3 q / 1 kv head, keys cut over several CTAs)
 """
 
 from __future__ import annotations
@@ -102,6 +105,40 @@ def attn_case(pkg, seqs, seed):
     return launch, kv_bytes, (pool, table_d, keep, q, gate, out, scratch), f"{seqs} sequences, {int(ctx.sum())} context tokens"
 
 
+def prefill_case(pkg, prefix, chunk, seed, nq=NQ, nkv=NKV, split_rows=0):
+    """One sequence: a `chunk`-token prefill step behind `prefix` cached tokens (random int8 pages)."""
+    K = pkg.kernels()
+    rng = np.random.default_rng(seed)
+    total = prefix + chunk
+    pages = (total + PAGE - 1) // PAGE
+    page_bytes = int(K.q38_kv_page_bytes(pkg.KV_INT8, nkv))
+    pool = torch.randint(0, 256, ((pages + 1) * page_bytes,), dtype=torch.uint8, device="cuda")
+    pool.view(torch.int16).bitwise_and_(0x3BFF)
+    table_d = torch.from_numpy((rng.permutation(pages) + 1).astype(np.int32)[None, :]).cuda()
+    kv = pkg.KvCacheDesc(pkg.ptr(pool), pkg.KV_INT8, nkv, pages + 1, page_bytes, (pages + 1) * page_bytes,
+                         pkg.ptr(table_d), pages)
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    t = {"seq_start": mk([0, chunk]), "seq_slot": mk([0]), "seq_pos0": mk([prefix]),
+         "tok_pos": mk(list(range(prefix, total))), "tok_seq": mk([0] * chunk)}
+    desc = pkg.BatchDesc(1, chunk, chunk, pkg.ptr(t["seq_start"]), pkg.ptr(t["seq_slot"]), pkg.ptr(t["seq_pos0"]),
+                         pkg.ptr(t["tok_pos"]), pkg.ptr(t["tok_seq"]))
+    q = torch.randn((chunk, nq, HD), device="cuda").to(torch.float16)
+    gate = torch.randn((chunk, nq * HD), device="cuda").to(torch.bfloat16)
+    out = torch.empty((chunk, nq * HD), dtype=torch.bfloat16, device="cuda")
+    max_splits = 16
+    rows = max(split_rows, 1)
+    scratch = torch.empty(rows * nq * max_splits * (HD + 2), dtype=torch.float32, device="cuda")
+    ap = pkg.AttentionParams(pkg.ptr(q), pkg.ptr(gate), nq * HD, pkg.ptr(out), nq, nkv, 0, pkg.ptr(scratch), max_splits,
+                             split_rows)
+    keys_seen = chunk * prefix + chunk * (chunk + 1) // 2
+    flops = 4 * HD * nq * keys_seen
+
+    def launch(stream):
+        pkg.check(K.q38_attention_prefill(C.byref(ap), C.byref(desc), C.byref(kv), stream))
+    return launch, flops, (pool, table_d, t, q, gate, out, scratch), (f"{chunk}-token chunk behind {prefix} tokens, "
+                                                                     f"{nq} q / {nkv} kv heads")
+
+
 def gdn_case(pkg, seqs, seed):
     K = pkg.kernels()
     g = torch.Generator(device="cuda").manual_seed(seed)
@@ -130,7 +167,9 @@ def gdn_case(pkg, seqs, seed):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="attn,gdn", help="comma-separated: attn, gdn")
+    ap.add_argument("--op", default="attn,gdn", help="comma-separated: attn, gdn, prefill")
+    ap.add_argument("--prefix", default="2048,32768,131072", help="prefill: cached tokens before the chunk")
+    ap.add_argument("--chunk", type=int, default=512, help="prefill: tokens of the step")
     ap.add_argument("--seqs", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--launches", type=int, default=3, help="with --untimed: number of plain launches")
@@ -143,6 +182,22 @@ def main(argv=None):
     pkg = _package()
     K = pkg.kernels()
     for op in args.op.split(","):
+        if op == "prefill":  # flash prefill attention: TFLOP/s of the visible (query, key) pairs
+            for prefix in [int(x) for x in args.prefix.split(",")]:
+                for nq, nkv, rows in ((NQ, NKV, 0), (3, 1, args.chunk)):  # the 27B layer; one rank of 8-way tensor parallelism
+                    launch, flops, keep, what = prefill_case(pkg, prefix, args.chunk, args.seed, nq, nkv, rows)
+                    if args.untimed:
+                        for _ in range(args.launches):
+                            launch(None)
+                        torch.cuda.synchronize()
+                        print(f"ok: prefill: {args.launches} launches, {what}")
+                    else:
+                        us = timed_graph(launch, max(2, args.iters // 4))
+                        print(f"prefill {what}: {us:9.1f} us  {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
+                    del keep
+            if K.q38_device_error(1):
+                raise SystemExit("device-side wait gave up")
+            continue
         launch, nbytes, keep, what = (attn_case if op == "attn" else gdn_case)(pkg, args.seqs, args.seed)
         if args.untimed:
             for _ in range(args.launches):

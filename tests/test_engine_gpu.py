@@ -448,3 +448,27 @@ def test_a_device_error_word_fails_the_step_and_the_engine_carries_on():
     assert done[second].finish == "length" and len(done[second].tokens) == 8
     e.close()
     model.close()
+
+
+def test_more_requests_than_slots_are_queued_and_all_finish():
+    """Slot exhaustion: seven requests on an engine with two sequence slots. The scheduler admits them as slots and KV
+    pages come back; every request finishes with its full length, in mixed-step mode as well, and the tokens of each
+    request do not depend on what shared the batch with it."""
+    model = eng.Model(GOLD / "tiny_cfg1_unit.q38")
+    rng = np.random.default_rng(12)
+    prompts = [rng.integers(0, 1000, size=int(n)).astype(np.int32) for n in (5, 70, 33, 129, 64, 9, 200)]
+    outs = {}
+    for mixed in (False, True):
+        e = eng.Engine(model, tiny_options(max_batch=2, kv_tokens=64 * 12), ragged_prefill=True, mixed_steps=mixed)
+        ids = [e.submit(p, eng.greedy(), max_new_tokens=12, ignore_eos=True) for p in prompts]
+        e.run()
+        done = {r.id: r for r in e.take_finished()}
+        assert sorted(done) == sorted(ids)
+        assert all(done[i].finish == "length" and len(done[i].tokens) == 12 for i in ids)
+        st = e.stats()
+        assert st.requests_done == 7 and st.prefill_tokens == sum(len(p) for p in prompts)
+        outs[mixed] = [done[i].tokens for i in ids]
+        e.close()
+    same = sum(int(np.array_equal(a, b)) for a, b in zip(outs[False], outs[True]))
+    assert same >= 5, "mixed steps changed more than near-tie continuations"
+    model.close()

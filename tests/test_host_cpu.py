@@ -99,3 +99,34 @@ def test_tensor_packer_gives_the_numpy_packers_bytes(bits):
     codes, scales = tl.bq.quantize_absmax(torch.randn((256, 320), generator=g) * 0.02, bits)
     a, b = tl.bq.pack(codes, scales, bits), tl.bq._pack_on_device(codes, scales, bits)
     assert (a.lo, a.hi, a.scales) == (b.lo, b.hi, b.scales)
+
+
+def test_converter_front_end_reproduces_the_direct_writer(tmp_path):
+    """A tiny random checkpoint saved the Hugging Face way (config.json + safetensors with the `model.` prefix) and
+    converted by the front end gives, byte for byte, the file the writer produces from the same tensors in memory
+    (whose quantiser, packer and tensor semantics the golden fixtures pin to the reference converter)."""
+    import json
+    import torch
+    from safetensors.torch import save_file
+    from q38b200 import convert, synth
+    cfg = synth.model_config(hidden=256, vocab=256, layers=4, intermediate=256, nq=2, nkv=1, lk=1, lv=1)
+    ckpt = synth.random_checkpoint(cfg, seed=3)
+    hf = tmp_path / "hf"
+    hf.mkdir()
+    names = {("lm_head.weight" if k == "lm_head.weight" else "model." + k): v.contiguous() for k, v in ckpt.items()}
+    save_file(names, str(hf / "model.safetensors"))
+    (hf / "config.json").write_text(json.dumps({
+        "hidden_size": 256, "num_hidden_layers": 4, "vocab_size": 256, "intermediate_size": 256, "num_attention_heads": 2,
+        "num_key_value_heads": 1, "head_dim": 256, "partial_rotary_factor": 0.25, "rope_theta": 1e7,
+        "linear_num_key_heads": 1, "linear_num_value_heads": 1, "linear_key_head_dim": 128, "linear_value_head_dim": 128,
+        "linear_conv_kernel_dim": 4, "rms_norm_eps": 1e-6, "max_position_embeddings": 4096, "eos_token_id": [1000, 1001],
+        "full_attention_interval": 4}))
+    got = convert.convert(hf, tmp_path / "a.q38", recipe="default", device="cpu")
+    assert got["layer_types"] == cfg["layer_types"] and got["rotary_dim"] == 64
+    synth.write_q38(tmp_path / "b.q38", got, ckpt, recipe="default", device="cpu")
+    assert (tmp_path / "a.q38").read_bytes() == (tmp_path / "b.q38").read_bytes()
+    m = eng.Model(tmp_path / "a.q38")
+    assert (m.vocab, m.hidden, m.layers) == (256, 256, 4)
+    m.close()
+    two = convert.convert(hf, tmp_path / "c.q38", layers=2, device="cpu")
+    assert two["num_layers"] == 2
