@@ -236,6 +236,11 @@ size_t q38_gdn_chunk_scratch_floats(int max_tokens, int max_seqs, int num_v_head
 int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, const q38_gdn_dims* d,
                                const q38_batch_desc* batch, const q38_gdn_state_desc* st, float* scratch,
                                size_t scratch_floats, void* stream);
+/* Which form of the chunk scan q38_gdn_recurrence_chunked launches: 1 (default) = the four per-chunk products on the
+ * tensor cores (mma.sync TF32 with every factor split into two TF32 numbers, three MMAs per product: fp32-like
+ * accuracy, fp32 sums), 0 = all fp32 on the CUDA cores. Process-wide; applies to launches made after the call. No
+ * counterpart in the reference (its recurrence is token-sequential). */
+void q38_gdn_set_chunk_scan_tensor_cores(int on);
 
 /* kernels::SamplingParamsDev / SamplingArgs / sample / target_logprobs, kernels.h:233-260 */
 typedef struct q38_sampling_params_dev {

@@ -129,6 +129,7 @@ KERNEL_API = {
                                C.POINTER(GdnStateDesc), C.c_void_p]),
     "q38_gdn_recurrence": (C.c_int, [C.POINTER(GdnRecurrenceParams), C.POINTER(GdnDims), C.POINTER(BatchDesc),
                                      C.POINTER(GdnStateDesc), C.c_void_p]),
+    "q38_gdn_set_chunk_scan_tensor_cores": (None, [C.c_int]),
     "q38_gdn_chunk_scratch_floats": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "q38_gdn_recurrence_chunked": (C.c_int, [C.POINTER(GdnRecurrenceParams), C.POINTER(GdnDims), C.POINTER(BatchDesc),
                                              C.POINTER(GdnStateDesc), C.c_void_p, C.c_size_t, C.c_void_p]),

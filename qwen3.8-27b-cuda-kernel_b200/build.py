@@ -24,6 +24,7 @@ OBJ = HERE / "build"
 LIB = HERE / "lib"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CUDA_LIB = str(Path(NVCC).resolve().parents[1] / "lib64")
 CUDA_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-I", str(ROOT / "include")]
 HOST_FLAGS = ["-std=c++20", "-O2", "-fPIC", "-I", str(ROOT / "include"), "-I", str(HOST / "include"),
@@ -71,14 +72,17 @@ def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = Fals
         list(pool.map(lambda c: _run(c, verbose or ptxas_verbose), jobs))
     kernels_so = LIB / "libq38_kernels.so"
     if force or _stale(kernels_so, cu_objs):
-        _run([NVCC, "-shared", "-o", str(kernels_so), *map(str, cu_objs)], verbose)
+        # both libraries use the one shared CUDA runtime of the process (a host application's, or torch's in the
+        # tests and benchmarks): same soname, so whichever copy is loaded first serves everybody
+        _run([NVCC, "-shared", "--cudart", "shared", "-o", str(kernels_so), *map(str, cu_objs),
+              "-Xlinker", f"-rpath,{CUDA_LIB}"], verbose)
     out = {"kernels": kernels_so}
     if host_objs:
         engine_so = LIB / "libq38_engine.so"
         if force or _stale(engine_so, host_objs + [kernels_so]):
             _run(["g++", "-shared", "-o", str(engine_so), *map(str, host_objs), "-L", str(LIB), "-lq38_kernels",
-                  "-L/usr/local/cuda/lib64", "-lcudart_static", "-ldl", "-lrt", "-lpthread",
-                  "-Wl,-rpath,$ORIGIN"], verbose)
+                  f"-L{CUDA_LIB}", "-lcudart", "-ldl", "-lrt", "-lpthread",
+                  f"-Wl,-rpath,$ORIGIN:{CUDA_LIB}"], verbose)
         out["engine"] = engine_so
     return out
 

@@ -595,41 +595,71 @@ __global__ void __launch_bounds__(kMmaThreads, 2) attn_decode_mma_kernel(
 // Replaces the reference's attention_prefill kernel (src/kernels/attention_prefill.cu:154-313) for int8 KV.
 //
 // One CTA per (KV split, kv head, tile of `tq` consecutive prompt tokens of one sequence). The tile's rows are its
-// (token, query head of the kv head's group) pairs, at most 64 = four warps of 16 rows; a fifth warp's lane streams
-// the (page, kv head) blocks of the keys the tile may see (causal: positions 0 .. last token of the tile) through
-// a two-stage shared-memory ring with the same four bulk copies per page as the decode kernel. Every K / V byte is
-// fetched once per tile instead of once per prompt token and query row.
-// Per 32-key half page a warp computes S = Q K^T with m16n8k16 f16 MMAs: Q rows are the A operand (fp16, staged in
-// shared memory once per tile), the keys are the B operand, dequantised in registers to fp16(int8) * fp16(scale)
-// (the rounding of the reference's prefill kernel); the dims of a k-step are permuted as in the decode kernel so a
-// lane reads 16 contiguous bytes per key. Online softmax in the log2 domain on the accumulator fragments (the
-// O accumulator is rescaled only when a row maximum of the warp moved), then O += P V with P as the A operand -
-// multiplied per 64-dim group by the V scales of its keys - and V's int8 bytes, two keys of one dim per register,
-// as exact fp16 integers. Only blocks that reach past a row's position are masked; blocks entirely beyond the
-// warp's last position are skipped. A single split normalises, applies the sigmoid output gate and writes bf16;
-// with several splits the (O, m, l) states go to the scratch for attn_merge_kernel.
+// (token, query head of the kv head's group) pairs, at most 128 = eight warps of 16 rows (eight warps are two per
+// scheduler, which leaves each thread the full 255 registers for the 16 x 256 fp32 output block it carries). Thread 0
+// streams the (page, kv head) blocks of the keys the tile may see (causal: positions 0 .. last token of the tile)
+// through a two-stage shared-memory ring with the same four bulk copies per page as the decode kernel: two pages up
+// front, then the page after next as soon as a stage has been converted. Every K / V byte is fetched once per tile
+// instead of once per prompt token and query row.
+// Per page the eight warps first turn the raw block into fp16 tiles K, V [64 keys][256] in shared memory, each element
+// fp16(int8) * fp16(scale of its key and 64-dim group) - the rounding of the reference's prefill kernel - once for
+// the whole tile (the raw stage goes back to the producer at that point); then every warp runs S = Q K^T for its 16
+// rows (Q fragments by ldmatrix from the staged fp16 query rows, K fragments by ldmatrix), the online softmax in the
+// log2 domain on the accumulator fragments (the O accumulator is rescaled only when a row maximum of the warp
+// moved), and O += P V with P straight from the S registers and V by transposing ldmatrix. Keys beyond a row's
+// position are masked; pages entirely beyond a warp's last position cost it nothing but the two barriers. A single
+// split normalises, applies the sigmoid output gate and writes bf16; with several splits the (O, m, l) states go to
+// the scratch for attn_merge_kernel.
 // ---------------------------------------------------------------------------------------------------
-constexpr int kPfWarps = 4;
+constexpr int kPfWarps = 8;
 constexpr int kPfRows = kPfWarps * 16;
-constexpr int kPfThreads = (kPfWarps + 1) * 32;
+constexpr int kPfConsumers = kPfWarps * 32;
+constexpr int kPfThreads = kPfConsumers;
 constexpr int kPfStages = 2;
-constexpr int kPfQStride = 2 * kHd + 8;        // bytes per staged fp16 query row (the pad spreads rows over banks)
+constexpr int kPfHStride = 2 * kHd + 16;       // bytes per fp16 row of the K / V / Q tiles: 16 mod 128, ldmatrix rows on distinct banks
 constexpr int kPfOStride = kHd + 4;            // floats per staged output row
 constexpr int kPfRingBytes = kPfStages * kStageBytes;
-static_assert(kPfRows * kPfOStride * 4 <= kPfRingBytes, "the output staging aliases the drained ring");
-constexpr int kPfSmem = kPfRingBytes + kPfRows * kPfQStride + 256;
+constexpr int kPfTileBytes = kPage * kPfHStride;
+constexpr int kPfKhOff = kPfRingBytes, kPfVhOff = kPfKhOff + kPfTileBytes, kPfQOff = kPfVhOff + kPfTileBytes;
+constexpr int kPfBarOff = kPfQOff + kPfRows * kPfHStride;
+static_assert(kPfRows * kPfOStride * 4 <= kPfQOff, "the output staging aliases the ring and the K / V tiles");
+constexpr int kPfSmem = kPfBarOff + 256;
 
-__global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// 16 int8 values (one 16-byte word group, biased by the caller's XOR) -> 16 fp16 values times `scale`, stored as 32 bytes
+__device__ __forceinline__ void dequant16_to_half(const uint4& raw, __half scale, uint8_t* dst) {
+  const __half2 sc = __half2half2(scale);
+  const uint32_t w[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+  uint32_t outw[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = bytes_to_half2<0x4140>(w[i]), hi = bytes_to_half2<0x4342>(w[i]);
+    const __half2 a = __hmul2(*reinterpret_cast<const __half2*>(&lo), sc);
+    const __half2 b = __hmul2(*reinterpret_cast<const __half2*>(&hi), sc);
+    outw[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+    outw[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  *reinterpret_cast<uint4*>(dst) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+  *reinterpret_cast<uint4*>(dst + 16) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+}
+
+__global__ void __launch_bounds__(kPfThreads, 1) attn_prefill_tile_kernel(
     const __half* __restrict__ q, const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ out,
     int nq, int group, int layer, int tq, int tiles_per_seq, float* __restrict__ scratch, int max_splits, int num_splits,
     const int* __restrict__ seq_start, const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0, KvView kv) {
   pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
   pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   extern __shared__ __align__(128) uint8_t dsm[];
-  uint8_t* qs = dsm + kPfRingBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(qs + kPfRows * kPfQStride);
-  uint64_t* empty = full + kPfStages;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kPfStages);
+  uint8_t* Kh = dsm + kPfKhOff;
+  uint8_t* Vh = dsm + kPfVhOff;
+  uint8_t* qs = dsm + kPfQOff;
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm + kPfBarOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(full + kPfStages);
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int b = blockIdx.z / tiles_per_seq, ti = blockIdx.z % tiles_per_seq;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -637,7 +667,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
   const int i0 = ti * tq;
   if (i0 >= n_seq) return;                       // this sequence's chunk has fewer tiles
   const int nt = min(tq, n_seq - i0);            // tokens of the tile
-  const int rows = nt * group;                   // (token, head) rows, <= 64
+  const int rows = nt * group;                   // (token, head) rows, <= 128
   const int m0 = s_first + i0;                   // first token row of the tile in the step's arrays
   const int pos0 = seq_pos0[b] + i0;             // its position; row r sees keys 0 .. pos0 + r / group
   const int slot = seq_slot[b];
@@ -654,49 +684,40 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
     return;
   }
   if (tid == 0) {
-    for (int s = 0; s < kPfStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kPfWarps);
-    }
+    for (int s = 0; s < kPfStages; ++s) mbar_init(&full[s], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
+  // Requests page p of the tile's key range into ring stage `s` (thread 0 only; the stage must be free).
+  auto request_page = [&](int p, int s) {
+    const int page = kv.block_table[(size_t)slot * kv.max_pages_per_seq + p];
+    if (page < 0 || page >= kv.num_pages) {
+      report_error(0x222);
+      *abort_flag = 1;
+      return;
+    }
+    const uint64_t pol = policy_evict_normal();  // the tiles of a chunk share their pages through L2
+    const uint8_t* base = kv.pool + (size_t)layer * kv.layer_stride + (size_t)page * kv.page_bytes;
+    uint8_t* st = dsm + (size_t)s * kStageBytes;
+    mbar_expect_tx(&full[s], 2 * 16384 + 2 * 512);
+    bulk_g2s(st + kStageK, base + kv.k_off(kvh, 0), 16384, &full[s], pol);
+    bulk_g2s(st + kStageV, base + kv.v_off(kvh, 0), 16384, &full[s], pol);
+    bulk_g2s(st + kStageKs, base + kv.ks_off(kvh, 0), 512, &full[s], pol);
+    bulk_g2s(st + kStageVs, base + kv.vs_off(kvh, 0), 512, &full[s], pol);
+  };
   // stage the tile's query rows (fp16), zero rows beyond the tile
-  for (int i = tid; i < kPfRows * (kHd / 4); i += kPfThreads) {
-    const int r = i / (kHd / 4), c = i % (kHd / 4);
-    uint2 v = make_uint2(0u, 0u);
+  for (int i = tid; i < kPfRows * (kHd / 8); i += kPfThreads) {
+    const int r = i / (kHd / 8), c = i % (kHd / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (r < rows)
-      v = *reinterpret_cast<const uint2*>(q + ((size_t)(m0 + r / group) * nq + (size_t)kvh * group + r % group) * kHd + 4 * c);
-    *reinterpret_cast<uint2*>(qs + (size_t)r * kPfQStride + 8 * c) = v;
+      v = *reinterpret_cast<const uint4*>(q + ((size_t)(m0 + r / group) * nq + (size_t)kvh * group + r % group) * kHd + 8 * c);
+    *reinterpret_cast<uint4*>(qs + (size_t)r * kPfHStride + 16 * c) = v;
   }
   __syncthreads();
 
-  if (warp == kPfWarps) {
-    if (lane == 0) {
-      const uint64_t pol = policy_evict_normal();  // the tiles of a chunk share their pages through L2
-      const int* table = kv.block_table + (size_t)slot * kv.max_pages_per_seq;
-      for (int p = p0, it = 0; p < p1; ++p, ++it) {
-        const int s = it % kPfStages;
-        if (*abort_flag || !mbar_wait(&empty[s], ((it / kPfStages) & 1) ^ 1, 0x221)) {
-          *abort_flag = 1;
-          break;
-        }
-        const int page = table[p];
-        if (page < 0 || page >= kv.num_pages) {
-          report_error(0x222);
-          *abort_flag = 1;
-          break;
-        }
-        const uint8_t* base = kv.pool + (size_t)layer * kv.layer_stride + (size_t)page * kv.page_bytes;
-        uint8_t* st = dsm + (size_t)s * kStageBytes;
-        mbar_expect_tx(&full[s], 2 * 16384 + 2 * 512);
-        bulk_g2s(st + kStageK, base + kv.k_off(kvh, 0), 16384, &full[s], pol);
-        bulk_g2s(st + kStageV, base + kv.v_off(kvh, 0), 16384, &full[s], pol);
-        bulk_g2s(st + kStageKs, base + kv.ks_off(kvh, 0), 512, &full[s], pol);
-        bulk_g2s(st + kStageVs, base + kv.vs_off(kvh, 0), 512, &full[s], pol);
-      }
-    }
-    return;
+  if (tid == 0) {  // barriers are initialised (the __syncthreads above): the first two pages
+    request_page(p0, 0);
+    if (p0 + 1 < p1) request_page(p0 + 1, 1);
   }
 
   const int g = lane >> 2, t = lane & 3;
@@ -704,9 +725,14 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
   const bool warp_live = 16 * warp < rows;
   const int pos_a = ra < rows ? pos0 + ra / group : -1;        // last key position a row may see (-1: padding row)
   const int pos_b = rb < rows ? pos0 + rb / group : -1;
-  const int warp_last = pos0 + (min(rows, 16 * warp + 16) - 1) / group;  // largest position among the warp's rows
-  const uint8_t* qa_ptr = qs + (size_t)ra * kPfQStride + 32 * t;
-  const uint8_t* qb_ptr = qs + (size_t)rb * kPfQStride + 32 * t;
+  const int warp_first = pos0 + (16 * warp) / group;           // smallest / largest position among the warp's rows
+  const int warp_last = pos0 + (min(rows, 16 * warp + 16) - 1) / group;
+  // ldmatrix lane addresses: Q A-fragments (rows 16 w + (lane & 15), dims + 8 (lane >> 4)); K fragments (keys
+  // 8 (mi >> 1) + (lane & 7), dims + 8 (mi & 1), mi = lane >> 3); V fragments transposed (keys 8 (mi & 1) + .., dims + 8 (mi >> 1))
+  const int mi = lane >> 3;
+  const uint32_t q_addr = smem_u32(qs) + (uint32_t)(16 * warp + (lane & 15)) * kPfHStride + 16u * (lane >> 4);
+  const uint32_t k_addr = smem_u32(Kh) + (uint32_t)(8 * (mi >> 1) + (lane & 7)) * kPfHStride + 16u * (mi & 1);
+  const uint32_t v_addr = smem_u32(Vh) + (uint32_t)(8 * (mi & 1) + (lane & 7)) * kPfHStride + 16u * (mi >> 1);
   float o[32][4];
 #pragma unroll
   for (int T = 0; T < 32; ++T)
@@ -720,61 +746,67 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
     bool ok = !*abort_flag && mbar_wait(&full[s], (it / kPfStages) & 1, 0x223);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) *abort_flag = 1;
-    const uint8_t* st = dsm + (size_t)s * kStageBytes;
-#pragma unroll 1
-    for (int hb = 0; hb < 2; ++hb) {
-      const int kbase = p * kPage + 32 * hb;  // first key of this half page
-      if (!ok || !warp_live || kbase > warp_last) continue;
-      const uint8_t* Kb = st + kStageK + (size_t)(32 * hb) * kHd;
-      const uint8_t* Vb = st + kStageV + (size_t)(32 * hb) * kHd;
-      const __half* Ksc = reinterpret_cast<const __half*>(st + kStageKs) + 32 * hb * 4;
-      const __half* Vsc = reinterpret_cast<const __half*>(st + kStageVs) + 32 * hb * 4;
-      // ---- S = Q K^T: rows = this warp's 16 query rows, columns = 32 keys (4 n-tiles of 8) ----
-      float sacc[4][4];
+    // ---- the page's K and V as fp16 tiles, once for all rows of the tile ----
+    if (ok) {
+      const uint8_t* st = dsm + (size_t)s * kStageBytes;
+      const __half* Ksc = reinterpret_cast<const __half*>(st + kStageKs);
+      const __half* Vsc = reinterpret_cast<const __half*>(st + kStageVs);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sacc[j][c] = 0.0f;
-#pragma unroll
-      for (int grp = 0; grp < 4; ++grp) {
-        uint32_t kw[4][4];
-        uint32_t ks2[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 kr = *reinterpret_cast<const uint4*>(Kb + (size_t)(8 * j + g) * kHd + 64 * grp + 16 * t);
-          kw[j][0] = kr.x ^ 0x80808080u;
-          kw[j][1] = kr.y ^ 0x80808080u;
-          kw[j][2] = kr.z ^ 0x80808080u;
-          kw[j][3] = kr.w ^ 0x80808080u;
-          const uint32_t h = __half_as_ushort(Ksc[(8 * j + g) * 4 + grp]);
-          ks2[j] = h | (h << 16);
-        }
-#pragma unroll
-        for (int ss = 0; ss < 4; ++ss) {
-          const uint2 qa = *reinterpret_cast<const uint2*>(qa_ptr + 128 * grp + 8 * ss);
-          const uint2 qb = *reinterpret_cast<const uint2*>(qb_ptr + 128 * grp + 8 * ss);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t lo = bytes_to_half2<0x4140>(kw[j][ss]), hi = bytes_to_half2<0x4342>(kw[j][ss]);
-            const __half2 sc = *reinterpret_cast<const __half2*>(&ks2[j]);
-            const __half2 b0 = __hmul2(*reinterpret_cast<const __half2*>(&lo), sc);
-            const __half2 b1 = __hmul2(*reinterpret_cast<const __half2*>(&hi), sc);
-            mma_f16_16816(sacc[j], qa.x, qb.x, qa.y, qb.y, *reinterpret_cast<const uint32_t*>(&b0),
-                          *reinterpret_cast<const uint32_t*>(&b1));
-          }
+      for (int r = 0; r < 4; ++r) {
+        const int u = tid + kPfConsumers * r;  // 16-byte group: key u / 16, dims 16 (u % 16) ..
+        const int key = u >> 4, ch = u & 15;
+        if (p * kPage + key < L) {
+          dequant16_to_half(*reinterpret_cast<const uint4*>(st + kStageK + 16 * u), Ksc[key * 4 + (ch >> 2)],
+                            Kh + (size_t)key * kPfHStride + 32 * ch);
+          dequant16_to_half(*reinterpret_cast<const uint4*>(st + kStageV + 16 * u), Vsc[key * 4 + (ch >> 2)],
+                            Vh + (size_t)key * kPfHStride + 32 * ch);
+        } else {  // positions nobody has written yet: whatever the page holds must not reach the products (0 x NaN)
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(Kh + (size_t)key * kPfHStride + 32 * ch) = zero;
+          *reinterpret_cast<uint4*>(Kh + (size_t)key * kPfHStride + 32 * ch + 16) = zero;
+          *reinterpret_cast<uint4*>(Vh + (size_t)key * kPfHStride + 32 * ch) = zero;
+          *reinterpret_cast<uint4*>(Vh + (size_t)key * kPfHStride + 32 * ch + 16) = zero;
         }
       }
-      // ---- online softmax (log2 domain); keys beyond a row's position are masked ----
+    }
+    __syncthreads();  // the fp16 tiles are complete, the raw stage is free: the page after next streams in during the products
+    if (tid == 0 && p + kPfStages < p1 && !*abort_flag) request_page(p + kPfStages, s);
+
+    const int kbase = p * kPage;
+    if (ok && warp_live && kbase <= warp_last) {
+      // ---- S = Q K^T: this warp's 16 rows x 64 keys (8 n-tiles), 16 k-steps of 16 dims ----
+      float sacc[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sacc[j][c] = 0.0f;
+#pragma unroll 4
+      for (int kk = 0; kk < 16; ++kk) {
+        uint32_t qa[4];
+        ldmatrix_x4(qa, q_addr + 32u * kk);
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) {  // keys 16 jp .. 16 jp + 15
+          uint32_t kb[4];
+          ldmatrix_x4(kb, k_addr + (uint32_t)(16 * jp) * kPfHStride + 32u * kk);
+          mma_f16_16816(sacc[2 * jp], qa[0], qa[1], qa[2], qa[3], kb[0], kb[1]);
+          mma_f16_16816(sacc[2 * jp + 1], qa[0], qa[1], qa[2], qa[3], kb[2], kb[3]);
+        }
+      }
+      // ---- online softmax (log2 domain); keys beyond a row's position are masked on pages that reach that far ----
+      const bool need_mask = kbase + kPage - 1 > warp_first;
       float bm_a = -INFINITY, bm_b = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < 8; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const int key = kbase + 8 * j + 2 * t + (c & 1);
-          const bool seen = key <= ((c & 2) ? pos_b : pos_a);
-          sacc[j][c] = seen ? sacc[j][c] * kScale : -INFINITY;
-          if (c & 2) bm_b = fmaxf(bm_b, sacc[j][c]);
-          else bm_a = fmaxf(bm_a, sacc[j][c]);
+          float v = sacc[j][c] * kScale;
+          if (need_mask) {
+            const int key = kbase + 8 * j + 2 * t + (c & 1);
+            if (key > ((c & 2) ? pos_b : pos_a)) v = -INFINITY;
+          }
+          sacc[j][c] = v;
+          if (c & 2) bm_b = fmaxf(bm_b, v);
+          else bm_a = fmaxf(bm_a, v);
         }
       bm_a = fmaxf(bm_a, __shfl_xor_sync(0xffffffffu, bm_a, 1));
       bm_a = fmaxf(bm_a, __shfl_xor_sync(0xffffffffu, bm_a, 2));
@@ -784,14 +816,16 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
       const float ref_a = mn_a == -INFINITY ? 0.0f : mn_a, ref_b = mn_b == -INFINITY ? 0.0f : mn_b;  // no inf - inf
       const float c_a = exp2f(m_a - ref_a), c_b = exp2f(m_b - ref_b);
       float ps_a = 0.0f, ps_b = 0.0f;
+      uint32_t pf[8][2];  // P as fp16 pairs: [n-tile][rows g / g + 8]
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        sacc[j][0] = exp2f(sacc[j][0] - ref_a);
-        sacc[j][1] = exp2f(sacc[j][1] - ref_a);
-        sacc[j][2] = exp2f(sacc[j][2] - ref_b);
-        sacc[j][3] = exp2f(sacc[j][3] - ref_b);
-        ps_a += sacc[j][0] + sacc[j][1];
-        ps_b += sacc[j][2] + sacc[j][3];
+      for (int j = 0; j < 8; ++j) {
+        const float e0 = exp2f(sacc[j][0] - ref_a), e1 = exp2f(sacc[j][1] - ref_a);
+        const float e2 = exp2f(sacc[j][2] - ref_b), e3 = exp2f(sacc[j][3] - ref_b);
+        ps_a += e0 + e1;
+        ps_b += e2 + e3;
+        const __half2 ha = __floats2half2_rn(e0, e1), hb = __floats2half2_rn(e2, e3);
+        pf[j][0] = *reinterpret_cast<const uint32_t*>(&ha);
+        pf[j][1] = *reinterpret_cast<const uint32_t*>(&hb);
       }
       l_a = l_a * c_a + ps_a;
       l_b = l_b * c_b + ps_b;
@@ -807,64 +841,34 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tile_kernel(
           o[T][3] *= c_b;
         }
       }
-      // ---- O += P V: 2 k-steps of 16 keys; P carries the V scale of its key and 64-dim group ----
+      // ---- O += P V: 4 k-steps of 16 keys, 32 n-tiles of 8 dims (two per transposing ldmatrix) ----
 #pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        const uint2 v0 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t) * 4);
-        const uint2 v1 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t + 1) * 4);
-        const uint2 v2 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t + 8) * 4);
-        const uint2 v3 = *reinterpret_cast<const uint2*>(Vsc + (16 * kk + 2 * t + 9) * 4);
-        const uint32_t sw0[2] = {v0.x, v0.y}, sw1[2] = {v1.x, v1.y}, sw2[2] = {v2.x, v2.y}, sw3[2] = {v3.x, v3.y};
+      for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-          const int sh = 16 * (grp & 1);
-          const float f0 = __half2float(__ushort_as_half((unsigned short)(sw0[grp >> 1] >> sh)));
-          const float f1 = __half2float(__ushort_as_half((unsigned short)(sw1[grp >> 1] >> sh)));
-          const float f2 = __half2float(__ushort_as_half((unsigned short)(sw2[grp >> 1] >> sh)));
-          const float f3 = __half2float(__ushort_as_half((unsigned short)(sw3[grp >> 1] >> sh)));
-          const __half2 a0 = __floats2half2_rn(sacc[2 * kk][0] * f0, sacc[2 * kk][1] * f1);
-          const __half2 a1 = __floats2half2_rn(sacc[2 * kk][2] * f0, sacc[2 * kk][3] * f1);
-          const __half2 a2 = __floats2half2_rn(sacc[2 * kk + 1][0] * f2, sacc[2 * kk + 1][1] * f3);
-          const __half2 a3 = __floats2half2_rn(sacc[2 * kk + 1][2] * f2, sacc[2 * kk + 1][3] * f3);
-          const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&a0), pa1 = *reinterpret_cast<const uint32_t*>(&a1);
-          const uint32_t pa2 = *reinterpret_cast<const uint32_t*>(&a2), pa3 = *reinterpret_cast<const uint32_t*>(&a3);
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int J = 2 * grp + jj;  // 32-dim group: n-tile 4 J + I holds dims 32 J + 4 n + I, n = 0..7
-            const uint8_t* vp = Vb + (size_t)(16 * kk) * kHd + 32 * J + 4 * g;
-            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vp + (2 * t) * kHd) ^ 0x80808080u;
-            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 1) * kHd) ^ 0x80808080u;
-            const uint32_t w2 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 8) * kHd) ^ 0x80808080u;
-            const uint32_t w3 = *reinterpret_cast<const uint32_t*>(vp + (2 * t + 9) * kHd) ^ 0x80808080u;
-            mma_f16_16816(o[4 * J + 0], pa0, pa1, pa2, pa3, byte_pair_to_half2<0>(w0, w1), byte_pair_to_half2<0>(w2, w3));
-            mma_f16_16816(o[4 * J + 1], pa0, pa1, pa2, pa3, byte_pair_to_half2<1>(w0, w1), byte_pair_to_half2<1>(w2, w3));
-            mma_f16_16816(o[4 * J + 2], pa0, pa1, pa2, pa3, byte_pair_to_half2<2>(w0, w1), byte_pair_to_half2<2>(w2, w3));
-            mma_f16_16816(o[4 * J + 3], pa0, pa1, pa2, pa3, byte_pair_to_half2<3>(w0, w1), byte_pair_to_half2<3>(w2, w3));
-          }
+        for (int dp = 0; dp < 16; ++dp) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, v_addr + (uint32_t)(16 * ks) * kPfHStride + 32u * dp);
+          mma_f16_16816(o[2 * dp], pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1], vb[0], vb[1]);
+          mma_f16_16816(o[2 * dp + 1], pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1], vb[2], vb[3]);
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
+    __syncthreads();  // every warp is through with the fp16 tiles before the next page overwrites them
   }
 
-  // ---- finish: row sums across the four lanes of a row, then through shared memory (the drained ring) for
+  // ---- finish: row sums across the four lanes of a row, then through shared memory (ring and tiles are drained) for
   //      coalesced gate reads and stores ----
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-  named_bar_sync(1, kPfWarps * 32);  // every warp is through with the ring
   float* os = reinterpret_cast<float*>(dsm);
   const float inv_a = (num_splits == 1 && l_a > 0.0f) ? 1.0f / l_a : 1.0f;
   const float inv_b = (num_splits == 1 && l_b > 0.0f) ? 1.0f / l_b : 1.0f;
 #pragma unroll
   for (int T = 0; T < 32; ++T) {
-    const int dim = 32 * (T >> 2) + 8 * t + (T & 3);  // column 2 t of n-tile T; column 2 t + 1 is 4 dims further
-    os[(size_t)ra * kPfOStride + dim] = o[T][0] * inv_a;
-    os[(size_t)ra * kPfOStride + dim + 4] = o[T][1] * inv_a;
-    os[(size_t)rb * kPfOStride + dim] = o[T][2] * inv_b;
-    os[(size_t)rb * kPfOStride + dim + 4] = o[T][3] * inv_b;
+    *reinterpret_cast<float2*>(os + (size_t)ra * kPfOStride + 8 * T + 2 * t) = make_float2(o[T][0] * inv_a, o[T][1] * inv_a);
+    *reinterpret_cast<float2*>(os + (size_t)rb * kPfOStride + 8 * T + 2 * t) = make_float2(o[T][2] * inv_b, o[T][3] * inv_b);
   }
   __syncwarp();
   for (int rr = 0; rr < 16; ++rr) {

@@ -10,6 +10,7 @@
 #include "host_util.h"
 
 namespace q38 {
+extern int g_chunk_scan_tensor_cores;  // 1: the chunk scan runs its products on the tensor cores (TF32)
 namespace {
 
 constexpr int kDk = 128, kDv = 128;
@@ -908,6 +909,240 @@ __global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_kernel(
     *reinterpret_cast<float4*>(S + (size_t)i * 4) = *reinterpret_cast<const float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31));
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The same scan with the four per-chunk products on the tensor cores (mma.sync m16n8k8 TF32, fp32 accumulation);
+// staging, the decay factors, the forward-substituted U0 / W of the preparation kernel and the state layout are those
+// of gdn_chunk_scan_kernel, which stays as the fp32 CUDA-core form of the operator. One TF32 product keeps 10 mantissa
+// bits of each factor, which is not enough here: outputs that are small through cancellation moved by more than the
+// operator's tolerance in a few elements per million. So every fp32 factor x is split as x = hi + lo, hi = the top 19
+// bits of x (exact in TF32), lo = x - hi (exact in fp32, its own low bits below 2^-20 |x|), and a product is three
+// MMAs, lo hi + hi lo + hi hi: the dropped lo lo term and lo's truncation are about 2^-20 relative, i.e. fp32-like.
+// Fragment reads straight from the padded fp32 tiles in shared memory (row strides 132 / 68 floats keep the eight
+// rows x four columns of a fragment on distinct banks).
+//   (a) X = W S0^T and (b) Y = Q S0^T   [64 tokens][NV v], k = 128: warps 0-7 X, warps 8-15 Y, one 16-token row
+//       block x NV / 16 column tiles each; U = U0 - X goes back to shared memory, Y e^{lg} stays in registers;
+//   (c) O = Y e^{lg} + P U: the Y warps go on over the chunk's tokens j <= their row block (P is lower triangular);
+//   (d) S = e^{lg_C} S0 + (U diag(e^{lg_C - lg}))^T K   [NV v][128 k], j = 64: all sixteen warps.
+// ---------------------------------------------------------------------------------------------------
+struct Tf32Pair {
+  uint32_t hi, lo;
+};
+__device__ __forceinline__ Tf32Pair split_tf32(float x) {
+  Tf32Pair p;
+  p.hi = __float_as_uint(x) & 0xFFFFE000u;             // sign, exponent, 10 mantissa bits: a TF32 number
+  p.lo = __float_as_uint(x - __uint_as_float(p.hi));   // exact; the tensor core reads its top 19 bits
+  return p;
+}
+// d += A B with A = (a0..a3), B = (b0, b1) given as split pairs: the two cross terms first, the main term last
+__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1);
+__device__ __forceinline__ void mma3_tf32(float (&d)[4], const Tf32Pair (&a)[4], const Tf32Pair& b0, const Tf32Pair& b1) {
+  mma_tf32_1688(d, a[0].lo, a[1].lo, a[2].lo, a[3].lo, b0.hi, b1.hi);
+  mma_tf32_1688(d, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.lo, b1.lo);
+  mma_tf32_1688(d, a[0].hi, a[1].hi, a[2].hi, a[3].hi, b0.hi, b1.hi);
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int VSPLIT>
+__global__ void __launch_bounds__(kChunkThreads, 1) gdn_chunk_scan_mma_kernel(
+    const float* __restrict__ qkv, int conv_dim, const __nv_bfloat16* __restrict__ z, int ld_z,
+    const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out, int layer, int num_layers, int nk,
+    int nv, float* __restrict__ recurrent, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+    const float* __restrict__ scratch, float* __restrict__ o_scratch) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int NV = kDv / VSPLIT;   // state rows (v) of this CTA
+  constexpr int NT = NV / 16;        // 8-wide column tiles per warp in (a)-(d): 4 or 8
+  extern __shared__ float scan_sm[];
+  float* Ss = scan_sm;               // [NV v][kLd]
+  float* Ws = Ss + NV * kLd;         // [64][kLd]: W, later the chunk's outputs (VSPLIT == 1)
+  float* Qs = Ws + kCh * kLd;
+  float* Kd = Qs + kCh * kLd;        // K rows
+  float* Us = Kd + kCh * kLd;        // U0, then U: [64][kLd], NV columns used
+  float* Ps = Us + kCh * kLd;        // [64][kLdP]
+  float* lg_s = Ps + kCh * kLdP;
+  float* eg_s = lg_s + kCh;          // e^{lg_t}
+  float* kd_s = eg_s + kCh;          // e^{lg_C - lg_j}
+  const int vh = blockIdx.x / VSPLIT, vbase = (blockIdx.x % VSPLIT) * NV, b = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int s0 = seq_start[b], n = seq_start[b + 1] - s0;
+  if (n <= 0) return;
+  const int kh = vh / (nv / nk);
+  float* S = recurrent + ((((size_t)seq_slot[b] * num_layers + layer) * nv + vh) * kDv + vbase) * kDk;
+  for (int i = tid; i < NV * 32; i += kChunkThreads)
+    *reinterpret_cast<float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31)) = *reinterpret_cast<const float4*>(S + (size_t)i * 4);
+  const int chunks = (n + kCh - 1) / kCh;
+  // (a)-(c): product X or Y, 16-token row block mt, column tiles nt0 .. nt0 + NT - 1 of the CTA's NV columns
+  const int which = warp >> 3, mt = (warp & 7) >> 1, nt0 = (warp & 1) * NT;
+  // (d): state rows 16 dm .. + 15, column tiles dn0 .. dn0 + NT - 1 of the 128 k columns
+  const int dm = warp / (16 / NT), dn0 = (warp % (16 / NT)) * NT;
+
+  for (int c = 0; c < chunks; ++c) {
+    const int nc = min(kCh, n - c * kCh), m0 = s0 + c * kCh;
+    const float* in = scratch + ((size_t)(s0 / kCh + b + c) * nv + vh) * kChunkFloats;
+    __syncthreads();  // the previous chunk's state update and output pass (or the initial state load) are complete
+    if (tid < kCh) {
+      const float lg = in[2 * kCh * 128 + kCh * kCh + tid], lgc = in[2 * kCh * 128 + kCh * kCh + kCh - 1];
+      lg_s[tid] = lg;
+      eg_s[tid] = expf(lg);
+      kd_s[tid] = expf(lgc - lg);
+    }
+    const float* rows = qkv + (size_t)m0 * conv_dim;
+    rows_async_128(Ws, in + kCh * 128, 128, kCh, tid);
+    rows_async_128(Qs, rows + (size_t)kh * kDk, conv_dim, nc, tid);
+    for (int i = tid; i < kCh * (NV / 4); i += kChunkThreads) {
+      const int r = i / (NV / 4), c4 = i % (NV / 4);
+      cp_async16(Us + r * kLd + 4 * c4, in + (size_t)r * 128 + vbase + 4 * c4, true);
+    }
+    cp_async_commit();
+    rows_async_128(Kd, rows + (size_t)nk * kDk + (size_t)kh * kDk, conv_dim, nc, tid);
+    for (int i = tid; i < kCh * 16; i += kChunkThreads)
+      cp_async16(Ps + (i >> 4) * kLdP + 4 * (i & 15), in + 2 * kCh * 128 + (size_t)i * 4, true);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // ---- (a) / (b): [16 tokens][8 NT v] += A[16][128] S0^T ----
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+    {
+      const float* Am = (which == 0 ? Ws : Qs) + (16 * mt + g) * kLd + t4;
+      const float* Bm = Ss + (8 * nt0 + g) * kLd + t4;
+#pragma unroll 4
+      for (int ks = 0; ks < 16; ++ks) {
+        const Tf32Pair a[4] = {split_tf32(Am[8 * ks]), split_tf32(Am[8 * kLd + 8 * ks]), split_tf32(Am[8 * ks + 4]),
+                               split_tf32(Am[8 * kLd + 8 * ks + 4])};
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          mma3_tf32(acc[j], a, split_tf32(Bm[(8 * j) * kLd + 8 * ks]), split_tf32(Bm[(8 * j) * kLd + 8 * ks + 4]));
+      }
+    }
+    const int ra = 16 * mt + g, rb = ra + 8;  // this lane's two token rows of the block
+    if (which == 0) {  // U = U0 - X
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int col = 8 * (nt0 + j) + 2 * t4;
+        float2* pa = reinterpret_cast<float2*>(Us + ra * kLd + col);
+        float2* pb = reinterpret_cast<float2*>(Us + rb * kLd + col);
+        float2 ua = *pa, ub = *pb;
+        ua.x -= acc[j][0];
+        ua.y -= acc[j][1];
+        ub.x -= acc[j][2];
+        ub.y -= acc[j][3];
+        *pa = ua;
+        *pb = ub;
+      }
+    } else {           // Y scaled by e^{lg_t}
+      const float ea = eg_s[ra], eb = eg_s[rb];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        acc[j][0] *= ea;
+        acc[j][1] *= ea;
+        acc[j][2] *= eb;
+        acc[j][3] *= eb;
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // U complete; nobody reads W any more; P and K have landed
+
+    // ---- (c) O = Y e^{lg} + P U on the Y warps; P[t][j] = 0 for j > t, so row block mt needs j < 16 mt + 16 ----
+    if (which == 1) {
+      const float* Pm = Ps + (16 * mt + g) * kLdP + t4;
+      const float* Um = Us + t4 * kLd + 8 * nt0 + g;
+      for (int ks = 0; ks < 2 * mt + 2; ++ks) {
+        const Tf32Pair a[4] = {split_tf32(Pm[8 * ks]), split_tf32(Pm[8 * kLdP + 8 * ks]), split_tf32(Pm[8 * ks + 4]),
+                               split_tf32(Pm[8 * kLdP + 8 * ks + 4])};
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          mma3_tf32(acc[j], a, split_tf32(Um[(8 * ks) * kLd + 8 * j]), split_tf32(Um[(8 * ks + 4) * kLd + 8 * j]));
+      }
+      if constexpr (VSPLIT == 1) {  // the chunk's outputs go through the W buffer: the norm runs over all 128 v of a token
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const int col = 8 * (nt0 + j) + 2 * t4;
+          *reinterpret_cast<float2*>(Ws + ra * kLd + col) = make_float2(acc[j][0], acc[j][1]);
+          *reinterpret_cast<float2*>(Ws + rb * kLd + col) = make_float2(acc[j][2], acc[j][3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const int col = vbase + 8 * (nt0 + j) + 2 * t4;
+          if (ra < nc)
+            *reinterpret_cast<float2*>(o_scratch + ((size_t)(m0 + ra) * nv + vh) * kDv + col) = make_float2(acc[j][0], acc[j][1]);
+          if (rb < nc)
+            *reinterpret_cast<float2*>(o_scratch + ((size_t)(m0 + rb) * nv + vh) * kDv + col) = make_float2(acc[j][2], acc[j][3]);
+        }
+      }
+    }
+
+    // ---- (d) S = e^{lg_C} S0 + (U diag(e^{lg_C - lg}))^T K: rows v = 16 dm + g (+ 8), columns k = 8 (dn0 + j) + 2 t4 ----
+    {
+      float sacc[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[j][e] = 0.0f;
+      const float* Um = Us + t4 * kLd + 16 * dm + g;
+      const float* Km = Kd + t4 * kLd + 8 * dn0 + g;
+#pragma unroll 2
+      for (int ks = 0; ks < 8; ++ks) {
+        const float d0 = kd_s[8 * ks + t4], d1 = kd_s[8 * ks + t4 + 4];
+        const Tf32Pair a[4] = {split_tf32(Um[(8 * ks) * kLd] * d0), split_tf32(Um[(8 * ks) * kLd + 8] * d0),
+                               split_tf32(Um[(8 * ks + 4) * kLd] * d1), split_tf32(Um[(8 * ks + 4) * kLd + 8] * d1)};
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          mma3_tf32(sacc[j], a, split_tf32(Km[(8 * ks) * kLd + 8 * j]), split_tf32(Km[(8 * ks + 4) * kLd + 8 * j]));
+      }
+      const float gC = eg_s[kCh - 1];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int col = 8 * (dn0 + j) + 2 * t4;
+        float2* pa = reinterpret_cast<float2*>(Ss + (16 * dm + g) * kLd + col);
+        float2* pb = reinterpret_cast<float2*>(Ss + (16 * dm + g + 8) * kLd + col);
+        float2 xa = *pa, xb = *pb;
+        xa.x = gC * xa.x + sacc[j][0];
+        xa.y = gC * xa.y + sacc[j][1];
+        xb.x = gC * xb.x + sacc[j][2];
+        xb.y = gC * xb.y + sacc[j][3];
+        *pa = xa;
+        *pb = xb;
+      }
+    }
+    if constexpr (VSPLIT == 1) {
+      __syncthreads();  // the chunk's outputs are in the W buffer
+      // gated RMSNorm over the 128 outputs of each token: a warp takes four tokens, a lane four v
+      for (int tt = 0; tt < 4; ++tt) {
+        const int t = 4 * warp + tt;
+        if (t >= nc) break;
+        const float4 ov = *reinterpret_cast<const float4*>(Ws + t * kLd + 4 * lane);
+        const float ss = warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w);
+        const float r = 1.0f / sqrtf(ss / float(kDv) + eps);
+        const size_t m = (size_t)(m0 + t);
+        const uint2 zraw = *reinterpret_cast<const uint2*>(z + m * ld_z + (size_t)vh * kDv + 4 * lane);
+        const __nv_bfloat162* zp = reinterpret_cast<const __nv_bfloat162*>(&zraw);
+        const float4 wv = *reinterpret_cast<const float4*>(norm_w + 4 * lane);
+        __nv_bfloat162 res[2];
+        res[0] = __floats2bfloat162_rn(ov.x * r * wv.x * silu_f(__low2float(zp[0])), ov.y * r * wv.y * silu_f(__high2float(zp[0])));
+        res[1] = __floats2bfloat162_rn(ov.z * r * wv.z * silu_f(__low2float(zp[1])), ov.w * r * wv.w * silu_f(__high2float(zp[1])));
+        *reinterpret_cast<uint2*>(out + m * nv * kDv + (size_t)vh * kDv + 4 * lane) = *reinterpret_cast<uint2*>(res);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < NV * 32; i += kChunkThreads)
+    *reinterpret_cast<float4*>(S + (size_t)i * 4) = *reinterpret_cast<const float4*>(Ss + (i >> 5) * kLd + 4 * (i & 31));
+}
+
 // Gated RMSNorm of the split scan's outputs: one CTA per (token, v head), 128 threads.
 __global__ void __launch_bounds__(kDv) gdn_norm_gate_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ z,
                                                             int ld_z, const float* __restrict__ norm_w, float eps,
@@ -926,6 +1161,8 @@ __global__ void __launch_bounds__(kDv) gdn_norm_gate_kernel(const float* __restr
 }
 
 }  // namespace
+
+int g_chunk_scan_tensor_cores = 1;
 
 unsigned int gdn_error(bool clear) { return read_tu_error(clear); }
 unsigned int* gdn_error_address() { return tu_error_address(); }
@@ -1011,6 +1248,8 @@ extern "C" int q38_gdn_recurrence(const q38_gdn_recurrence_params* p, const q38_
   return Q38_OK;
 }
 
+extern "C" void q38_gdn_set_chunk_scan_tensor_cores(int on) { q38::g_chunk_scan_tensor_cores = on != 0; }
+
 extern "C" size_t q38_gdn_chunk_scratch_floats(int max_tokens, int max_seqs, int num_v_heads) {
   // per-chunk U0 / W / P / lg for every chunk slot, then one [tokens][v heads * 128] fp32 row block for the split scan
   return (size_t)(max_tokens / kCh + max_seqs) * (size_t)num_v_heads * kChunkFloats +
@@ -1037,9 +1276,16 @@ extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, co
       cudaFuncSetAttribute(gdn_chunk_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
   static const cudaError_t attr3 =
       cudaFuncSetAttribute(gdn_chunk_scan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  static const cudaError_t attr4 =
+      cudaFuncSetAttribute(gdn_chunk_scan_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
+  static const cudaError_t attr5 =
+      cudaFuncSetAttribute(gdn_chunk_scan_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemBytes);
   Q38_CUDA_OK(attr1);
   Q38_CUDA_OK(attr2);
   Q38_CUDA_OK(attr3);
+  Q38_CUDA_OK(attr4);
+  Q38_CUDA_OK(attr5);
+  const bool tc = g_chunk_scan_tensor_cores != 0;
   const cudaStream_t s = as_stream(stream);
   const int max_chunks = (batch->max_tokens_per_seq + kCh - 1) / kCh;
   (void)launch_kernel(gdn_chunk_prep_kernel, dim3(max_chunks, d->num_v_heads, batch->num_seqs), dim3(kChunkThreads), kPrepSmemBytes, s, 
@@ -1051,7 +1297,7 @@ extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, co
   // the sequential part has one CTA per (v head, sequence); with few of them, two CTAs share a head's state rows
   const bool split = 2 * d->num_v_heads * batch->num_seqs <= num_sms();
   if (split) {
-    (void)launch_kernel(gdn_chunk_scan_kernel<2>, dim3(2 * d->num_v_heads, batch->num_seqs), dim3(kChunkThreads),
+    (void)launch_kernel(tc ? gdn_chunk_scan_mma_kernel<2> : gdn_chunk_scan_kernel<2>, dim3(2 * d->num_v_heads, batch->num_seqs), dim3(kChunkThreads),
                         kScanSmemBytes, s, p->qkv, d->conv_dim, zp, p->ld_z, p->norm_w, p->eps, outp, p->gdn_layer,
                         st->num_gdn_layers, d->num_k_heads, d->num_v_heads, st->recurrent, batch->seq_start,
                         batch->seq_slot, scratch, o_scratch);
@@ -1060,7 +1306,7 @@ extern "C" int q38_gdn_recurrence_chunked(const q38_gdn_recurrence_params* p, co
                         p->ld_z, p->norm_w, p->eps, outp, d->num_v_heads);
     Q38_LAUNCH_OK("gdn_norm_gate_kernel");
   } else {
-    (void)launch_kernel(gdn_chunk_scan_kernel<1>, dim3(d->num_v_heads, batch->num_seqs), dim3(kChunkThreads),
+    (void)launch_kernel(tc ? gdn_chunk_scan_mma_kernel<1> : gdn_chunk_scan_kernel<1>, dim3(d->num_v_heads, batch->num_seqs), dim3(kChunkThreads),
                         kScanSmemBytes, s, p->qkv, d->conv_dim, zp, p->ld_z, p->norm_w, p->eps, outp, p->gdn_layer,
                         st->num_gdn_layers, d->num_k_heads, d->num_v_heads, st->recurrent, batch->seq_start,
                         batch->seq_slot, scratch, o_scratch);

@@ -23,6 +23,7 @@ Fixtures written:
 from __future__ import annotations
 
 import argparse
+import os
 import subprocess
 import sys
 import tempfile
@@ -70,7 +71,8 @@ def reference_convert(ref_tools: Path, cfg: dict, ckpt: dict, out: Path, recipe:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("Q38_REFERENCE", ""), required=not os.environ.get("Q38_REFERENCE"),
+                    help="checkout of the reference project (or set Q38_REFERENCE)")
     args = ap.parse_args()
     ref_root = Path(args.reference)
     ref_ops = tl.reference_ops()

