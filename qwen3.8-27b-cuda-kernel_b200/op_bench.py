@@ -12,6 +12,9 @@ working set of either kernel is far larger than L2.
   python qwen3.8-27b-cuda-kernel_b200/op_bench.py --op prefill --prefix 2048,32768,131072
       # the query-tiled prefill attention: one 512-token chunk behind a cached prefix, for the 27B layer (24 q / 4 kv
       # heads) and for one rank of the 8-way tensor-parallel layout (3 q / 1 kv head, keys cut over several CTAs)
+  python qwen3.8-27b-cuda-kernel_b200/op_bench.py --op scan --chunk 512
+      # the chunked Gated DeltaNet recurrence over one prefill step (per-chunk preparation + state scan), with the scan's
+      # products on the tensor cores (split TF32) and as fp32 FMAs
 """
 
 from __future__ import annotations
@@ -165,9 +168,45 @@ def gdn_case(pkg, seqs, seed):
     return launch, state_bytes, (rec, conv, keep, qkv, ab, A, dt, nw, proj, out), f"{seqs} sequences x {NV} heads"
 
 
+def scan_case(pkg, tokens, seed):
+    """One sequence: the chunked recurrence (per-chunk preparation + state scan) over a `tokens`-token prefill step of
+    one GDN layer of the 27B geometry."""
+    K = pkg.kernels()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    conv_dim = (2 * NK + NV) * 128
+    ld = conv_dim + NV * 128
+    rec = torch.randn((1, 1, NV, 128, 128), generator=g, device="cuda") * 0.1
+    conv = torch.zeros((1, 1, 3, conv_dim), dtype=torch.bfloat16, device="cuda")
+    st = pkg.GdnStateDesc(pkg.ptr(rec), pkg.ptr(conv), 1)
+    dims = pkg.GdnDims(NK, NV, conv_dim, ld)
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    t = {"seq_start": mk([0, tokens]), "seq_slot": mk([0]), "seq_pos0": mk([0]), "tok_pos": mk(list(range(tokens))),
+         "tok_seq": mk([0] * tokens)}
+    desc = pkg.BatchDesc(1, tokens, tokens, pkg.ptr(t["seq_start"]), pkg.ptr(t["seq_slot"]), pkg.ptr(t["seq_pos0"]),
+                         pkg.ptr(t["tok_pos"]), pkg.ptr(t["tok_seq"]))
+    qkv = torch.randn((tokens, conv_dim), generator=g, device="cuda") * 0.1
+    ab = torch.randn((tokens, 2 * NV), generator=g, device="cuda")
+    A = -torch.rand(NV, generator=g, device="cuda") - 0.5
+    dt = torch.randn(NV, generator=g, device="cuda") * 0.5
+    nw = torch.ones(128, device="cuda")
+    proj = torch.randn((tokens, ld), generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.empty((tokens, NV * 128), dtype=torch.bfloat16, device="cuda")
+    rp = pkg.GdnRecurrenceParams(pkg.ptr(qkv), pkg.ptr(ab), pkg.ptr(A), pkg.ptr(dt), pkg.ptr(proj) + conv_dim * 2, ld,
+                                 pkg.ptr(nw), 1e-6, pkg.ptr(out), 0)
+    need = int(K.q38_gdn_chunk_scratch_floats(tokens, 1, NV))
+    scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+    # per (token, value head): four 64x128x128-shaped products of the scan, 2 flops per multiply-add
+    flops = 4 * 2 * tokens * NV * 128 * 128
+
+    def launch(stream):
+        pkg.check(K.q38_gdn_recurrence_chunked(C.byref(rp), C.byref(dims), C.byref(desc), C.byref(st), pkg.ptr(scratch),
+                                               need, stream))
+    return launch, flops, (rec, conv, t, qkv, ab, A, dt, nw, proj, out, scratch), f"{tokens} tokens x {NV} heads"
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="attn,gdn", help="comma-separated: attn, gdn, prefill")
+    ap.add_argument("--op", default="attn,gdn", help="comma-separated: attn, gdn, prefill, scan")
     ap.add_argument("--prefix", default="2048,32768,131072", help="prefill: cached tokens before the chunk")
     ap.add_argument("--chunk", type=int, default=512, help="prefill: tokens of the step")
     ap.add_argument("--seqs", type=int, default=64)
@@ -195,6 +234,24 @@ def main(argv=None):
                         us = timed_graph(launch, max(2, args.iters // 4))
                         print(f"prefill {what}: {us:9.1f} us  {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
                     del keep
+            if K.q38_device_error(1):
+                raise SystemExit("device-side wait gave up")
+            continue
+        if op == "scan":  # chunked GDN recurrence of one prefill step, both forms of the scan
+            for tensor_cores in (1, 0):
+                K.q38_gdn_set_chunk_scan_tensor_cores(tensor_cores)
+                launch, flops, keep, what = scan_case(pkg, args.chunk, args.seed)
+                form = "tensor cores (split TF32)" if tensor_cores else "fp32 FMA"
+                if args.untimed:
+                    for _ in range(args.launches):
+                        launch(None)
+                    torch.cuda.synchronize()
+                    print(f"ok: scan [{form}]: {args.launches} launches, {what}")
+                else:
+                    us = timed_graph(launch, args.iters)
+                    print(f"scan  {what} [{form}]: {us:8.1f} us  {flops / us / 1e6:6.1f} TFLOP/s of scan products", flush=True)
+                del keep
+            K.q38_gdn_set_chunk_scan_tensor_cores(1)
             if K.q38_device_error(1):
                 raise SystemExit("device-side wait gave up")
             continue

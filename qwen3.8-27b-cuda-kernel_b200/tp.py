@@ -207,7 +207,10 @@ class TPRunner:
         self.ab, self.qkv = f32(T, 2 * self.lv), f32(T, self.conv_dim)
         self.mixer, self.act = b16(T, max(self.nq * HD, self.lv * GD)), b16(T, self.inter)
         self.q16 = torch.empty((T, self.nq, HD), dtype=torch.float16, device="cuda")
-        self.split = f32(max(1, self.nq) * 256 * (HD + 2))  # up to 256 splits: one sequence must fill the GPU
+        # decode: one row, up to 256 splits (one sequence must fill the GPU); prefill: one row per token of a chunk with up
+        # to 16 splits, so that the few query tiles of a rank (one kv head) cut their keys over several CTAs
+        self.prefill_splits = 16
+        self.split = f32(max(1, self.nq) * max(256, T * self.prefill_splits) * (HD + 2))
         self.logits_local = f32(self.head_rows_max)
         self.gdn_scratch = f32(int(self.K.q38_gdn_chunk_scratch_floats(T, 1, max(1, self.lv))))
         sms = self.K.q38_num_sms()
@@ -290,7 +293,8 @@ class TPRunner:
                                           float(self.cfg["rope_theta"]), self.nq, self.nkv, pkg.ptr(self.q16), attn_i)
                 pkg.check(K.q38_qk_norm_rope_append(C.byref(qp), C.byref(batch), C.byref(self.kv), s))
                 ap = pkg.AttentionParams(pkg.ptr(self.q16), pkg.ptr(self.proj) + self.nq * HD * 2, self.proj_ld,
-                                         pkg.ptr(self.mixer), self.nq, self.nkv, attn_i, pkg.ptr(self.split), 256)
+                                         pkg.ptr(self.mixer), self.nq, self.nkv, attn_i, pkg.ptr(self.split),
+                                         256 if decode else self.prefill_splits, 1 if decode else self.T)
                 fn = K.q38_attention_decode if decode else K.q38_attention_prefill
                 pkg.check(fn(C.byref(ap), C.byref(batch), C.byref(self.kv), s))
                 attn_i += 1
