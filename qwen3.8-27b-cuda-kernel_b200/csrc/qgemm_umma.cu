@@ -26,10 +26,12 @@
 //   warp 0       raw producer (six copies per stage, one lane each);
 //   warp 1       stays converged; one elected lane issues tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32), four per
 //                k-group in one block (ATM) or one per k16 step, and tcgen05.commit per unit / per accumulator;
+//   warp 3       up to 128 tokens a second issuer (an MMA costs its issuing thread more time than the tensor pipe
+//                there): warp 1 takes the even units into accumulator 0, warp 3 the odd ones into accumulator 1;
+//                idle above that (it keeps the decode warps aligned to the TMEM lane quarters);
 //   warp 2       activation producer - the first thread that touches data of earlier kernels (griddepcontrol.wait);
 //                everything before it (set-up, TMEM allocation, weight prefetch and decode) overlaps the previous
 //                kernel's tail;
-//   warp 3       idle (keeps the decode warps aligned to the TMEM lane quarters);
 //   warps 4-19   decode: lane-owned slab bytes -> bf16(code * scale) in registers (bq_dequant.cuh) -> operand ring.
 //                ATM: a warp owns the TMEM lane quarter its index selects (32 of the tile's 128 columns = half a
 //                64-column block, all k); with two-group units it takes a whole unit quarter every other stage.
@@ -67,8 +69,7 @@ struct UCfg {
 #ifndef Q38_TMEM_UNITS_SMALL
 #define Q38_TMEM_UNITS_SMALL 6
 #endif
-  static constexpr int kUnits = ATM ? (TOK <= 64 ? Q38_TMEM_UNITS_SMALL : 4)
-                                    : (TOK <= 64 ? 3 : TOK <= 128 ? 2 : TOK <= 256 ? 3 : 2);
+  static constexpr int kUnits = ATM ? (TOK <= 64 ? Q38_TMEM_UNITS_SMALL : 4) : (TOK <= 128 ? 2 : TOK <= 256 ? 3 : 2);
   static constexpr int kXBytes = TOK * 128;  // activation k-slice [TOK][64] bf16
   static constexpr int kWBytes = ATM ? 0 : kSliceBytes;  // decoded slice held in shared memory
   static constexpr int kUnitBytes = kSpu * (kWBytes + kXBytes);
@@ -76,7 +77,15 @@ struct UCfg {
   static constexpr int kRawConsumers = ATM && kSpu == 2 ? kDecodeWarps / 2 : kDecodeWarps;  // warps that release a raw stage
   // tensor memory: accumulator [128 lanes][TOK columns] at column 0, then (ATM) the ring of decoded units, one
   // 64-wide k-group = 128 lanes x 32 columns of packed bf16 pairs
-  static constexpr int kACol0 = TOK < 32 ? 32 : TOK;
+  // Issuing one tcgen05.mma costs the issuing thread 40-60 cycles whatever the token count, which at 128 tokens and
+  // fewer is more than the MMA's time in the tensor pipe: two warps issue, each the units of its own parity into
+  // its own accumulator (the epilogue adds the two).
+  static constexpr int kIssuers = TOK <= 128 ? 2 : 1;
+  static constexpr int kAccCols = TOK < 32 ? 32 : TOK;  // columns of one accumulator
+  static constexpr int kACol0 = kIssuers * kAccCols;
+  // A slot's successive uses must all belong to one issuer: a parity wait cannot tell the fill it expects from the
+  // one before, which with an odd ring would be the other issuer's and possibly still outstanding.
+  static_assert(kUnits % kIssuers == 0, "operand ring length must be a multiple of the number of issuing warps");
   static constexpr int kUnitCols = kSpu * 32;
   static_assert(!ATM || kACol0 + kUnits * kUnitCols <= 512, "tensor memory columns");
   static constexpr int kLoOff = 0;
@@ -91,7 +100,7 @@ struct UCfg {
   static constexpr int kUnitOff = kStages * kStageBytes;
   static constexpr int kTailOff = kUnitOff + kUnits * kUnitBytes;
   static constexpr int kSmemBytes = 1024 + kTailOff + kTail;
-  static constexpr int kTmemCols = ATM ? 512 : (TOK < 32 ? 32 : TOK);
+  static constexpr int kTmemCols = ATM ? 512 : kIssuers * kAccCols;  // a power of two (32 ... 512)
   static constexpr int kMmaN = TOK < 256 ? TOK : 256;  // tokens per MMA instruction and per activation box
   static constexpr int kEpiChunks = TOK >= 64 ? 4 : 2;  // decode warps per TMEM lane quarter that run the epilogue
   static constexpr int kColsPerWarp = TOK / kEpiChunks;
@@ -261,7 +270,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       mbar_init(&op_full[s], C::kDecodeWarpsPerUnit + 1);  // the unit's decode warps + the activation copies' expect_tx
       mbar_init(&op_empty[s], 1);
     }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, C::kIssuers);
     mbar_init(acc_empty, kDecodeWarps);
     flags[0] = 0;
     flags[1] = 0;
@@ -355,16 +364,21 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         u += kg_b - kg_a;
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    // The warp stays converged and one elected lane issues; the serial work per unit is one barrier wait, 4 MMAs
-    // per slice with precomputed descriptors, and one commit, because at small TOK the tensor work per slice is
-    // shorter than any of those round trips.
+  } else if (warp == 1 || (C::kIssuers == 2 && warp == 3)) {
+    // ------------------------------ MMA issuers ------------------------------
+    // A warp stays converged and one elected lane issues. Its serial work per unit - one barrier wait, 4 MMAs per
+    // slice in one block, one commit - is what bounds the kernel at small TOK (the tensor work of a unit is shorter
+    // than any of these), so with two issuers warp 1 takes the even units into accumulator 0 and warp 3 the odd ones
+    // into accumulator 1, and ring positions are carried along instead of being derived from counters.
     {
       constexpr uint32_t idesc =
           (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(C::kMmaN >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+      constexpr int kI = C::kIssuers;
+      const int iss = kI == 2 ? (warp >> 1) : 0;
+      const uint32_t d_acc = tmem_base + uint32_t(iss * C::kAccCols);
       const uint64_t desc0 = smem_desc_sw128(smem_u32(units));
-      uint32_t uc = 0, seg = 0;
+      uint32_t seg = 0;
+      uint32_t uc0 = 0;  // units of all earlier segments
       bool alive = true;
       // Everything this warp waits for needs the activations, which the previous kernel of the stream produces: the
       // bounded waits below start counting only once that kernel is complete.
@@ -372,13 +386,18 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       for (long long u = u0; u < u1 && alive; ++seg) {
         const int kg_a = int(u % a.kg);
         const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+        const int nunits = (kg_b - kg_a + C::kSpu - 1) / C::kSpu;
         alive = __all_sync(0xffffffffu, wait_flag(acc_empty, (seg & 1) ^ 1, flags, 0x302));
         tc_fence_after();
         uint32_t accumulate = 0;
-        for (int g = kg_a; g < kg_b && alive; g += C::kSpu, ++uc) {
-          const int slot = uc % C::kUnits;
+        // this warp's first unit of the segment and its ring position
+        int i = kI == 2 ? int((uint32_t(iss) - uc0) & 1u) : 0;
+        int slot = int((uc0 + uint32_t(i)) % uint32_t(C::kUnits));
+        uint32_t par = ((uc0 + uint32_t(i)) / uint32_t(C::kUnits)) & 1u;
+        for (; i < nunits && alive; i += kI) {
+          const int g = kg_a + i * C::kSpu;
           const int nu = min(C::kSpu, kg_b - g);
-          alive = __all_sync(0xffffffffu, wait_flag(&op_full[slot], (uc / C::kUnits) & 1, flags, 0x303));
+          alive = __all_sync(0xffffffffu, wait_flag(&op_full[slot], par, flags, 0x303));
           if (!alive) break;
           tc_fence_after();
           const uint64_t da = desc0 + uint64_t((uint32_t(slot) * C::kUnitBytes) >> 4);
@@ -390,7 +409,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
 #pragma unroll
             for (int gi = 0; gi < C::kSpu; ++gi) {
               if (gi < nu) {
-                umma_group_ta(tmem_base, ta + uint32_t(gi * 32), b_lo + uint32_t((gi * C::kXBytes) >> 4), b_hi, idesc,
+                umma_group_ta(d_acc, ta + uint32_t(gi * 32), b_lo + uint32_t((gi * C::kXBytes) >> 4), b_hi, idesc,
                               accumulate);
                 accumulate = 1;
               }
@@ -403,7 +422,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                 for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
                   for (int nh = 0; nh < TOK / C::kMmaN; ++nh)
-                    umma_bf16(tmem_base + uint32_t(nh * C::kMmaN), da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
+                    umma_bf16(d_acc + uint32_t(nh * C::kMmaN), da + uint64_t((gi * kSliceBytes + ks * 32) >> 4),
                               dx + uint64_t((gi * C::kXBytes + nh * C::kMmaN * 128 + ks * 32) >> 4), idesc, accumulate);
                   accumulate = 1;
                 }
@@ -411,8 +430,14 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
             }
           }
           umma_commit(&op_empty[slot]);
+          slot += kI;
+          if (slot >= C::kUnits) {
+            slot -= C::kUnits;
+            par ^= 1u;
+          }
         }
-        umma_commit(acc_full);
+        umma_commit(acc_full);  // tracks this warp's MMAs only; the barrier counts one arrival per issuer
+        uc0 += uint32_t(nunits);
         u += kg_b - kg_a;
       }
     }
@@ -485,6 +510,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
     };
     // ring positions are carried along (slot + phase bit) instead of being derived from counters by division
     uint32_t seg = 0;
+    uint32_t units_done = 0;     // operand units produced so far (all segments): its parity names the issuing warp
     uint32_t stage_no = 0;       // raw stages consumed so far (all segments)
     int s = 0;                   // raw stage and the parity of its current use
     uint32_t s_par = 0;
@@ -503,6 +529,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       const int tile = item % a.tiles;          // weight tile
       const int row0 = (item / a.tiles) * TOK;  // first token of the token block
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
+      const uint32_t first_unit = units_done;
       for (int g = kg_a; g < kg_b; g += kGroupsPerStage) {
         const int ng = min(kGroupsPerStage, kg_b - g);
         const uint8_t* st = stages + (size_t)s * C::kStageBytes;
@@ -517,8 +544,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           const int ui = kNG == 2 ? ((dw >> 2) & 1) : (dw >> 2);
           const bool mine = kNG == 2 ? ((stage_no & 1u) == uint32_t(dw >> 3)) : true;
           if (mine) {
+            // Also a warp whose unit does not exist in a partial last stage waits for the stage before it releases
+            // it: an arrival that did not wait could be counted with the previous use of the stage (the warp may be
+            // a whole turn ahead of a slower one), and the producer would refill a stage that is still being read.
+            const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
             if (ui * kNG < ng) {
-              const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
               const int anb = quarter >> 1, fh = quarter & 1;
               int slot;
               uint32_t par;
@@ -656,6 +686,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         }
         ++stage_no;
         unit_at((ng + C::kSpu - 1) / C::kSpu, u_slot, u_par);
+        units_done += uint32_t((ng + C::kSpu - 1) / C::kSpu);
       }
 
       // ---- epilogue of this tile segment ----
@@ -675,6 +706,29 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       constexpr int kColsPerWarp = C::kColsPerWarp;
       const int col_base = cchunk * kColsPerWarp;
       constexpr int kTileFloats = TOK * kTileN;
+      // which accumulators this segment wrote: with two issuers, unit j of the kernel goes to accumulator j & 1, so a
+      // segment of one unit leaves the other accumulator with an earlier segment's sums
+      const bool acc0_live = C::kIssuers == 1 || units_done - first_unit >= 2u || (first_unit & 1u) == 0u;
+      const bool acc1_live = C::kIssuers == 2 && (units_done - first_unit >= 2u || (first_unit & 1u) == 1u);
+      // 16 accumulator columns of this thread's row: the sum over the issuers' accumulators
+      auto load_acc = [&](int col, float (&v)[16]) {
+        const uint32_t taddr = tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col);
+        uint32_t r[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+        if (acc0_live) {
+          tmem_ld16(taddr, r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        if constexpr (C::kIssuers == 2) {
+          if (acc1_live) {
+            tmem_ld16(taddr + uint32_t(C::kAccCols), r);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
+          }
+        }
+      };
 
       auto finish_chunk = [&](const float (&v)[16], int col0) {
         if (a.kind == Q38_EPI_RESIDUAL) {
@@ -724,11 +778,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         if (epi_active) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
-            uint32_t r[16];
             float v[16];
-            if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = got ? __uint_as_float(r[j]) : 0.0f;
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            if (got) load_acc(col_base + c0, v);
             finish_chunk(v, col_base + c0);
           }
         }
@@ -741,11 +794,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         if (epi_active) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
-            uint32_t r[16];
-            if (got) tmem_ld16(tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(col_base + c0), r);
+            float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              mine[(size_t)(col_base + c0 + j) * kTileN + n_row] = got ? __uint_as_float(r[j]) : 0.0f;
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            if (got) load_acc(col_base + c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mine[(size_t)(col_base + c0 + j) * kTileN + n_row] = v[j];
           }
         }
         tc_fence_before();

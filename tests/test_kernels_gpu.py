@@ -45,11 +45,12 @@ def test_dequantised_weights_are_bit_exact(bits):
 # ---------------------------------------------------------------------------------------------------
 # qgemm
 # ---------------------------------------------------------------------------------------------------
-def run_gemm_f32(a_dev, m, w, ws, config):
+def run_gemm_f32(a_dev, m, w, ws, config, sync=True):
     out = torch.empty((m, w.packed.n), dtype=torch.float32, device="cuda")
     ep = pkg.GemmEpilogue(pkg.EPI_STORE_F32, pkg.ptr(out), w.packed.n, 0, None, None, None, None, 0, 1e-6)
     pkg.check(K().q38_qgemm(pkg.ptr(a_dev), m, C.byref(w.desc), C.byref(ep), C.byref(ws) if ws else None, None, config))
-    torch.cuda.synchronize()
+    if sync:
+        torch.cuda.synchronize()
     return out
 
 
@@ -191,6 +192,45 @@ def test_qgemm_27b_shapes(n, k, bits):
         assert not (err > 1e-6 + 2e-3 * mag).any(), (m, float(err.max()))
         assert torch.equal(got, run_gemm_f32(a_dev, m, w, ws.desc, -1))
     sync_ok()
+
+
+@pytest.mark.parametrize("bits", [5, 8])
+def test_qgemm_even_cut_over_all_sms(bits):
+    """More than four tiles per SM (the LM head's regime): the tcgen05 kernel cuts the list of (tile, k-group) evenly
+    over the SMs, so segments begin and end anywhere inside a tile - partial stages, units of one k-group, segments
+    of a single unit - and the tiles' pieces meet in the workspace. 11 k-groups per tile make every remainder occur.
+    Each configuration against the oracle on a seeded subset of columns, both operand paths bit-identical, and twenty
+    launches back to back (each overlapping the tail of the one before) equal to a launch on its own."""
+    n, k = 76800, 704
+    g = torch.Generator(device="cuda").manual_seed(bits)
+    wt = torch.randn((n, k), generator=g, device="cuda") * 0.02
+    codes, scales = bq.quantize_absmax(wt, bits)
+    p = bq.pack(codes, scales, bits)
+    w = tl.DeviceBQ(p)
+    ws = tl.Workspace()
+    names = {K().q38_qgemm_config_name(c).decode(): c for c in range(K().q38_qgemm_num_configs())}
+    rng = np.random.default_rng(bits)
+    cols = np.sort(rng.choice(n, size=160, replace=False))
+    wd = bq.dequantize(codes[cols].cpu(), scales[cols].cpu()).numpy()
+    for m, tok in ((24, 32), (64, 64), (100, 128)):
+        a = tl.bf16_round(rng.standard_normal((m, k)))
+        want = np.zeros((m, len(cols)), np.float32)
+        tl.oracle().qgemm(a, wd, None, 3, out=want, ldo=len(cols))
+        mag = np.abs(a).astype(np.float64) @ np.abs(wd).astype(np.float64).T
+        a_dev = tl.to_dev_bf16(a)
+        outs = {}
+        for name in (f"tmem_t{tok}", f"umma_t{tok}"):
+            got = run_gemm_f32(a_dev, m, w, ws.desc, names[name])
+            err = np.abs(got[:, cols].cpu().numpy().astype(np.float64) - want)
+            assert not (err > 1e-6 + 2e-3 * mag).any(), (bits, m, name, float(err.max()))
+            outs[name] = got
+        assert torch.equal(outs[f"tmem_t{tok}"], outs[f"umma_t{tok}"]), (bits, m)
+        for name in (f"tmem_t{tok}", f"umma_t{tok}"):
+            for _ in range(20):
+                last = run_gemm_f32(a_dev, m, w, ws.desc, names[name], sync=False)
+            assert torch.equal(last, outs[name]), (bits, m, name, "back-to-back launches")
+    sync_ok()
+    assert int(ws.counters.abs().sum()) == 0, "tile counters must reset themselves"
 
 
 @pytest.mark.parametrize("bits", [4, 5, 8])
