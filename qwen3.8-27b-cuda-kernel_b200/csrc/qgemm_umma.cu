@@ -755,21 +755,29 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
           }
           return;
         }
+        // every value is finished before the first store: a shared-memory read placed after a store through a
+        // pointer it might alias is held back until that store has left, once per column
+        float x[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int col = col0 + j;
-          const float x = v[j] * rs_sm[col];
-          if (a.kind == Q38_EPI_SWIGLU) {
-            const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-            if ((lane & 1) == 0 && col < m_here && n_glob < n_lim)
-              static_cast<__nv_bfloat16*>(a.out)[(size_t)(row0 + col) * a.ldo + n_glob / 2] =
-                  __float2bfloat16_rn(silu_f(x) * other);
-          } else if (col < m_here && n_glob < n_lim) {
-            if (a.kind == Q38_EPI_STORE_BF16)
-              static_cast<__nv_bfloat16*>(a.out)[(size_t)(row0 + col) * a.ldo + n_glob] = __float2bfloat16_rn(x);
-            else
-              static_cast<float*>(a.out)[(size_t)(row0 + col) * a.ldo + n_glob] = x;
-          }
+        for (int j = 0; j < 16; ++j) x[j] = v[j] * rs_sm[col0 + j];
+        const bool n_ok = n_glob < n_lim;
+        if (a.kind == Q38_EPI_SWIGLU) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) x[j] = silu_f(x[j]) * __shfl_xor_sync(0xffffffffu, x[j], 1);
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + col0) * a.ldo + n_glob / 2;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if ((lane & 1) == 0 && col0 + j < m_here && n_ok) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(x[j]);
+        } else if (a.kind == Q38_EPI_STORE_BF16) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + col0) * a.ldo + n_glob;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (col0 + j < m_here && n_ok) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(x[j]);
+        } else {
+          float* dst = static_cast<float*>(a.out) + (size_t)(row0 + col0) * a.ldo + n_glob;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (col0 + j < m_here && n_ok) dst[(size_t)j * a.ldo] = x[j];
         }
       };
 
