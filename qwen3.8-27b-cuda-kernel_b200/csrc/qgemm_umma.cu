@@ -530,74 +530,81 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       const int row0 = (item / a.tiles) * TOK;  // first token of the token block
       const int kg_b = int(min((long long)a.kg, kg_a + (u1 - u)));
       const uint32_t first_unit = units_done;
-      for (int g = kg_a; g < kg_b; g += kGroupsPerStage) {
-        const int ng = min(kGroupsPerStage, kg_b - g);
-        const uint8_t* st = stages + (size_t)s * C::kStageBytes;
-        if constexpr (ATM) {
-          // A warp owns one TMEM lane quarter: 32 of the tile's 128 columns, i.e. half of a 64-column block (pairs
-          // j = 4 fh .. 4 fh + 3 of every slab: lo words 2 fh, 2 fh + 1), and decodes whole 64-wide k-groups of it.
-          // Two-group units: the stage's two units x four quarters occupy eight warps; warps 0-7 take the even
-          // stages and warps 8-15 the odd ones, so a warp pays its barrier round trips once per two k-groups and
-          // has two stage times for them. One-group units: sixteen warps = four k-groups x four quarters, every stage.
-          // Either way a warp's successive units are at most four apart (the ring holds four or more).
-          constexpr int kNG = C::kSpu;  // k-groups per warp and turn
-          const int ui = kNG == 2 ? ((dw >> 2) & 1) : (dw >> 2);
-          const bool mine = kNG == 2 ? ((stage_no & 1u) == uint32_t(dw >> 3)) : true;
-          if (mine) {
-            // Also a warp whose unit does not exist in a partial last stage waits for the stage before it releases
-            // it: an arrival that did not wait could be counted with the previous use of the stage (the warp may be
-            // a whole turn ahead of a slower one), and the producer would refill a stage that is still being read.
-            const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
-            if (ui * kNG < ng) {
-              const int anb = quarter >> 1, fh = quarter & 1;
-              int slot;
-              uint32_t par;
-              unit_at(ui, slot, par);
-              const uint32_t ta =
-                  tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(C::kACol0 + slot * C::kUnitCols);
-              bool free_slot = true;
+      if constexpr (ATM) {
+        // A warp owns one TMEM lane quarter: 32 of the tile's 128 columns, i.e. half of a 64-column block (pairs
+        // j = 4 fh .. 4 fh + 3 of every slab: lo words 2 fh, 2 fh + 1), and decodes whole 64-wide k-groups of it.
+        // Two-group units: a stage's two units x four quarters occupy eight warps; warps 0-7 take the even stages of
+        // the kernel and warps 8-15 the odd ones, so a warp pays its barrier round trips once per two k-groups and has
+        // two stage times for them. One-group units: sixteen warps = four k-groups x four quarters, every stage.
+        // The warp walks its own stages only; every stage before a segment's last is full, so the ring positions of
+        // its stage and unit follow from the segment's first ones by fixed steps (one wrap at most per step).
+        constexpr int kNG = C::kSpu;                      // k-groups per unit
+        constexpr int kUPS = kGroupsPerStage / kNG;       // units of a full stage
+        constexpr int kStep = kNG == 2 ? 2 : 1;           // distance between this warp's stages
+        static_assert(kUPS * kStep <= C::kUnits && kStep <= C::kStages, "one wrap per step");
+        const int ui = kNG == 2 ? ((dw >> 2) & 1) : (dw >> 2);
+        const int anb = quarter >> 1, fh = quarter & 1;
+        const int nst = (kg_b - kg_a + kGroupsPerStage - 1) / kGroupsPerStage;
+        const int j0 = kNG == 2 ? int((uint32_t(dw >> 3) - stage_no) & 1u) : 0;
+        // ring positions of this warp's first stage and unit of the segment
+        int ws = s + j0;
+        uint32_t ws_par = s_par;
+        if (ws >= C::kStages) {
+          ws -= C::kStages;
+          ws_par ^= 1u;
+        }
+        int slot = u_slot + kUPS * j0 + ui;
+        uint32_t par = u_par;
+        if (slot >= C::kUnits) {
+          slot -= C::kUnits;
+          par ^= 1u;
+        }
+        // byte offsets of this lane's words inside a stage (k-group e of the unit adds whole groups)
+        const uint32_t lo_off = uint32_t(C::kLoOff + (anb * kGroupsPerStage + ui * kNG) * G::kLoGroupBytes + lane * 16 + fh * 8);
+        const uint32_t hi_off = uint32_t(C::kHiOff + (anb * kGroupsPerStage + ui * kNG) * G::kHiGroupBytes);
+        const uint32_t sc_off = uint32_t(C::kScOff + (anb * kGroupsPerStage + ui * kNG) * G::kScGroupBytes + 16 * gl + 8 * fh);
+        bool alive = true;
+        for (int j = j0; j < nst && alive; j += kStep) {
+          const int ng = min(kGroupsPerStage, kg_b - kg_a - j * kGroupsPerStage);
+          const uint8_t* st = stages + (size_t)ws * C::kStageBytes;
+          // Also a warp whose unit does not exist in a partial last stage waits for the stage before it releases
+          // it: an arrival that did not wait could be counted with the previous use of the stage (the warp may be
+          // a whole turn ahead of a slower one), and the producer would refill a stage that is still being read.
+          alive = wait_flag(&raw_full[ws], ws_par, flags, 0x305);
+          if (alive && ui * kNG < ng) {
+            const uint32_t ta = tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(C::kACol0 + slot * C::kUnitCols);
 #pragma unroll
-              for (int e = 0; e < kNG; ++e) {
-                const int gi = ui * kNG + e;
-                const bool have = ok && gi < ng;  // a unit at the end of a segment may lack its second k-group
+            for (int e = 0; e < kNG; ++e) {
+              if (ui * kNG + e < ng) {  // a unit at the end of a segment may lack its second k-group
                 // raw words of the k-group: the lane's two lo words of this half for the four k16 slabs, the matching
                 // hi words, the four scales
                 uint2 lv[4];
                 uint32_t h0[4], h1[4];
                 uint32_t s2[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s2[i] = 0;
+                const uint8_t* lo_g = st + lo_off + e * G::kLoGroupBytes;
+                const uint8_t* hi_g = st + hi_off + e * G::kHiGroupBytes;
+                const uint2 sv = *reinterpret_cast<const uint2*>(st + sc_off + e * G::kScGroupBytes);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
-                  lv[k4] = make_uint2(0, 0);
+                  lv[k4] = *reinterpret_cast<const uint2*>(lo_g + k4 * 512);
                   h0[k4] = h1[k4] = 0;
-                }
-                if (have) {
-                  const int rslot = anb * kGroupsPerStage + gi;
-                  const uint8_t* lo_g = st + C::kLoOff + rslot * G::kLoGroupBytes + lane * 16 + fh * 8;
-                  const uint8_t* hi_g = st + C::kHiOff + rslot * G::kHiGroupBytes;
-                  const uint2 sv =
-                      *reinterpret_cast<const uint2*>(st + C::kScOff + rslot * G::kScGroupBytes + 16 * gl + 8 * fh);
-                  s2[0] = __byte_perm(sv.x, 0, 0x1010);
-                  s2[1] = __byte_perm(sv.x, 0, 0x3232);
-                  s2[2] = __byte_perm(sv.y, 0, 0x1010);
-                  s2[3] = __byte_perm(sv.y, 0, 0x3232);
-#pragma unroll
-                  for (int k4 = 0; k4 < 4; ++k4) {
-                    lv[k4] = *reinterpret_cast<const uint2*>(lo_g + k4 * 512);
-                    if constexpr (BITS == 5) {
-                      h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 128 + lane * 4) >> (8 * fh);
-                    } else if constexpr (BITS == 6) {
-                      h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 256 + lane * 8 + fh * 4);
-                    } else if constexpr (BITS == 8) {
-                      const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + k4 * 512 + lane * 16 + fh * 8);
-                      h0[k4] = hv.x;
-                      h1[k4] = hv.y;
-                    }
+                  if constexpr (BITS == 5) {
+                    h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 128 + lane * 4) >> (8 * fh);
+                  } else if constexpr (BITS == 6) {
+                    h0[k4] = *reinterpret_cast<const uint32_t*>(hi_g + k4 * 256 + lane * 8 + fh * 4);
+                  } else if constexpr (BITS == 8) {
+                    const uint2 hv = *reinterpret_cast<const uint2*>(hi_g + k4 * 512 + lane * 16 + fh * 8);
+                    h0[k4] = hv.x;
+                    h1[k4] = hv.y;
                   }
                 }
+                s2[0] = __byte_perm(sv.x, 0, 0x1010);
+                s2[1] = __byte_perm(sv.x, 0, 0x3232);
+                s2[2] = __byte_perm(sv.y, 0, 0x1010);
+                s2[3] = __byte_perm(sv.y, 0, 0x3232);
+                s2[4] = s2[5] = s2[6] = s2[7] = 0;
                 if (e == 0) {
-                  free_slot = wait_slot(slot, par);
+                  alive = wait_slot(slot, par);
                   tc_fence_after();
                 }
                 // rows 0-15 of the quarter (pairs j' = 0, 1), then rows 16-31 (j' = 2, 3): an mma A fragment per slab
@@ -608,24 +615,48 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                   const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
                   decode_fragment<BITS, 0>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
                 }
-                if (have && free_slot) tmem_st_16x128b_x8(ta + uint32_t(e * 32), f);
+                if (alive) tmem_st_16x128b_x8(ta + uint32_t(e * 32), f);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
                   const uint32_t lo[4] = {lv[k4].x, lv[k4].y, 0, 0};
                   const uint32_t hi[4] = {h0[k4], h1[k4], 0, 0};
                   decode_fragment<BITS, 1>(lo, hi, s2, dc, f[4 * k4], f[4 * k4 + 1], f[4 * k4 + 2], f[4 * k4 + 3]);
                 }
-                if (have && free_slot) tmem_st_16x128b_x8(ta + (16u << 16) + uint32_t(e * 32), f);
+                if (alive) tmem_st_16x128b_x8(ta + (16u << 16) + uint32_t(e * 32), f);
               }
-              tmem_wait_st();
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&op_full[slot]);
             }
+            tmem_wait_st();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_empty[s]);
+            if (lane == 0) mbar_arrive(&op_full[slot]);
           }
-        } else {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[ws]);
+          ws += kStep;
+          if (ws >= C::kStages) {
+            ws -= C::kStages;
+            ws_par ^= 1u;
+          }
+          slot += kUPS * kStep;
+          if (slot >= C::kUnits) {
+            slot -= C::kUnits;
+            par ^= 1u;
+          }
+        }
+        // the segment's stages and units, for the next segment's first positions
+        const uint32_t nun = uint32_t((kg_b - kg_a + kNG - 1) / kNG);
+        const uint32_t sn = uint32_t(s) + uint32_t(nst), un = uint32_t(u_slot) + nun;
+        s_par ^= (sn / uint32_t(C::kStages)) & 1u;
+        s = int(sn % uint32_t(C::kStages));
+        u_par ^= (un / uint32_t(C::kUnits)) & 1u;
+        u_slot = int(un % uint32_t(C::kUnits));
+        stage_no += uint32_t(nst);
+        units_done += nun;
+      } else {
+      for (int g = kg_a; g < kg_b; g += kGroupsPerStage) {
+        const int ng = min(kGroupsPerStage, kg_b - g);
+        const uint8_t* st = stages + (size_t)s * C::kStageBytes;
+        {
           const bool ok = wait_flag(&raw_full[s], s_par, flags, 0x305);
           const int g0 = C::kSpu == 2 ? 2 * half : half;  // first of this warp's two k-groups of the stage
           constexpr int kGStep = C::kSpu == 2 ? 1 : 2;      // distance to its second one
@@ -687,6 +718,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         ++stage_no;
         unit_at((ng + C::kSpu - 1) / C::kSpu, u_slot, u_par);
         units_done += uint32_t((ng + C::kSpu - 1) / C::kSpu);
+      }
       }
 
       // ---- epilogue of this tile segment ----
@@ -761,18 +793,74 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) x[j] = v[j] * rs_sm[col0 + j];
         const bool n_ok = n_glob < n_lim;
+        // bf16 results leave as pairs of neighbouring columns: two lanes that hold neighbouring columns exchange
+        // every other token, so that each stores 4 bytes for half of the tokens instead of 2 bytes for all of them.
+        // `bit` is the lane distance of the partner, `c` this lane's output column (even in the lower lane of a pair).
+        auto store_pairs = [&](int bit, int c, int c_lim, bool lane_on) {
+          __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + col0) * a.ldo;
+          const bool upper = (lane & bit) != 0;
+          const bool paired = (a.ldo & 1) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 3u) == 0;  // 4-byte aligned pairs
+          if (paired) {
+            const int c0p = upper ? c - 1 : c;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              const float mine = upper ? x[2 * jj + 1] : x[2 * jj];
+              const float theirs = __shfl_xor_sync(0xffffffffu, upper ? x[2 * jj] : x[2 * jj + 1], bit);
+              const int tok = 2 * jj + (upper ? 1 : 0);
+              const __nv_bfloat162 pr = upper ? __floats2bfloat162_rn(theirs, mine) : __floats2bfloat162_rn(mine, theirs);
+              if (lane_on && col0 + tok < m_here) {
+                __nv_bfloat16* d = base + (size_t)tok * a.ldo + c0p;
+                if (c0p + 1 < c_lim)
+                  *reinterpret_cast<__nv_bfloat162*>(d) = pr;
+                else if (c0p < c_lim)
+                  *d = pr.x;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (lane_on && col0 + j < m_here && c < c_lim) base[(size_t)j * a.ldo + c] = __float2bfloat16_rn(x[j]);
+          }
+        };
         if (a.kind == Q38_EPI_SWIGLU) {
+          // Lanes 2i / 2i + 1 hold the gate / up column of output column n / 2 for sixteen tokens. They split the tokens
+          // (the even lane takes the even ones): each sends the other what it needs and computes eight products, then
+          // lanes two apart (neighbouring output columns) exchange every other product and store column pairs.
+          const bool odd = (lane & 1) != 0;
+          float y[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) x[j] = silu_f(x[j]) * __shfl_xor_sync(0xffffffffu, x[j], 1);
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + col0) * a.ldo + n_glob / 2;
+          for (int jj = 0; jj < 8; ++jj) {
+            const float got_v = __shfl_xor_sync(0xffffffffu, odd ? x[2 * jj] : x[2 * jj + 1], 1);
+            y[jj] = odd ? silu_f(got_v) * x[2 * jj + 1] : silu_f(x[2 * jj]) * got_v;
+          }
+          const int c = n_glob / 2, c_lim = (n_lim + 1) / 2;
+          __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + col0) * a.ldo;
+          if ((a.ldo & 1) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 3u) == 0) {
+            const bool upper = (lane & 2) != 0;
+            const int c0p = upper ? c - 1 : c;
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if ((lane & 1) == 0 && col0 + j < m_here && n_ok) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(x[j]);
+            for (int q = 0; q < 4; ++q) {
+              const float theirs = __shfl_xor_sync(0xffffffffu, upper ? y[2 * q] : y[2 * q + 1], 2);
+              const int tok = 2 * (2 * q + (upper ? 1 : 0)) + (odd ? 1 : 0);
+              const __nv_bfloat162 pr =
+                  upper ? __floats2bfloat162_rn(theirs, y[2 * q + 1]) : __floats2bfloat162_rn(y[2 * q], theirs);
+              if (col0 + tok < m_here) {
+                __nv_bfloat16* d = base + (size_t)tok * a.ldo + c0p;
+                if (c0p + 1 < c_lim)
+                  *reinterpret_cast<__nv_bfloat162*>(d) = pr;
+                else if (c0p < c_lim)
+                  *d = pr.x;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              const int tok = 2 * jj + (odd ? 1 : 0);
+              if (col0 + tok < m_here && c < c_lim) base[(size_t)tok * a.ldo + c] = __float2bfloat16_rn(y[jj]);
+            }
+          }
         } else if (a.kind == Q38_EPI_STORE_BF16) {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + col0) * a.ldo + n_glob;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (col0 + j < m_here && n_ok) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(x[j]);
+          store_pairs(1, n_glob, n_lim, true);
         } else {
           float* dst = static_cast<float*>(a.out) + (size_t)(row0 + col0) * a.ldo + n_glob;
 #pragma unroll
