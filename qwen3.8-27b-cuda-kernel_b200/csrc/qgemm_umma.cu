@@ -131,6 +131,7 @@ struct UmmaArgs {
   int items;       // tiles * mblocks
   long long units; // items * kg
   int split;
+  int cps;         // split with every CTA inside one tile: CTAs per tile (grid = tiles * cps); 0 otherwise
   DecodeConsts dc;
 };
 
@@ -766,7 +767,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         if (a.kind == Q38_EPI_RESIDUAL) {
           // the old values are requested four at a time before the first new one of the four is stored: a load
           // placed after a store to the same array has to wait for it, and the chunk took sixteen round trips to memory
-          constexpr int kRG = 4;
+          constexpr int kRG = 8;
           float rv[kRG];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -887,6 +888,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
       } else {
         // stream-K: publish this CTA's partial accumulator [token][128 n], then the last arriver reduces
         float* mine = a.ws + ((size_t)cta * 2 + (kg_a != 0 ? 0 : 1)) * kTileFloats;
+        // with one 16-column chunk per warp the thread's own partial sums stay in registers for the reduction
+        constexpr bool kKeepOwn = kColsPerWarp == 16;
+        float own[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) own[j] = 0.0f;
         if (epi_active) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
@@ -896,21 +902,36 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
             if (got) load_acc(col_base + c0, v);
 #pragma unroll
             for (int j = 0; j < 16; ++j) mine[(size_t)(col_base + c0 + j) * kTileN + n_row] = v[j];
+            if constexpr (kKeepOwn) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) own[j] = v[j];
+            }
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty);
-        __threadfence();
+        // Publication: the CTA's stores are ordered before the barrier, and the one thread that then counts the CTA in
+        // fences on both sides of its atomic (the fence is cumulative over what the barrier made visible to it), so
+        // whoever sees the full count also sees every piece.
         named_bar_sync(1, kDecodeThreads);
+        // the CTAs that hold pieces of this tile: c_first .. c_last; the first of them may have started before the tile
         const long long t_begin = (long long)tile * a.kg, t_end = t_begin + a.kg;
-        int c_first = int(t_begin * grid / a.units);
-        while (c_first > 0 && u_begin(a, c_first, grid) > t_begin) --c_first;
-        while (u_begin(a, c_first + 1, grid) <= t_begin) ++c_first;
-        int c_last = c_first;
-        while (c_last + 1 < grid && u_begin(a, c_last + 1, grid) < t_end) ++c_last;
+        int c_first, c_last;
+        if (a.cps > 0) {  // every CTA inside one tile: no 64-bit divisions
+          c_first = tile * a.cps;
+          c_last = c_first + a.cps - 1;
+        } else {
+          c_first = int(t_begin * grid / a.units);
+          while (c_first > 0 && u_begin(a, c_first, grid) > t_begin) --c_first;
+          while (u_begin(a, c_first + 1, grid) <= t_begin) ++c_first;
+          c_last = c_first;
+          while (c_last + 1 < grid && u_begin(a, c_last + 1, grid) < t_end) ++c_last;
+        }
         if (et == 0) {
+          __threadfence();
           const int prev = atomicAdd(&a.counters[tile], 1);
+          __threadfence();
           const int last = prev == c_last - c_first;
           if (last) a.counters[tile] = 0;
           flags[1] = last;
@@ -918,14 +939,21 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
         named_bar_sync(1, kDecodeThreads);
         run_epilogue = flags[1] != 0;
         if (run_epilogue && epi_active) {
-          __threadfence();
 #pragma unroll 1
           for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
             float v[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            // in CTA order (the sum is the same whichever CTA arrives last); this CTA's own piece comes from registers
             for (int c = c_first; c <= c_last; ++c) {
-              const float* src = a.ws + ((size_t)c * 2 + (u_begin(a, c, grid) > t_begin ? 0 : 1)) * kTileFloats;
+              if (kKeepOwn && c == cta) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += own[j];
+                continue;
+              }
+              // a piece that begins inside the tile lies in its CTA's first buffer, one that begins with it in the second
+              const bool inside = a.cps > 0 ? c != c_first : u_begin(a, c, grid) > t_begin;
+              const float* src = a.ws + ((size_t)c * 2 + (inside ? 0 : 1)) * kTileFloats;
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)(col_base + c0 + j) * kTileN + n_row);
             }
@@ -1029,6 +1057,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, int mblocks, const q38_bq_weig
     if (!have_ws || ws->partial_floats < (size_t)a.tiles * s * 2 * TOK * kTileN) s = 1;
     grid = a.tiles * s;
     a.split = s > 1;
+    a.cps = s > 1 ? s : 0;
   } else {
     grid = sms;
     a.split = TOK <= 128 && have_ws && ws->partial_floats >= (size_t)grid * 2 * TOK * kTileN;
