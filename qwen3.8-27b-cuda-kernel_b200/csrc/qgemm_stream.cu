@@ -80,6 +80,7 @@ struct StreamArgs {
   int tiles, kg;
   long long units;
   int split;
+  int cps;  // split with every CTA inside one tile: CTAs per tile (grid = tiles * cps); 0 otherwise
   DecodeConsts dc;
 };
 
@@ -276,17 +277,28 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
       constexpr int kTileFloats = C::kMpad * kTileN;
       float* mine = a.ws + ((size_t)cta * 2 + (kg_a != 0 ? 0 : 1)) * kTileFloats;
       for (int i = tid; i < kTileFloats; i += kConsumers) mine[i] = csm[(i >> 7) * kLdc + (i & 127)];
-      __threadfence();
+      // Publication: the CTA's stores are ordered before the barrier, and the one thread that then counts the CTA in
+      // fences on both sides of its atomic (the fence is cumulative over what the barrier made visible to it), so
+      // whoever sees the full count also sees every piece.
       named_bar_sync(1, kConsumers);
-      // contributors of this tile: CTAs whose unit range intersects [tile * kg, (tile + 1) * kg)
+      // contributors of this tile: CTAs whose unit range intersects [tile * kg, (tile + 1) * kg); the first of them
+      // begins at or before the tile (this piece is the one in its second buffer), the others inside it
       const long long t_begin = (long long)tile * a.kg, t_end = t_begin + a.kg;
-      int c_first = int(t_begin * grid / a.units);
-      while (c_first > 0 && cta_begin(a, c_first, grid) > t_begin) --c_first;
-      while (cta_begin(a, c_first + 1, grid) <= t_begin) ++c_first;
-      int c_last = c_first;
-      while (c_last + 1 < grid && cta_begin(a, c_last + 1, grid) < t_end) ++c_last;
+      int c_first, c_last;
+      if (a.cps > 0) {  // every CTA inside one tile: no 64-bit divisions
+        c_first = tile * a.cps;
+        c_last = c_first + a.cps - 1;
+      } else {
+        c_first = int(t_begin * grid / a.units);
+        while (c_first > 0 && cta_begin(a, c_first, grid) > t_begin) --c_first;
+        while (cta_begin(a, c_first + 1, grid) <= t_begin) ++c_first;
+        c_last = c_first;
+        while (c_last + 1 < grid && cta_begin(a, c_last + 1, grid) < t_end) ++c_last;
+      }
       if (tid == 0) {
+        __threadfence();
         const int prev = atomicAdd(&a.counters[tile], 1);
+        __threadfence();
         const int last = prev == c_last - c_first;
         if (last) a.counters[tile] = 0;
         flags[1] = last;
@@ -294,11 +306,10 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
       named_bar_sync(1, kConsumers);
       run_epilogue = flags[1] != 0;
       if (run_epilogue) {
-        __threadfence();
         for (int i = tid; i < kTileFloats; i += kConsumers) {
           float sum = 0.0f;
           for (int c = c_first; c <= c_last; ++c) {
-            const int which = cta_begin(a, c, grid) > t_begin ? 0 : 1;
+            const int which = c != c_first ? 0 : 1;  // c_first begins at or before the tile: its second buffer
             sum += __ldcg(a.ws + ((size_t)c * 2 + which) * kTileFloats + i);
           }
           csm[(i >> 7) * kLdc + (i & 127)] = sum;
@@ -418,6 +429,7 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
     if (!have_ws || ws->partial_floats < (size_t)a.tiles * s * 2 * C::kMpad * kTileN) s = 1;
     grid = a.tiles * s;
     a.split = s > 1;
+    a.cps = s > 1 ? s : 0;
   } else {
     grid = sms;
     a.split = have_ws && ws->partial_floats >= (size_t)grid * 2 * C::kMpad * kTileN;

@@ -951,9 +951,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap xmap, const UmmaArgs a) {
                 for (int j = 0; j < 16; ++j) v[j] += own[j];
                 continue;
               }
-              // a piece that begins inside the tile lies in its CTA's first buffer, one that begins with it in the second
-              const bool inside = a.cps > 0 ? c != c_first : u_begin(a, c, grid) > t_begin;
-              const float* src = a.ws + ((size_t)c * 2 + (inside ? 0 : 1)) * kTileFloats;
+              // c_first begins at or before the tile (this piece is in its second buffer), the others inside it
+              const float* src = a.ws + ((size_t)c * 2 + (c != c_first ? 0 : 1)) * kTileFloats;
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)(col_base + c0 + j) * kTileN + n_row);
             }
