@@ -80,6 +80,23 @@ typedef struct q38_bq_weight {
 #define Q38_EPI_SWIGLU 1     /* out[i] = bf16(silu(C[2i] * rs) * C[2i+1] * rs) */
 #define Q38_EPI_RESIDUAL 2   /* residual += C; xbf = bf16(residual); partials_out = sum of squares / 128 cols */
 #define Q38_EPI_STORE_F32 3  /* out = C * rs */
+/* Tensor parallelism, row-parallel projections of up to 16 tokens: C is this rank's partial product. The GEMM kernel
+ * itself stores each finished 128-column tile into every rank's receive buffer (plain peer stores over NVLink), raises
+ * a per-tile flag there, waits - bounded - for the other ranks' flags in its own memory, sums the pieces in rank order
+ * (every rank gets the same bits) and then runs the Residual epilogue on the sum. No counterpart in the reference
+ * (single GPU); replaces the all-reduce a host would otherwise place between q38_qgemm and q38_residual_update. */
+#define Q38_EPI_ALLREDUCE_RESIDUAL 4
+#define Q38_MAX_PEERS 8
+#define Q38_ALLREDUCE_ROWS 16
+typedef struct q38_peer_allreduce {
+  int world, rank;
+  /* rank r's receive buffer as mapped into this process, [2][world][Q38_ALLREDUCE_ROWS][n] floats (two buffers used in
+   * turn), and its flags, [n / 128][world] words; entry `rank` is this rank's own memory. All zero before first use. */
+  float* recv[Q38_MAX_PEERS];
+  unsigned int* flags[Q38_MAX_PEERS];
+  unsigned int* seq;       /* this rank's call counters, [n / 128] words, zero before first use */
+  unsigned int poll_limit; /* polls of a flag before the wait gives up and sets q38_device_error(); 0 = 2^22 */
+} q38_peer_allreduce;
 typedef struct q38_gemm_epilogue {
   int kind;
   void* out;
@@ -91,6 +108,7 @@ typedef struct q38_gemm_epilogue {
   const float* partials_in; /* rs = rsqrt(sum(partials_in[row]) / hidden + eps); NULL = 1 */
   int hidden;
   float eps;
+  const q38_peer_allreduce* allreduce; /* Q38_EPI_ALLREDUCE_RESIDUAL only; NULL otherwise */
 } q38_gemm_epilogue;
 
 typedef struct q38_gemm_workspace {
@@ -136,6 +154,15 @@ int q38_embed(const q38_bf16* table, const int32_t* tokens, int m, int hidden, f
  * (Q38_EPI_STORE_F32) that are summed over the ranks first. No counterpart in the reference (single GPU). */
 int q38_residual_update(const float* delta, int m, int hidden, float* residual, q38_bf16* xbf, float* partials,
                         void* stream);
+
+/* Device memory that other processes of the node can map (buffers and flags of Q38_EPI_ALLREDUCE_RESIDUAL): allocation
+ * (zero-filled), the 64-byte handle a peer process opens, opening and closing a peer's handle. The handles travel
+ * through whatever the host uses between its ranks. One process per GPU; peer access is enabled on opening. */
+int q38_peer_alloc(size_t bytes, void** ptr);
+int q38_peer_free(void* ptr);
+int q38_peer_export(void* ptr, unsigned char handle[64]);
+int q38_peer_open(const unsigned char handle[64], void** ptr);
+int q38_peer_close(void* ptr);
 
 /* Packs rows rows[0..n) of the step's LM-head inputs (bf16 hidden rows x [M][hidden] and their norm partial sums
  * [M][hidden / 128]) into rows 0..n-1 of x_out / partials_out: the last-token rows of the sequences that sample in a

@@ -45,10 +45,20 @@ class BQWeight(C.Structure):
                 ("k", C.c_int), ("rows", C.c_int)]
 
 
+MAX_PEERS, ALLREDUCE_ROWS = 8, 16
+
+
+class PeerAllreduce(C.Structure):
+    """q38_peer_allreduce: the ranks' receive buffers and flags as mapped into this process."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * MAX_PEERS),
+                ("flags", C.c_void_p * MAX_PEERS), ("seq", C.c_void_p), ("poll_limit", C.c_uint)]
+
+
 class GemmEpilogue(C.Structure):
     _fields_ = [("kind", C.c_int), ("out", C.c_void_p), ("ldo", C.c_int), ("n_store", C.c_int),
                 ("residual", C.c_void_p), ("xbf", C.c_void_p), ("partials_out", C.c_void_p),
-                ("partials_in", C.c_void_p), ("hidden", C.c_int), ("eps", C.c_float)]
+                ("partials_in", C.c_void_p), ("hidden", C.c_int), ("eps", C.c_float),
+                ("allreduce", C.POINTER(PeerAllreduce))]
 
 
 class GemmWorkspace(C.Structure):
@@ -98,7 +108,7 @@ class SamplingArgs(C.Structure):
                 ("logprob_out", C.c_void_p)]
 
 
-EPI_STORE_BF16, EPI_SWIGLU, EPI_RESIDUAL, EPI_STORE_F32 = 0, 1, 2, 3
+EPI_STORE_BF16, EPI_SWIGLU, EPI_RESIDUAL, EPI_STORE_F32, EPI_ALLREDUCE_RESIDUAL = 0, 1, 2, 3, 4
 KV_INT8, KV_BF16 = 0, 1
 
 # every entry point include/q38_kernels.h declares, with its ctypes signature
@@ -116,6 +126,11 @@ KERNEL_API = {
     "q38_embed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "q38_residual_update": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "q38_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "q38_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "q38_peer_free": (C.c_int, [C.c_void_p]),
+    "q38_peer_export": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "q38_peer_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "q38_peer_close": (C.c_int, [C.c_void_p]),
     "q38_qk_norm_rope_append": (C.c_int, [C.POINTER(QkNormRopeParams), C.POINTER(BatchDesc), C.POINTER(KvCacheDesc),
                                           C.c_void_p]),
     "q38_attention_decode_splits": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),

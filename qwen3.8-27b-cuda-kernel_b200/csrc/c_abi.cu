@@ -146,3 +146,46 @@ extern "C" size_t q38_kv_page_bytes(int dtype, int kv_heads) {
   return dtype == Q38_KV_INT8 ? 2 * size_t(kv_heads) * Q38_PAGE_TOKENS * (Q38_HEAD_DIM + 4 * 2)
                               : 2 * size_t(kv_heads) * Q38_PAGE_TOKENS * Q38_HEAD_DIM * 2;
 }
+
+// ---- device memory shared between the processes of one node (tensor-parallel all-reduce buffers) -------------------
+extern "C" int q38_peer_alloc(size_t bytes, void** ptr) {
+  Q38_REQUIRE(ptr && bytes > 0, "peer_alloc: null argument");
+  void* p = nullptr;
+  Q38_CUDA_OK(cudaMalloc(&p, bytes));
+  const cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) {
+    (void)cudaFree(p);
+    Q38_CUDA_OK(e);
+  }
+  *ptr = p;
+  return Q38_OK;
+}
+
+extern "C" int q38_peer_free(void* ptr) {
+  if (ptr) Q38_CUDA_OK(cudaFree(ptr));
+  return Q38_OK;
+}
+
+extern "C" int q38_peer_export(void* ptr, unsigned char handle[64]) {
+  Q38_REQUIRE(ptr && handle, "peer_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  Q38_CUDA_OK(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle, &h, 64);
+  return Q38_OK;
+}
+
+extern "C" int q38_peer_open(const unsigned char handle[64], void** ptr) {
+  Q38_REQUIRE(ptr && handle, "peer_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* p = nullptr;
+  Q38_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = p;
+  return Q38_OK;
+}
+
+extern "C" int q38_peer_close(void* ptr) {
+  if (ptr) Q38_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return Q38_OK;
+}

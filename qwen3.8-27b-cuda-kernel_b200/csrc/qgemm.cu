@@ -107,8 +107,18 @@ extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const
   Q38_REQUIRE(w->lo && w->scales && (w->bits == 4 || w->hi), "qgemm: missing weight plane");
   Q38_REQUIRE(config >= -1 && config < kNumConfigs, "qgemm: config %d out of range", config);
   Q38_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0, "qgemm: A must be 16-byte aligned");
-  if (ep->kind == Q38_EPI_RESIDUAL) {
+  if (ep->kind == Q38_EPI_RESIDUAL || ep->kind == Q38_EPI_ALLREDUCE_RESIDUAL) {
     Q38_REQUIRE(ep->residual && ep->xbf && ep->partials_out, "qgemm: Residual epilogue needs residual/xbf/partials");
+    if (ep->kind == Q38_EPI_ALLREDUCE_RESIDUAL) {
+      const q38_peer_allreduce* ar = ep->allreduce;
+      Q38_REQUIRE(ar != nullptr, "qgemm: the all-reduce epilogue needs its peer description");
+      Q38_REQUIRE(m <= Q38_ALLREDUCE_ROWS, "qgemm: the all-reduce epilogue serves up to %d tokens, got %d", Q38_ALLREDUCE_ROWS, m);
+      Q38_REQUIRE(ar->world >= 1 && ar->world <= Q38_MAX_PEERS && ar->rank >= 0 && ar->rank < ar->world && ar->seq,
+                  "qgemm: all-reduce world %d rank %d", ar->world, ar->rank);
+      for (int r = 0; r < ar->world; ++r)
+        Q38_REQUIRE(ar->recv[r] && ar->flags[r] && (reinterpret_cast<uintptr_t>(ar->recv[r]) & 15) == 0,
+                    "qgemm: all-reduce buffers of rank %d", r);
+    }
   } else {
     Q38_REQUIRE(ep->kind >= 0 && ep->kind <= 3 && ep->out && ep->ldo > 0, "qgemm: epilogue output");
   }
@@ -118,13 +128,15 @@ extern "C" int q38_qgemm(const q38_bf16* a, int m, const q38_bq_weight* w, const
     if (t >= 0 && t < kNumConfigs) config = t;
   }
   if (config < 0) config = auto_config(m, *w, ws);
+  Q38_REQUIRE(ep->kind != Q38_EPI_ALLREDUCE_RESIDUAL || !kConfigs[config].umma,
+              "qgemm: the all-reduce epilogue exists in the streaming kernel only (configurations stream_*)");
   const int tm = kConfigs[config].tile_m;
   const cudaStream_t s = as_stream(stream);
   const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(a);
   for (int r0 = 0; r0 < m; r0 += tm) {
     const int rows = std::min(tm, m - r0);
     q38_gemm_epilogue e = *ep;
-    if (e.kind == Q38_EPI_RESIDUAL) {
+    if (e.kind == Q38_EPI_RESIDUAL || e.kind == Q38_EPI_ALLREDUCE_RESIDUAL) {
       e.residual += (size_t)r0 * w->n;
       e.xbf += (size_t)r0 * w->n;
       e.partials_out += (size_t)r0 * (w->n / 128);

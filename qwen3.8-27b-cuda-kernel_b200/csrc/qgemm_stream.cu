@@ -60,6 +60,15 @@ struct Cfg {
   static_assert(kStages >= 2, "pipeline needs two stages");
 };
 
+// Q38_EPI_ALLREDUCE_RESIDUAL: the ranks' buffers as this process sees them (entry `rank` is local memory)
+struct AllreduceArgs {
+  int world, rank;
+  float* recv[Q38_MAX_PEERS];
+  unsigned int* flags[Q38_MAX_PEERS];
+  unsigned int* seq;
+  unsigned int poll_limit;
+};
+
 struct StreamArgs {
   const uint8_t* lo;
   const uint8_t* hi;
@@ -82,7 +91,17 @@ struct StreamArgs {
   int split;
   int cps;  // split with every CTA inside one tile: CTAs per tile (grid = tiles * cps); 0 otherwise
   DecodeConsts dc;
+  AllreduceArgs ar;
 };
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ long long cta_begin(const StreamArgs& a, int cta, int grid) {
   if (a.split) return (long long)cta * a.units / grid;
@@ -318,6 +337,57 @@ qgemm_stream_kernel(const __grid_constant__ CUtensorMap xmap, const StreamArgs a
       named_bar_sync(1, kConsumers);
     }
 
+    if (run_epilogue && a.kind == Q38_EPI_ALLREDUCE_RESIDUAL) {
+      // ---- sum of this tile over the tensor-parallel ranks, inside the GEMM ----
+      // Push: every rank stores its finished tile rows into slot `rank` of every rank's receive buffer (plain stores
+      // to peer memory; its own buffer included), fences, and raises flag [tile][rank] there to the call's sequence
+      // number. Pull: it waits until all flags [tile][*] in its own memory have reached that number - a bounded wait
+      // that records an error and goes on - and adds the pieces in rank order, so every rank holds the same bits.
+      // Two buffers are used in turn: a rank can be one call ahead of another at most (it needs the other's flag of
+      // the call before), so the buffer it writes next is one the other has finished reading.
+      __shared__ unsigned int ar_seq;
+      const AllreduceArgs& ar = a.ar;
+      if (tid == 0) ar_seq = ar.seq[tile] + 1u;
+      named_bar_sync(1, kConsumers);
+      const unsigned int seq = ar_seq;
+      const size_t slot_floats = (size_t)Q38_ALLREDUCE_ROWS * a.n;
+      const size_t buf_off = (size_t)(seq & 1u) * ar.world * slot_floats;
+      const int col = tile * kTileN + 4 * lane;
+      for (int m = warp; m < a.m; m += kConsumerWarps) {
+        const float4 cv = *reinterpret_cast<const float4*>(csm + m * kLdc + 4 * lane);
+        const size_t off = buf_off + (size_t)ar.rank * slot_floats + (size_t)m * a.n + col;
+        for (int p = 0; p < ar.world; ++p) *reinterpret_cast<float4*>(ar.recv[p] + off) = cv;
+      }
+      __threadfence_system();
+      named_bar_sync(1, kConsumers);
+      if (tid == 0) ar.seq[tile] = seq;
+      if (tid < ar.world) {
+        st_release_sys(ar.flags[tid] + (size_t)tile * ar.world + ar.rank, seq);
+        const unsigned int* mine = ar.flags[ar.rank] + (size_t)tile * ar.world + tid;
+        const unsigned int limit = ar.poll_limit ? ar.poll_limit : (1u << 22);
+        bool seen = false;
+        for (unsigned int i = 0; i < limit && !seen; ++i) {
+          seen = int(ld_acquire_sys(mine) - seq) >= 0;
+          if (!seen) __nanosleep(32);
+        }
+        if (!seen) report_error(0x120);
+      }
+      named_bar_sync(1, kConsumers);
+      for (int m = warp; m < a.m; m += kConsumerWarps) {
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int p = 0; p < ar.world; ++p) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(ar.recv[ar.rank] + buf_off + (size_t)p * slot_floats +
+                                                                  (size_t)m * a.n + col));
+          sum.x += v.x;
+          sum.y += v.y;
+          sum.z += v.z;
+          sum.w += v.w;
+        }
+        *reinterpret_cast<float4*>(csm + m * kLdc + 4 * lane) = sum;
+      }
+      named_bar_sync(1, kConsumers);
+    }
+
     if (run_epilogue) {
       const int n0 = tile * kTileN + 4 * lane;
       const int n_lim = a.n_store > 0 ? a.n_store : a.n;
@@ -414,6 +484,17 @@ int launch_one(const __nv_bfloat16* a_ptr, int m, const q38_bq_weight& w, const 
   a.partials_in = ep.partials_in;
   a.hidden = ep.hidden;
   a.eps = ep.eps;
+  if (ep.kind == Q38_EPI_ALLREDUCE_RESIDUAL) {
+    const q38_peer_allreduce& ar = *ep.allreduce;
+    a.ar.world = ar.world;
+    a.ar.rank = ar.rank;
+    for (int r = 0; r < ar.world; ++r) {
+      a.ar.recv[r] = ar.recv[r];
+      a.ar.flags[r] = ar.flags[r];
+    }
+    a.ar.seq = ar.seq;
+    a.ar.poll_limit = ar.poll_limit;
+  }
   a.tiles = w.n / kTileN;
   a.kg = w.k / 64;
   a.units = (long long)a.tiles * a.kg;

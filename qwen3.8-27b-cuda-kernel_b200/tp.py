@@ -133,13 +133,77 @@ class _DevBQ:
         self.desc = pkg.BQWeight(pkg.ptr(self.lo), pkg.ptr(self.hi), pkg.ptr(self.sc), p.bits, p.n, p.k, self.rows)
 
 
+class PeerBuffers:
+    """Receive buffers, flags and call counters of the all-reduce that runs inside the row-parallel GEMM
+    (Q38_EPI_ALLREDUCE_RESIDUAL): allocated by the library so that other processes can map them, the handles exchanged
+    over `dist`, every peer's memory opened here. `dist=None`: a single rank, which pushes to and pulls from itself."""
+
+    def __init__(self, pkg, hidden: int, rank: int, world: int, dist=None, poll_limit: int = 0):
+        assert 1 <= world <= pkg.MAX_PEERS and hidden % 128 == 0
+        self.pkg, self.K, self.world, self.rank = pkg, pkg.kernels(), world, rank
+        tiles = hidden // 128
+        sizes = (2 * world * pkg.ALLREDUCE_ROWS * hidden * 4, tiles * world * 4)
+        self.own = []
+        for nbytes in sizes + (tiles * 4,):
+            ptr = C.c_void_p()
+            pkg.check(self.K.q38_peer_alloc(nbytes, C.byref(ptr)))
+            self.own.append(ptr.value)
+        handles = []
+        for ptr in self.own[:2]:
+            h = C.create_string_buffer(64)
+            pkg.check(self.K.q38_peer_export(ptr, h))
+            handles.append(h.raw)
+        everyone = [None] * world
+        if dist is not None and world > 1:
+            dist.all_gather_object(everyone, handles)
+        else:
+            everyone[rank] = handles
+        self.opened = []
+        self.absent = []  # world > 1 without a group (tests of the bounded wait): local stand-ins nobody ever writes
+        self.desc = pkg.PeerAllreduce()
+        self.desc.world, self.desc.rank, self.desc.seq, self.desc.poll_limit = world, rank, self.own[2], poll_limit
+        for r in range(world):
+            if r == rank:
+                self.desc.recv[r], self.desc.flags[r] = self.own[0], self.own[1]
+                continue
+            for which in range(2):
+                ptr = C.c_void_p()
+                if everyone[r] is None:
+                    pkg.check(self.K.q38_peer_alloc(sizes[which], C.byref(ptr)))
+                    self.absent.append(ptr.value)
+                else:
+                    pkg.check(self.K.q38_peer_open(everyone[r][which], C.byref(ptr)))
+                    self.opened.append(ptr.value)
+                if which == 0:
+                    self.desc.recv[r] = ptr.value
+                else:
+                    self.desc.flags[r] = ptr.value
+        if dist is not None and world > 1:
+            dist.barrier()  # nobody pushes before everybody has its buffers mapped
+
+    def close(self, dist=None):
+        """Unmaps the peers' memory, then (after a barrier: nobody may still be writing here) frees this rank's."""
+        for ptr in self.opened:
+            self.K.q38_peer_close(ptr)
+        self.opened = []
+        if dist is not None and self.world > 1:
+            dist.barrier()
+        for ptr in self.own + self.absent:
+            self.K.q38_peer_free(ptr)
+        self.own, self.absent = [], []
+
+
 class TPRunner:
-    """One request, sharded over `dist`'s ranks (dist=None: a single rank, the same code path without all-reduce)."""
+    """One request, sharded over `dist`'s ranks (dist=None: a single rank, the same code path without all-reduce).
+    `fused_allreduce`: steps of up to 16 tokens sum the row-parallel projections inside the GEMM kernel, over peer
+    memory (PeerBuffers), instead of NCCL all-reduce + q38_residual_update."""
 
     def __init__(self, pkg, model_path, rank: int = 0, world: int = 1, dist=None, max_tokens: int = 512,
-                 max_context: int = 4096):
+                 max_context: int = 4096, fused_allreduce: bool = False, poll_limit: int = 0):
         self.pkg, self.K, self.dist = pkg, pkg.kernels(), dist if world > 1 else None
         self.rank, self.world = rank, world
+        self.peers = None
+        self._fused, self._poll_limit = fused_allreduce, poll_limit
         f = bq.Q38File(model_path)
         cfg = self.cfg = f.config
         plan = self.plan = rank_plan(cfg, rank, world)
@@ -218,7 +282,9 @@ class TPRunner:
         self.ws_counters = torch.zeros(65536, dtype=torch.int32, device="cuda")
         self.ws = pkg.GemmWorkspace(pkg.ptr(self.ws_partials), self.ws_partials.numel(), pkg.ptr(self.ws_counters), 65536)
         self.gdn_dims = pkg.GdnDims(self.lk, self.lv, self.conv_dim, self.proj_ld)
-        self.reduce_calls = 0
+        self.reduce_calls = self.fused_calls = 0
+        if self._fused:
+            self.peers = PeerBuffers(pkg, H, rank, world, self.dist, self._poll_limit)
         # step inputs live in fixed device buffers, so that a captured decode step can be replayed
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")
         self.m_seq_start, self.m_seq_slot, self.m_seq_pos0 = i32(2), i32(1), i32(1)
@@ -233,6 +299,13 @@ class TPRunner:
     def _into_residual(self, a, m, w):
         """Row-parallel projection: fp32 partial product, sum over the ranks, then the Residual epilogue as an op."""
         pkg = self.pkg
+        if self.peers is not None and m <= pkg.ALLREDUCE_ROWS:
+            # one kernel: the partial product, its sum over the ranks through peer memory, the residual update
+            ep = pkg.GemmEpilogue(pkg.EPI_ALLREDUCE_RESIDUAL, None, 0, 0, pkg.ptr(self.residual), pkg.ptr(self.xbf),
+                                  pkg.ptr(self.partials), None, 0, self.eps, C.pointer(self.peers.desc))
+            self._gemm(a, m, w, ep)
+            self.fused_calls += 1
+            return
         ep = pkg.GemmEpilogue(pkg.EPI_STORE_F32, pkg.ptr(self.delta), self.H, self.H, None, None, None, None, 0, self.eps)
         self._gemm(a, m, w, ep)
         if self.dist is not None:
@@ -350,6 +423,9 @@ class TPRunner:
         collectives keeps the communicator busy and the group's shutdown waits for it."""
         torch.cuda.synchronize()
         self._graph = None
+        if self.peers is not None:
+            self.peers.close(self.dist)
+            self.peers = None
 
     def device_error(self) -> int:
         return int(self.K.q38_device_error(1))

@@ -52,7 +52,67 @@ def test_single_rank_tp_runner_matches_reference():
         assert worst <= 2e-2
 
 
-def _worker(rank, world, port, out_dir, graph_from):
+def test_fused_allreduce_on_one_rank_equals_the_separate_path():
+    """The all-reduce inside the row-parallel GEMM (push of the tile to every rank's buffer, flags, bounded wait, sum in
+    rank order, residual update) with a world of one: the rank pushes to and pulls from itself, so every step of up to
+    16 tokens must give the logits of the path with a separate residual update - eagerly and as a replayed graph."""
+    import __graft_entry__ as entry
+    entry.load_package()
+    import q38b200
+    from q38b200 import tp
+    gold = np.load(GOLD / "tiny_cfg1_golden.npz")
+    prompt, gen = gold["prompt3"], gold["gen_unit3"]
+    runs = []
+    for fused in (False, True):
+        runner = tp.TPRunner(q38b200, GOLD / "tiny_cfg1_unit.q38", max_tokens=256, max_context=512, fused_allreduce=fused)
+        runner.forward(prompt, 0)
+        rows = [runner.logits()]
+        for step in range(12):
+            pos = len(prompt) + step
+            if step < 3:
+                runner.forward([int(gen[step])], pos)
+            elif step == 3:
+                runner.forward([int(t) for t in gen[3:8]], pos)  # five tokens in one step (still the fused path)
+            elif step >= 8:
+                runner.decode_replay(int(gen[step]), pos)
+            else:
+                continue
+            rows.append(runner.logits())
+        assert runner.device_error() == 0
+        assert (runner.fused_calls > 0) == fused
+        runs.append(rows)
+        runner.close()
+    assert len(runs[0]) == len(runs[1])
+    # the same sums in the same order; only the norm statistics are accumulated by another kernel (the GEMM epilogue's
+    # lane order instead of the update kernel's), which moves the logits in the last bits
+    for a, b in zip(*runs):
+        assert float(np.abs(a - b).max()) <= 1e-4 * float(np.abs(a).max())
+
+
+def test_fused_allreduce_wait_gives_up_when_a_rank_never_arrives():
+    """A world of two in which the other rank does not exist (its buffers are local stand-ins nobody writes): the wait
+    for its flag runs out after the given number of polls, the kernel records the error and completes, and the host
+    reads the error word. Nothing hangs and nothing faults; the context stays usable."""
+    import __graft_entry__ as entry
+    entry.load_package()
+    import q38b200
+    from q38b200 import tp
+    gold = np.load(GOLD / "tiny_cfg1_golden.npz")
+    runner = tp.TPRunner(q38b200, GOLD / "tiny_cfg1_unit.q38", 0, 2, None, max_tokens=256, max_context=512,
+                         fused_allreduce=True, poll_limit=2000)
+    runner.forward(gold["prompt3"][:64], 0)        # 64 tokens: the separate path, no wait
+    assert runner.device_error() == 0
+    runner.forward([int(gold["gen_unit3"][0])], 64)  # one token: the fused path waits for rank 1
+    torch.cuda.synchronize()
+    assert runner.device_error() == 0x120
+    assert runner.device_error() == 0                # the word was cleared by the read; the context still works
+    runner.forward(gold["prompt3"][:32], 65)
+    torch.cuda.synchronize()
+    assert runner.device_error() == 0
+    runner.close()
+
+
+def _worker(rank, world, port, out_dir, graph_from, fused=False):
     logf = open(Path(out_dir) / f"rank{rank}.log", "w")
 
     def log(*a):
@@ -67,11 +127,13 @@ def _worker(rank, world, port, out_dir, graph_from):
     import q38b200
     from q38b200 import tp
     log("process group up")
-    runner = tp.TPRunner(q38b200, GOLD / "tiny_cfg1_unit.q38", rank, world, dist, max_tokens=256, max_context=512)
+    runner = tp.TPRunner(q38b200, GOLD / "tiny_cfg1_unit.q38", rank, world, dist, max_tokens=256, max_context=512,
+                         fused_allreduce=fused)
     log("runner built")
     worst, agree = _check_against_golden(runner, "_unit", 3, graph_from=graph_from, log=log)
     log("checked", worst, agree)
     assert runner.reduce_calls > 0
+    assert (runner.fused_calls > 0) == fused
     runner.close()
     del runner
     log("closed")
@@ -91,13 +153,16 @@ def _log_dir(tmp_path, name):
 
 @pytest.mark.timeout(150)
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("fused", [False, True], ids=["nccl", "fused"])
 @pytest.mark.parametrize("graph_from", [99, 8], ids=["eager", "graph"])
-def test_two_rank_tp_runner_matches_reference(tmp_path, graph_from):
-    """Two NCCL ranks; "graph" replays the decode step (kernels and all-reduces) as a CUDA graph from step 8 on."""
+def test_two_rank_tp_runner_matches_reference(tmp_path, graph_from, fused):
+    """Two ranks; "graph" replays the decode step as a CUDA graph from step 8 on. "nccl": all-reduce by NCCL between the
+    GEMM and the residual update; "fused": decode steps sum the partial products inside the GEMM over peer memory (plain
+    loads and stores, no multicast), the 130-token prefill still goes through NCCL."""
     import torch.multiprocessing as mp
-    world, port = 2, 29100 + (os.getpid() + graph_from) % 2000
-    d = _log_dir(tmp_path, f"tp2_{graph_from}")
-    mp.spawn(_worker, args=(world, port, str(d), graph_from), nprocs=world, join=True)
+    world, port = 2, 29100 + (os.getpid() + graph_from + 7 * int(fused)) % 2000
+    d = _log_dir(tmp_path, f"tp2_{graph_from}_{int(fused)}")
+    mp.spawn(_worker, args=(world, port, str(d), graph_from, fused), nprocs=world, join=True)
     print([(d / f"ok{r}").read_text() for r in range(world)])
 
 
