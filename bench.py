@@ -354,6 +354,8 @@ def main():
                     help="trace: a prefill step and a separate decode step per iteration (the reference's schedule)")
     ap.add_argument("--trace-slice", type=int, default=64,
                     help="requests of the trace that the default run serves after the decode measurement (0 = none)")
+    ap.add_argument("--no-tp8", action="store_true",
+                    help="with 8 GPUs: leave out the tensor-parallel measurement of one 262,144-token request (tp8_262k)")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: reserve the KV pages but leave them zero-filled (the line is then not a bench value)")
     args = ap.parse_args()
@@ -554,9 +556,25 @@ def main():
         tr = run_trace(args, eng, model, rank, world, dist, config, barrier, num_requests=args.trace_slice * world, quiet=True)
         tr.pop("config", None)
         line["trace_slice"] = tr
+    model.close()
+    if world == 8 and args.layers == 64 and not args.no_tp8:
+        # The other multi-GPU mode of the path: ONE request of 262,144 tokens, tensor-parallel over the eight ranks
+        # (lean recipe; the whole context really prefilled; decode with the all-reduce inside the row-parallel GEMM and,
+        # for comparison, with NCCL all-reduces). About a minute; a failure is reported in the line, not raised.
+        try:
+            import q38b200
+            sys.path.insert(0, str(Path(q38b200.__file__).resolve().parent))
+            import tp_bench
+            tp8 = tp_bench.measure(q38b200, dist, rank, world, context=262144, real_prefill=-1, steps=20,
+                                   prefill_budget_s=60.0)
+            line["tp8_262k"] = {k: tp8[k] for k in ("value", "unit", "ms_per_step", "ms_per_step_nccl_allreduce",
+                                                     "context_tokens", "recipe", "prefill_tokens_really_run",
+                                                     "prefill_total_s", "prefill_512_at_context_end_ms",
+                                                     "prefill_tok_per_s_short_context", "allreduce", "device_error")}
+        except Exception as exc:  # noqa: BLE001 - the replica benchmark above stands on its own
+            line["tp8_262k"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if rank == 0:
         print(json.dumps(line))
-    model.close()
     if dist is not None:
         dist.destroy_process_group()
 

@@ -118,7 +118,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
-// 2-D tiled tensor-map load (no multicast). x is the innermost coordinate: x * elem_size % 16 == 0.
+// 2-D tiled tensor-map load into this CTA only. x is the innermost coordinate: x * elem_size % 16 == 0.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

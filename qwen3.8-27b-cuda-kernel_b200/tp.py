@@ -204,6 +204,7 @@ class TPRunner:
         self.rank, self.world = rank, world
         self.peers = None
         self._fused, self._poll_limit = fused_allreduce, poll_limit
+        self.use_fused = True  # False: keep the peer buffers but take the NCCL path (for comparisons)
         f = bq.Q38File(model_path)
         cfg = self.cfg = f.config
         plan = self.plan = rank_plan(cfg, rank, world)
@@ -299,7 +300,7 @@ class TPRunner:
     def _into_residual(self, a, m, w):
         """Row-parallel projection: fp32 partial product, sum over the ranks, then the Residual epilogue as an op."""
         pkg = self.pkg
-        if self.peers is not None and m <= pkg.ALLREDUCE_ROWS:
+        if self.peers is not None and self.use_fused and m <= pkg.ALLREDUCE_ROWS:
             # one kernel: the partial product, its sum over the ranks through peer memory, the residual update
             ep = pkg.GemmEpilogue(pkg.EPI_ALLREDUCE_RESIDUAL, None, 0, 0, pkg.ptr(self.residual), pkg.ptr(self.xbf),
                                   pkg.ptr(self.partials), None, 0, self.eps, C.pointer(self.peers.desc))

@@ -158,7 +158,7 @@ def _log_dir(tmp_path, name):
 def test_two_rank_tp_runner_matches_reference(tmp_path, graph_from, fused):
     """Two ranks; "graph" replays the decode step as a CUDA graph from step 8 on. "nccl": all-reduce by NCCL between the
     GEMM and the residual update; "fused": decode steps sum the partial products inside the GEMM over peer memory (plain
-    loads and stores, no multicast), the 130-token prefill still goes through NCCL."""
+    loads and stores only), the 130-token prefill still goes through NCCL."""
     import torch.multiprocessing as mp
     world, port = 2, 29100 + (os.getpid() + graph_from + 7 * int(fused)) % 2000
     d = _log_dir(tmp_path, f"tp2_{graph_from}_{int(fused)}")
