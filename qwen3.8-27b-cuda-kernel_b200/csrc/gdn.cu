@@ -350,7 +350,7 @@ constexpr int kDecStateBytes = kDv * kDk * 4;
 constexpr int kDecQOff = kDecStateBytes, kDecKOff = kDecQOff + 512, kDecVOff = kDecKOff + 512, kDecZOff = kDecVOff + 512;
 constexpr int kDecSlotBytes = kDecStateBytes + 2048;
 constexpr int kDecTxBytes = kDecStateBytes + 3 * 512 + 256;
-constexpr int kDecSmemBytes = 128 + kDecSlots * kDecSlotBytes + (kDv + kRecWarps) * 4 + 2 * kDecSlots * 8 + 16;
+constexpr int kDecSmemBytes = 128 + kDecSlots * kDecSlotBytes + 2 * (kDv + 2 * kRecWarps) * 4 + 2 * kDecSlots * 8 + 16;
 constexpr int kDecThreads = (kRecWarps + 1) * 32;
 
 __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
@@ -362,9 +362,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
   extern __shared__ uint8_t dec_smem_raw[];
   uint8_t* smem = dec_smem_raw + ((128 - (smem_u32(dec_smem_raw) & 127)) & 127);
   uint8_t* slots = smem;
-  float* o_sm = reinterpret_cast<float*>(smem + kDecSlots * kDecSlotBytes);
-  float* red = o_sm + kDv;
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + kRecWarps);
+  // outputs, partial sums of squares and the warps' wait results of an item: two sets used in turn, so that one barrier
+  // per item is enough (a warp may start the next item while the others still read this one's set)
+  float* o_sm_all = reinterpret_cast<float*>(smem + kDecSlots * kDecSlotBytes);
+  float* red_all = o_sm_all + 2 * kDv;
+  int* okf_all = reinterpret_cast<int*>(red_all + 2 * kRecWarps);
+  uint64_t* full = reinterpret_cast<uint64_t*>(okf_all + 2 * kRecWarps);
   uint64_t* empty = full + kDecSlots;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kDecSlots);  // [0] compute warps, [1] producer
 
@@ -443,6 +446,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
     // a wait that runs out marks the launch as failed; the warps leave the loop together below
     const bool ok = mbar_wait(&full[slot], (it / kDecSlots) & 1, 0x402);
     if (!ok) abort_flag[0] = 1;
+    float* o_sm = o_sm_all + (it & 1u) * kDv;
+    float* red = red_all + (it & 1u) * kRecWarps;
+    int* okf = okf_all + (it & 1u) * kRecWarps;
     const uint8_t* src = slots + (size_t)slot * kDecSlotBytes;
     float4 st[kRowsPerWarp];
     float vv[kRowsPerWarp];
@@ -487,7 +493,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
     float ss = 0.0f;
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r) ss += ov[r] * ov[r];
-    if (lane == 0) red[warp] = ss;
+    if (lane == 0) {
+      red[warp] = ss;
+      okf[warp] = ok ? 1 : 0;
+    }
     if (lane < kRowsPerWarp) {
       float mine = ov[0];
 #pragma unroll
@@ -496,7 +505,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
       o_sm[row0 + lane] = mine;
     }
     named_bar_sync(1, kRecWarps * 32);
-    const int stop = abort_flag[0];  // written only before the barrier above: the same value in every compute warp
+    // a wait of any warp ran out: all of them leave after this item (the item's set was written before the barrier, so
+    // every warp reads the same value)
+    int stop = 0;
+#pragma unroll
+    for (int w = 0; w < kRecWarps; ++w) stop |= okf[w] ^ 1;
     if (tid < kDv && ok) {
       float total = 0.0f;
 #pragma unroll
@@ -504,7 +517,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) gdn_recurrence_decode_kernel(
       const float r = 1.0f / sqrtf(total / float(kDv) + eps);
       out[(size_t)m * nv * kDv + (size_t)vh * kDv + tid] = __float2bfloat16_rn(o_sm[tid] * r * nw * silu_f(zz));
     }
-    named_bar_sync(1, kRecWarps * 32);
     if (stop) break;
     ++it;
   }
