@@ -648,6 +648,22 @@ __device__ __forceinline__ void dequant16_to_half(const uint4& raw, __half scale
   *reinterpret_cast<uint4*>(dst + 16) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
 }
 
+// 8 bf16 values (16 bytes) -> 8 fp16 values (exact for every magnitude an fp16 holds; K and V rows are O(1))
+__device__ __forceinline__ uint4 bf16x8_to_half(const uint4& raw) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// kInt8: int8 pages with fp16 scales, brought in by bulk copies through the raw ring and dequantised; otherwise bf16
+// pages, read with plain 16-byte loads and converted on the way into the same fp16 tiles (no ring: this is not the
+// benchmarked cache type, the loads of a page are simply exposed).
+template <bool kInt8>
 __global__ void __launch_bounds__(kPfThreads, 1) attn_prefill_tile_kernel(
     const __half* __restrict__ q, const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ out,
     int nq, int group, int layer, int tq, int tiles_per_seq, float* __restrict__ scratch, int max_splits, int num_splits,
@@ -715,7 +731,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) attn_prefill_tile_kernel(
   }
   __syncthreads();
 
-  if (tid == 0) {  // barriers are initialised (the __syncthreads above): the first two pages
+  if (kInt8 && tid == 0) {  // barriers are initialised (the __syncthreads above): the first two pages
     request_page(p0, 0);
     if (p0 + 1 < p1) request_page(p0 + 1, 1);
   }
@@ -743,11 +759,37 @@ __global__ void __launch_bounds__(kPfThreads, 1) attn_prefill_tile_kernel(
 
   for (int p = p0, it = 0; p < p1; ++p, ++it) {
     const int s = it % kPfStages;
-    bool ok = !*abort_flag && mbar_wait(&full[s], (it / kPfStages) & 1, 0x223);
+    bool ok = !*abort_flag && (!kInt8 || mbar_wait(&full[s], (it / kPfStages) & 1, 0x223));
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) *abort_flag = 1;
     // ---- the page's K and V as fp16 tiles, once for all rows of the tile ----
-    if (ok) {
+    if constexpr (!kInt8) {
+      if (ok) {
+        const int page = kv.block_table[(size_t)slot * kv.max_pages_per_seq + p];  // the same entry in every thread
+        if (page < 0 || page >= kv.num_pages) {
+          if (tid == 0) report_error(0x222);
+          *abort_flag = 1;
+          ok = false;
+        } else {
+          const uint8_t* base = kv.pool + (size_t)layer * kv.layer_stride + (size_t)page * kv.page_bytes;
+          const uint8_t* ksrc = base + kv.k_off(kvh, 0);
+          const uint8_t* vsrc = base + kv.v_off(kvh, 0);
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int u = tid + kPfConsumers * r;  // 16-byte group: key u / 32, dims 8 (u % 32) ..
+            const int key = u >> 5, ch = u & 31;
+            uint4 kh = make_uint4(0u, 0u, 0u, 0u), vh = kh;  // positions nobody has written yet stay zero
+            if (p * kPage + key < L) {
+              kh = bf16x8_to_half(__ldg(reinterpret_cast<const uint4*>(ksrc) + u));
+              vh = bf16x8_to_half(__ldg(reinterpret_cast<const uint4*>(vsrc) + u));
+            }
+            *reinterpret_cast<uint4*>(Kh + (size_t)key * kPfHStride + 16 * ch) = kh;
+            *reinterpret_cast<uint4*>(Vh + (size_t)key * kPfHStride + 16 * ch) = vh;
+          }
+        }
+      }
+    }
+    if (kInt8 && ok) {
       const uint8_t* st = dsm + (size_t)s * kStageBytes;
       const __half* Ksc = reinterpret_cast<const __half*>(st + kStageKs);
       const __half* Vsc = reinterpret_cast<const __half*>(st + kStageVs);
@@ -770,7 +812,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) attn_prefill_tile_kernel(
       }
     }
     __syncthreads();  // the fp16 tiles are complete, the raw stage is free: the page after next streams in during the products
-    if (tid == 0 && p + kPfStages < p1 && !*abort_flag) request_page(p + kPfStages, s);
+    if (kInt8 && tid == 0 && p + kPfStages < p1 && !*abort_flag) request_page(p + kPfStages, s);
 
     const int kbase = p * kPage;
     if (ok && warp_live && kbase <= warp_last) {
@@ -1057,14 +1099,17 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
   if (rc != Q38_OK) return rc;
   if (batch->num_tokens == 0) return Q38_OK;
   const int group = p->num_q_heads / p->num_kv_heads;
-  if (kv->dtype != Q38_KV_INT8) return dispatch_group(group, *p, *batch, *kv, false, 1, as_stream(stream));
+  const bool int8 = kv->dtype == Q38_KV_INT8;
   if (batch->max_tokens_per_seq > 1 && group >= 1 && group <= kPfRows) {
     // chunks of more than one token: the query-tiled kernel. With few tiles for the GPU (one long request, or a
     // tensor-parallel rank with one kv head) the keys are cut over several CTAs per tile when the caller's scratch
     // (laid out [token][q head][max_splits][258]) allows it.
     static const cudaError_t attr_pf =
-        cudaFuncSetAttribute(attn_prefill_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
+        cudaFuncSetAttribute(attn_prefill_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
+    static const cudaError_t attr_pf16 =
+        cudaFuncSetAttribute(attn_prefill_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
     Q38_CUDA_OK(attr_pf);
+    Q38_CUDA_OK(attr_pf16);
     const int tq = kPfRows / group;
     const int tiles_per_seq = (batch->max_tokens_per_seq + tq - 1) / tq;
     const int tiles = (batch->num_tokens + tq - 1) / tq + batch->num_seqs;  // upper bound of the live tiles
@@ -1076,10 +1121,11 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
     const cudaStream_t s = as_stream(stream);
     const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p->gate);
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p->out);
-    (void)launch_kernel(attn_prefill_tile_kernel, dim3(splits, p->num_kv_heads, batch->num_seqs * tiles_per_seq),
-                        dim3(kPfThreads), kPfSmem, s, reinterpret_cast<const __half*>(p->q), gate, p->ld_gate, out,
-                        p->num_q_heads, group, p->attn_layer, tq, tiles_per_seq, p->split_scratch, p->max_splits, splits,
-                        batch->seq_start, batch->seq_slot, batch->seq_pos0, make_view(*kv));
+    (void)launch_kernel(int8 ? attn_prefill_tile_kernel<true> : attn_prefill_tile_kernel<false>,
+                        dim3(splits, p->num_kv_heads, batch->num_seqs * tiles_per_seq), dim3(kPfThreads), kPfSmem, s,
+                        reinterpret_cast<const __half*>(p->q), gate, p->ld_gate, out, p->num_q_heads, group, p->attn_layer,
+                        tq, tiles_per_seq, p->split_scratch, p->max_splits, splits, batch->seq_start, batch->seq_slot,
+                        batch->seq_pos0, make_view(*kv));
     Q38_LAUNCH_OK("attn_prefill_tile_kernel");
     if (splits > 1) {
       (void)launch_kernel(attn_merge_kernel, dim3(p->num_q_heads, batch->num_tokens), dim3(kHd), 0, s, p->split_scratch,
@@ -1088,6 +1134,7 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
     }
     return Q38_OK;
   }
+  if (!int8) return dispatch_group(group, *p, *batch, *kv, false, 1, as_stream(stream));
   // single-token chunks: the decode kernel, one CTA per (kv head, token)
   Q38_REQUIRE(group >= 1 && group <= 8, "attention: GQA group %d is not implemented (1..8)", group);
   static const cudaError_t attr =

@@ -476,13 +476,15 @@ def test_attention_decode_16_sequences_up_to_32768():
         assert np.all(np.abs(out_got[s] - want) <= 2e-2 * (np.abs(want) + 0.02 * np.abs(want).max())), (s, c)
 
 
+@pytest.mark.parametrize("dtype", [0, 1], ids=["int8", "bf16"])
 @pytest.mark.parametrize("nq,nkv,split_rows", [(24, 4, 4), (3, 1, 800)])
-def test_attention_prefill_ragged_chunks_at_long_prefixes(nq, nkv, split_rows):
+def test_attention_prefill_ragged_chunks_at_long_prefixes(nq, nkv, split_rows, dtype):
     """One ragged prefill step of three sequences: a 512-token chunk behind an 8,200-token prefix, a 200-token chunk
     behind 300 tokens and a 65-token chunk at position 0 (query tiles that start inside a page, end inside a page and
     span pages). 24 q / 4 kv heads is the 27B layer (ten tokens x six heads per tile); 3 q / 1 kv head is one rank of
     the 8-way tensor-parallel layout, where the few tiles cut their keys over several CTAs and the merge kernel
-    finishes (the scratch is sized per token for it). The oracle attends over the cache as the kernel wrote it, on a
+    finishes (the scratch is sized per token for it). Both cache types: int8 pages come through the raw ring, bf16 pages
+    by plain loads into the same fp16 tiles. The oracle attends over the cache as the kernel wrote it, on a
     sample of the prompt tokens (every position of the short chunks, every 29th and the ends of the long one)."""
     ld = 2 * nq * 256 + 2 * nkv * 256
     r3 = np.random.default_rng(3)
@@ -491,7 +493,7 @@ def test_attention_prefill_ragged_chunks_at_long_prefixes(nq, nkv, split_rows):
     qn_dev, kn_dev = torch.from_numpy(qn).cuda(), torch.from_numpy(kn).cuda()
     prefix, chunk, slots, layer = [8200, 300, 0], [512, 200, 65], [2, 0, 1], 1
     need = [(a + c + 63) // 64 for a, c in zip(prefix, chunk)]
-    pool = tl.KvPool(nkv, layers=2, num_pages=sum(need) + 3, slots=3, max_pages_per_seq=max(need), dtype=0)
+    pool = tl.KvPool(nkv, layers=2, num_pages=sum(need) + 3, slots=3, max_pages_per_seq=max(need), dtype=dtype)
     perm = np.random.default_rng(5).permutation(sum(need) + 3).astype(np.int32)
     used = 0
     for s, pages in zip(slots, need):
