@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __re
                                                        const int* __restrict__ seq_start,
                                                        const int* __restrict__ seq_slot,
                                                        const int* __restrict__ tok_seq, int roll_state, int num_tokens,
-                                                       int tokens_per_cta) {
+                                                       int tokens_per_cta, int one_token_each) {
   pdl_wait();               // everything written by earlier kernels of the stream is visible from here on
   pdl_launch_dependents();  // the next kernel may be scheduled now; it holds its own dependent work back the same way
   __shared__ float red[4];
@@ -114,8 +114,10 @@ __global__ void __launch_bounds__(128) gdn_conv_kernel(const __nv_bfloat16* __re
   const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)c * 4);
   const int m_end = min(num_tokens, (int(blockIdx.y) + 1) * tokens_per_cta);
   for (int m = blockIdx.y * tokens_per_cta; m < m_end; ++m) {
-    const int b = tok_seq[m];
-    const int i = m - seq_start[b];  // index of the token inside its sequence's chunk
+    // one_token_each (a decode batch: every sequence has exactly one token, so token m is sequence m's and the first of
+    // its run): two dependent loads fewer on the way to the taps
+    const int b = one_token_each ? m : tok_seq[m];
+    const int i = one_token_each ? 0 : m - seq_start[b];  // index of the token inside its sequence's chunk
     __nv_bfloat16* st = conv_state + ((size_t)seq_slot[b] * num_layers + layer) * 3 * conv_dim;
     float x[4];
     __nv_bfloat16 xb[4];
@@ -1220,7 +1222,7 @@ extern "C" int q38_gdn_conv(const q38_gdn_conv_params* p, const q38_gdn_dims* d,
     (void)launch_kernel(gdn_conv_kernel, dim3(d->conv_dim / 128, (batch->num_tokens + per_cta - 1) / per_cta),
                         dim3(128), 0, s, proj, d->ld_proj, p->conv_w, p->qkv, d->conv_dim, d->num_k_heads * 128,
                         p->gdn_layer, st->num_gdn_layers, cs, batch->seq_start, batch->seq_slot, batch->tok_seq, roll,
-                        batch->num_tokens, per_cta);
+                        batch->num_tokens, per_cta, (roll && batch->num_tokens == batch->num_seqs) ? 1 : 0);
     Q38_LAUNCH_OK("gdn_conv_kernel");
   }
   if (roll) return Q38_OK;
