@@ -1115,8 +1115,21 @@ extern "C" int q38_attention_prefill(const q38_attention_params* p, const q38_ba
     const int tiles = (batch->num_tokens + tq - 1) / tq + batch->num_seqs;  // upper bound of the live tiles
     int splits = 1;
     if (p->split_scratch && p->max_splits > 1 && p->scratch_rows >= batch->num_tokens) {
-      splits = (2 * num_sms()) / std::max(1, tiles * p->num_kv_heads);
-      splits = std::max(1, std::min(splits, std::min(p->max_splits, 16)));
+      // The cut that gives every CTA the fewest keys per wave of CTAs: s / ceil(tiles * kv heads * s / SMs) is largest
+      // (thirteen tiles of one kv head: eleven cuts fill one wave of 143 CTAs, sixteen would need two waves of longer
+      // tails). One sequence: the tile count is exact; otherwise it is the upper bound above. Up to two waves.
+      const int live = (batch->num_seqs == 1 ? tiles_per_seq : tiles) * p->num_kv_heads;
+      const int sms = num_sms(), cap = std::min(p->max_splits, 16);
+      double best = 0.0;
+      for (int c = 1; c <= cap; ++c) {
+        const int waves = (live * c + sms - 1) / sms;
+        if (waves > 2) break;
+        const double gain = double(c) / waves;
+        if (gain > best * 1.02) {  // a further cut must pay for its share of the merge
+          best = gain;
+          splits = c;
+        }
+      }
     }
     const cudaStream_t s = as_stream(stream);
     const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(p->gate);
