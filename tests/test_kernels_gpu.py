@@ -842,3 +842,25 @@ def test_launchers_reject_bad_arguments_without_launching():
     bad = pkg.BQWeight(w.desc.lo, None, w.desc.scales, 7, 128, 64, 128)
     assert K().q38_qgemm(pkg.ptr(a), 1, C.byref(bad), C.byref(ep), None, None, -1) == -1
     assert K().q38_embed(None, None, 0, 128, None, None, None, None) == 0  # m == 0 is a no-op
+    # the all-reduce epilogue: its peer description is required, it serves up to 16 tokens, and only the streaming kernel
+    res = torch.zeros((32, 128), dtype=torch.float32, device="cuda")
+    xbf = torch.zeros((32, 128), dtype=torch.bfloat16, device="cuda")
+    part = torch.zeros((32, 1), dtype=torch.float32, device="cuda")
+    ep = pkg.GemmEpilogue(pkg.EPI_ALLREDUCE_RESIDUAL, None, 0, 0, pkg.ptr(res), pkg.ptr(xbf), pkg.ptr(part), None, 0, 1e-6)
+    assert K().q38_qgemm(pkg.ptr(a), 1, C.byref(w.desc), C.byref(ep), None, None, -1) == -1
+    assert b"peer description" in K().q38_last_error()
+    ar = pkg.PeerAllreduce()
+    ar.world, ar.rank = 1, 0
+    buf = torch.zeros(2 * 16 * 128, dtype=torch.float32, device="cuda")
+    words = torch.zeros(8, dtype=torch.int32, device="cuda")
+    ar.recv[0], ar.flags[0], ar.seq = pkg.ptr(buf), pkg.ptr(words), pkg.ptr(words) + 16
+    ep = pkg.GemmEpilogue(pkg.EPI_ALLREDUCE_RESIDUAL, None, 0, 0, pkg.ptr(res), pkg.ptr(xbf), pkg.ptr(part), None, 0, 1e-6,
+                          C.pointer(ar))
+    a32 = torch.zeros((32, 64), dtype=torch.bfloat16, device="cuda")
+    assert K().q38_qgemm(pkg.ptr(a32), 17, C.byref(w.desc), C.byref(ep), None, None, -1) == -1
+    assert b"up to 16 tokens" in K().q38_last_error()
+    names = {K().q38_qgemm_config_name(c).decode(): c for c in range(K().q38_qgemm_num_configs())}
+    assert K().q38_qgemm(pkg.ptr(a32), 8, C.byref(w.desc), C.byref(ep), None, None, names["tmem_t32"]) == -1
+    assert b"streaming kernel only" in K().q38_last_error()
+    ar.world = 9
+    assert K().q38_qgemm(pkg.ptr(a), 1, C.byref(w.desc), C.byref(ep), None, None, -1) == -1
